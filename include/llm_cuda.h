@@ -1,0 +1,223 @@
+/* llm_cuda.h - C ABI of the B200 token sampler.
+ *
+ * One path of biffjezos/scriptonait behind a plain C boundary: the per-row
+ * sampler `sample_with` (crates/llm-core/src/generate.rs:325-420) - allowed
+ * mask, repetition penalty over a token history, temperature, top-k, min-p,
+ * top-p and a seeded categorical draw - batched over the rows of a logits
+ * matrix that already lives in GPU memory. The parameter surface is the
+ * reference's (`temperature, top_k, top_p, min_p, repetition_penalty, seed`,
+ * crates/llm-core/src/generate.rs:24-95; crates/wasm-app/src/inference.rs:90-108).
+ *
+ * Conventions
+ *  - every function returns an int32_t status (LLM_CUDA_OK or a negative
+ *    LLM_CUDA_ERR_*); nothing throws or aborts across this boundary;
+ *  - "device pointer" = memory of the handle's GPU; the caller owns all
+ *    buffers and the stream; the library owns only the handle's scratch;
+ *  - calls that take device pointers are asynchronous on `stream`;
+ *  - a handle is used from one host thread and one stream at a time;
+ *  - there is no CPU fallback: without a usable GPU every call fails.
+ */
+#ifndef LLM_CUDA_H
+#define LLM_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LLM_CUDA_ABI_VERSION 1u
+
+/* status codes */
+#define LLM_CUDA_OK 0
+#define LLM_CUDA_ERR_BAD_ARGUMENT (-1)  /* NULL where a pointer is required, wrong struct_size, bad dtype, ... */
+#define LLM_CUDA_ERR_CAPACITY (-2)      /* batch / vocab / history / top_k beyond what the handle was created for */
+#define LLM_CUDA_ERR_CUDA (-3)          /* a CUDA runtime call failed; see llm_cuda_last_error */
+#define LLM_CUDA_ERR_UNSUPPORTED (-4)   /* e.g. vocabulary sharding with top_k == 0 */
+#define LLM_CUDA_ERR_NO_DEVICE (-5)     /* no CUDA device / wrong architecture */
+
+/* logits element types */
+#define LLM_CUDA_DTYPE_F32 0u
+#define LLM_CUDA_DTYPE_BF16 1u /* widened exactly to f32 (crates/llm-core/src/bf16.rs:22-25) before any arithmetic */
+
+/* per-row flags written to `row_flags` */
+#define LLM_CUDA_ROW_GREEDY 1u         /* temperature <= 0: argmax after mask+penalty, no draw consumed (generate.rs:354-356) */
+#define LLM_CUDA_ROW_DEGENERATE 2u     /* softmax sum <= 0 or not finite: first id of the ordering returned, no draw consumed (generate.rs:375-377) */
+#define LLM_CUDA_ROW_FALLBACK_LAST 4u  /* the walk ran past the kept set: last kept id returned (generate.rs:419) */
+#define LLM_CUDA_ROW_DRAW_CONSUMED 8u  /* exactly one RNG output was used: the caller advances draw_index by one */
+#define LLM_CUDA_ROW_FULL_SORT 16u     /* the row was resolved by the full-sort kernel (candidate window too small) */
+#define LLM_CUDA_ROW_INVALID 64u       /* a per-row parameter was NaN; token 0 returned */
+#define LLM_CUDA_ROW_WINDOWED 128u     /* ordering ran on the significant-value window, not on a top-k list */
+
+/* The end-of-text id the allowed mask never blocks (crates/llm-core/src/tokenizer.rs:38). */
+#define LLM_CUDA_EOS_DEFAULT 258u
+
+/* Number of floats per row in `row_stats`: max, sum, total, u, min-p threshold, r = u*total. */
+#define LLM_CUDA_ROW_STATS 6u
+
+typedef struct llm_cuda_sampler llm_cuda_sampler; /* opaque */
+
+/* Mirrors `SamplingConfig` (crates/llm-core/src/generate.rs:24-95) for the one-row
+ * host wrapper. `llm_cuda_sampling_config_default` fills the reference's defaults
+ * (generate.rs:82-95): 0.9 / 40 / 0.95 / 0.0 / 1.1 / 128 / 0 / no mask. */
+typedef struct llm_cuda_sampling_config {
+    float temperature;          /* <= 0 means greedy */
+    uint32_t top_k;             /* 0 disables */
+    float top_p;                /* 1.0 disables */
+    float min_p;                /* 0.0 disables */
+    float repetition_penalty;   /* 1.0 disables */
+    uint32_t repetition_window; /* how many trailing history tokens the caller passes as `recent` */
+    uint64_t seed;
+    const uint8_t* allowed;     /* host, one byte per id (0 = blocked), or NULL = allow everything */
+    uint32_t allowed_len;       /* ids >= allowed_len count as allowed */
+} llm_cuda_sampling_config;
+
+/* Batched call: row r of `logits` is one independent `sample_with`.
+ * Scalars apply to every row unless the matching *_rows device array is given. */
+typedef struct llm_cuda_sample_args {
+    uint32_t struct_size;       /* = sizeof(llm_cuda_sample_args) */
+    uint32_t logits_dtype;      /* LLM_CUDA_DTYPE_* */
+    const void* logits;         /* device, [batch, row_stride_elems]; read only, never modified (generate.rs:331) */
+    uint32_t batch;
+    uint32_t vocab;             /* columns of this matrix */
+    uint64_t row_stride_elems;  /* elements between rows; 0 = every row reads row 0 */
+
+    float temperature;
+    uint32_t top_k;
+    float top_p;
+    float min_p;
+    float repetition_penalty;
+    uint32_t reserved0;
+    const float* temperature_rows;        /* device [batch] or NULL */
+    const uint32_t* top_k_rows;           /* device [batch] or NULL */
+    const float* top_p_rows;              /* device [batch] or NULL */
+    const float* min_p_rows;              /* device [batch] or NULL */
+    const float* repetition_penalty_rows; /* device [batch] or NULL */
+
+    const uint32_t* history;     /* device [batch, history_stride] token ids (any value, repeats allowed), or NULL */
+    uint32_t history_stride;
+    uint32_t history_len;        /* used when history_len_rows is NULL; <= history_stride */
+    const uint32_t* history_len_rows; /* device [batch] or NULL */
+
+    const uint32_t* allowed_bits; /* device, bit i of word i/32 set = id i allowed; NULL = allow everything */
+    uint32_t allowed_len;         /* ids >= allowed_len count as allowed */
+    uint32_t eos_id;              /* never blocked by the mask */
+
+    const uint64_t* seeds;       /* device [batch]: Rng::seed_from_u64(seeds[r]); NULL = seed_base + r */
+    const uint64_t* draw_index;  /* device [batch]: outputs already consumed from that Rng; NULL = 0 */
+    uint64_t seed_base;
+    const float* uniforms;       /* device [batch] or NULL: replaces rng.next_f32() (pins the uniform stream) */
+
+    uint32_t* tokens;            /* device [batch], out */
+
+    /* optional per-stage outputs (NULL to skip) */
+    uint32_t* row_flags;         /* device [batch] LLM_CUDA_ROW_* */
+    uint32_t* kept_count;        /* device [batch]: size of the kept set */
+    uint32_t* kept_ids;          /* device [batch, kept_capacity]: kept ids, most likely first */
+    float* kept_probs;           /* device [batch, kept_capacity]: their probabilities p_i / sum */
+    uint32_t kept_capacity;
+    uint32_t reserved1;
+    float* row_stats;            /* device [batch, LLM_CUDA_ROW_STATS] */
+
+    /* vocabulary sharding (llm_cuda_shard_select only; 0 / vocab otherwise) */
+    uint32_t column_offset;      /* global id of column 0 of this matrix */
+    uint32_t vocab_global;       /* 0 = vocab */
+
+    uint32_t split;              /* CTAs per row; 0 = choose */
+    uint32_t force_full_sort;    /* testing aid: resolve every row with the full-sort kernel */
+    void* stream;                /* cudaStream_t */
+} llm_cuda_sample_args;
+
+/* Reference defaults (generate.rs:82-95). */
+void llm_cuda_sampling_config_default(llm_cuda_sampling_config* out);
+
+/* Creates a sampler bound to `device` with scratch sized for the given maxima.
+ * Replaces nothing in the reference (it allocates two Vecs per call,
+ * generate.rs:331,364); this is where the device scratch those become lives. */
+int32_t llm_cuda_sampler_create(int32_t device, uint32_t max_batch, uint32_t max_vocab, uint32_t max_history,
+                                uint32_t max_top_k, llm_cuda_sampler** out);
+int32_t llm_cuda_sampler_destroy(llm_cuda_sampler* s);
+
+/* Text of the last error on this handle (or of the last failed create when s is NULL). */
+const char* llm_cuda_last_error(const llm_cuda_sampler* s);
+
+/* Batched `sample_with` over device buffers - the hot path.
+ * Replaces the sampling call of the GPU generation loop
+ * (crates/wasm-app/src/inference.rs:326-327) and of Generator::step
+ * (crates/llm-core/src/generate.rs:157-165), without the per-token logits
+ * read-back (crates/llm-gpu/src/model.rs:483-490,520-550). */
+int32_t llm_cuda_sample_batch(llm_cuda_sampler* s, const llm_cuda_sample_args* args);
+
+/* Same call with every array in HOST memory: copies inputs to the device, runs
+ * llm_cuda_sample_batch, copies `tokens` (and any requested per-stage outputs)
+ * back and synchronises. Pointers in `args` are host pointers here. This is the
+ * path a caller takes whose logits were produced on the host, as the reference's
+ * CPU generation loop does (crates/llm-core/src/generate.rs:157-165). */
+int32_t llm_cuda_sample_batch_host(llm_cuda_sampler* s, const llm_cuda_sample_args* host_args);
+
+/* One row, host buffers, the reference's own signature:
+ * sample_with(logits, sampling, recent, rng) -> token (generate.rs:325-330).
+ * `rng_state` is the SplitMix64 state word (crates/llm-core/src/rng.rs:6-22); it
+ * is advanced by one output exactly when the reference would draw. */
+int32_t llm_cuda_sample_with(llm_cuda_sampler* s, const float* logits, uint32_t vocab,
+                             const llm_cuda_sampling_config* sampling, const uint32_t* recent, uint32_t n_recent,
+                             uint64_t* rng_state, uint32_t* token_out);
+
+/* sample(logits, temperature, rng) (generate.rs:423-433): temperature only. */
+int32_t llm_cuda_sample(llm_cuda_sampler* s, const float* logits, uint32_t vocab, float temperature,
+                        uint64_t* rng_state, uint32_t* token_out);
+
+/* Vocabulary sharding, step 1 of 2: this GPU holds columns
+ * [column_offset, column_offset + vocab) of every row. Applies mask, penalty
+ * and temperature to its columns and writes, per row, its best
+ * min(top_k, vocab) candidates in order (value descending, global id ascending)
+ * - the ordering of generate.rs:364-367 - into
+ * cand_values[batch, cand_stride] / cand_ids[batch, cand_stride], with the
+ * number written in cand_count[batch]. Requires 0 < top_k <= cand_stride; greedy
+ * rows (temperature <= 0) send one candidate. No reference counterpart (the
+ * reference is single-device); exact because the global top-k is a subset of
+ * the union of per-shard top-k lists and the softmax runs over the kept k only
+ * (generate.rs:368-380). */
+int32_t llm_cuda_shard_select(llm_cuda_sampler* s, const llm_cuda_sample_args* args, float* cand_values,
+                              uint32_t* cand_ids, uint32_t* cand_count, uint32_t cand_stride);
+
+/* Vocabulary sharding, step 2 of 2: after the candidate lists of all `n_shards`
+ * have been gathered as [n_shards, batch, cand_stride] (+ counts
+ * [n_shards, batch]), merges them per row with the same comparator and runs
+ * softmax, min-p, top-p and the draw (generate.rs:368-419). `args` supplies the
+ * parameters, RNG and outputs; its logits/history fields are ignored. Every
+ * rank that calls this with the same inputs gets the same tokens. */
+int32_t llm_cuda_merge_draw(llm_cuda_sampler* s, const llm_cuda_sample_args* args, const float* cand_values,
+                            const uint32_t* cand_ids, const uint32_t* cand_count, uint32_t n_shards,
+                            uint32_t cand_stride);
+
+/* Device-side decode-loop glue (Generator::step / recent_tokens,
+ * crates/llm-core/src/generate.rs:157-182; the EOS test of
+ * crates/wasm-app/src/inference.rs:326-333): for each row that is not finished,
+ * appends tokens[r] to its history ring (history[r, (history_pos[r]) % history_stride]),
+ * bumps history_pos / history_len (capped at the window), adds one to
+ * draw_index[r] when row_flags[r] has DRAW_CONSUMED, and sets finished[r] when the
+ * token is eos_id (the token is then not appended, as step() returns None).
+ * All pointers are device pointers; asynchronous on `stream`. */
+int32_t llm_cuda_advance_rows(llm_cuda_sampler* s, uint32_t batch, const uint32_t* tokens, const uint32_t* row_flags,
+                              uint32_t* history, uint32_t history_stride, uint32_t window, uint32_t* history_len,
+                              uint32_t* history_pos, uint64_t* draw_index, uint8_t* finished, uint32_t eos_id,
+                              void* stream);
+
+/* Packs a host bool-per-id slice (Corpus::seen_tokens, crates/llm-core/src/corpus.rs:236-246;
+ * SamplingConfig::allowed, generate.rs:67-80) into the device bit mask
+ * `allowed_bits` expects: ceil(n/32) words. `bits_out` is a device pointer. */
+int32_t llm_cuda_pack_allowed(llm_cuda_sampler* s, const uint8_t* allowed_host, uint32_t n, uint32_t* bits_out,
+                              void* stream);
+
+/* Launch statistics of the last call on this handle (for benchmarks): how many
+ * kernels it launched and the CTAs-per-row split it chose. */
+int32_t llm_cuda_last_launch_info(const llm_cuda_sampler* s, uint32_t* kernels_launched, uint32_t* split_used);
+
+uint32_t llm_cuda_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LLM_CUDA_H */

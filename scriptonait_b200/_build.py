@@ -1,0 +1,60 @@
+"""Builds libllm_cuda.so (the C-ABI library of include/llm_cuda.h) in-tree with nvcc for sm_100a.
+
+`python -m scriptonait_b200._build [--force] [--verbose]`. nvcc cross-compiles without a GPU.
+-fmad=false: the sampler's arithmetic must round exactly where the reference's f32
+code rounds (no fused multiply-add, no fast-math).
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+LIBDIR = os.path.join(HERE, "lib")
+LIBRARY = os.path.join(LIBDIR, "libllm_cuda.so")
+SOURCES = ["sampler_kernels.cu", "llm_cuda_api.cu"]
+HEADERS = ["sampler_kernels.h", "sampler_device.cuh", os.path.join("..", "..", "include", "llm_cuda.h")]
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-fmad=false", "-prec-div=true", "-prec-sqrt=true", "-ftz=false",
+    "-Xcompiler", "-fPIC", "-shared", "-cudart", "shared",
+]
+
+
+def _sources() -> list[str]:
+    return [os.path.join(CSRC, s) for s in SOURCES if os.path.exists(os.path.join(CSRC, s))]
+
+
+def is_stale() -> bool:
+    if not os.path.exists(LIBRARY):
+        return True
+    built = os.path.getmtime(LIBRARY)
+    deps = _sources() + [os.path.normpath(os.path.join(CSRC, h)) for h in HEADERS]
+    return any(os.path.getmtime(d) > built for d in deps if os.path.exists(d))
+
+
+def nvcc_path() -> str:
+    for cand in (shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.exists(cand):
+            return cand
+    raise RuntimeError("nvcc not found: libllm_cuda.so cannot be built")
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    if not (force or is_stale()):
+        return LIBRARY
+    os.makedirs(LIBDIR, exist_ok=True)
+    cmd = [nvcc_path(), *NVCC_FLAGS]
+    if verbose:
+        cmd += ["-Xptxas", "-v"]
+    cmd += _sources() + ["-o", LIBRARY]
+    subprocess.run(cmd, check=True)
+    return LIBRARY
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

@@ -1,0 +1,125 @@
+"""ctypes view of libllm_cuda.so (include/llm_cuda.h).
+
+Loading fails loudly: there is no Python or CPU stand-in for the CUDA library.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+from . import _build
+
+ABI_VERSION = 1
+
+OK = 0
+ERR_BAD_ARGUMENT = -1
+ERR_CAPACITY = -2
+ERR_CUDA = -3
+ERR_UNSUPPORTED = -4
+ERR_NO_DEVICE = -5
+
+DTYPE_F32 = 0
+DTYPE_BF16 = 1
+
+ROW_GREEDY = 1
+ROW_DEGENERATE = 2
+ROW_FALLBACK_LAST = 4
+ROW_DRAW_CONSUMED = 8
+ROW_FULL_SORT = 16
+ROW_INVALID = 64
+ROW_WINDOWED = 128
+
+EOS_DEFAULT = 258
+ROW_STATS = 6
+
+EXPORTS = [
+    "llm_cuda_abi_version", "llm_cuda_sampling_config_default", "llm_cuda_sampler_create", "llm_cuda_sampler_destroy",
+    "llm_cuda_last_error", "llm_cuda_sample_batch", "llm_cuda_sample_batch_host", "llm_cuda_sample_with",
+    "llm_cuda_sample", "llm_cuda_shard_select", "llm_cuda_merge_draw", "llm_cuda_advance_rows",
+    "llm_cuda_pack_allowed", "llm_cuda_last_launch_info",
+]
+
+
+class SamplingConfigC(C.Structure):
+    _fields_ = [
+        ("temperature", C.c_float), ("top_k", C.c_uint32), ("top_p", C.c_float), ("min_p", C.c_float),
+        ("repetition_penalty", C.c_float), ("repetition_window", C.c_uint32), ("seed", C.c_uint64),
+        ("allowed", C.c_void_p), ("allowed_len", C.c_uint32),
+    ]
+
+
+class SampleArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32), ("logits_dtype", C.c_uint32), ("logits", C.c_void_p),
+        ("batch", C.c_uint32), ("vocab", C.c_uint32), ("row_stride_elems", C.c_uint64),
+        ("temperature", C.c_float), ("top_k", C.c_uint32), ("top_p", C.c_float), ("min_p", C.c_float),
+        ("repetition_penalty", C.c_float), ("reserved0", C.c_uint32),
+        ("temperature_rows", C.c_void_p), ("top_k_rows", C.c_void_p), ("top_p_rows", C.c_void_p),
+        ("min_p_rows", C.c_void_p), ("repetition_penalty_rows", C.c_void_p),
+        ("history", C.c_void_p), ("history_stride", C.c_uint32), ("history_len", C.c_uint32),
+        ("history_len_rows", C.c_void_p),
+        ("allowed_bits", C.c_void_p), ("allowed_len", C.c_uint32), ("eos_id", C.c_uint32),
+        ("seeds", C.c_void_p), ("draw_index", C.c_void_p), ("seed_base", C.c_uint64), ("uniforms", C.c_void_p),
+        ("tokens", C.c_void_p),
+        ("row_flags", C.c_void_p), ("kept_count", C.c_void_p), ("kept_ids", C.c_void_p), ("kept_probs", C.c_void_p),
+        ("kept_capacity", C.c_uint32), ("reserved1", C.c_uint32), ("row_stats", C.c_void_p),
+        ("column_offset", C.c_uint32), ("vocab_global", C.c_uint32),
+        ("split", C.c_uint32), ("force_full_sort", C.c_uint32), ("stream", C.c_void_p),
+    ]
+
+
+_lib = None
+
+
+def library_path() -> str:
+    return _build.LIBRARY
+
+
+def load() -> C.CDLL:
+    """Builds (when stale and nvcc is present) and loads the CUDA library. Raises if it
+    cannot be produced or loaded; nothing else can stand in for it."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = _build.LIBRARY
+    if _build.is_stale():
+        try:
+            _build.build()
+        except Exception as exc:  # keep a prebuilt library if the toolchain is missing
+            if not os.path.exists(path):
+                raise RuntimeError(f"libllm_cuda.so is missing and could not be built: {exc}") from exc
+    L = C.CDLL(path)
+    vp, u32, i32 = C.c_void_p, C.c_uint32, C.c_int32
+    L.llm_cuda_abi_version.restype = u32
+    L.llm_cuda_abi_version.argtypes = []
+    L.llm_cuda_sampling_config_default.restype = None
+    L.llm_cuda_sampling_config_default.argtypes = [C.POINTER(SamplingConfigC)]
+    L.llm_cuda_sampler_create.restype = i32
+    L.llm_cuda_sampler_create.argtypes = [i32, u32, u32, u32, u32, C.POINTER(vp)]
+    L.llm_cuda_sampler_destroy.restype = i32
+    L.llm_cuda_sampler_destroy.argtypes = [vp]
+    L.llm_cuda_last_error.restype = C.c_char_p
+    L.llm_cuda_last_error.argtypes = [vp]
+    L.llm_cuda_sample_batch.restype = i32
+    L.llm_cuda_sample_batch.argtypes = [vp, C.POINTER(SampleArgs)]
+    L.llm_cuda_sample_batch_host.restype = i32
+    L.llm_cuda_sample_batch_host.argtypes = [vp, C.POINTER(SampleArgs)]
+    L.llm_cuda_sample_with.restype = i32
+    L.llm_cuda_sample_with.argtypes = [vp, vp, u32, C.POINTER(SamplingConfigC), vp, u32, C.POINTER(C.c_uint64),
+                                       C.POINTER(u32)]
+    L.llm_cuda_sample.restype = i32
+    L.llm_cuda_sample.argtypes = [vp, vp, u32, C.c_float, C.POINTER(C.c_uint64), C.POINTER(u32)]
+    L.llm_cuda_shard_select.restype = i32
+    L.llm_cuda_shard_select.argtypes = [vp, C.POINTER(SampleArgs), vp, vp, vp, u32]
+    L.llm_cuda_merge_draw.restype = i32
+    L.llm_cuda_merge_draw.argtypes = [vp, C.POINTER(SampleArgs), vp, vp, vp, u32, u32]
+    L.llm_cuda_advance_rows.restype = i32
+    L.llm_cuda_advance_rows.argtypes = [vp, u32, vp, vp, vp, u32, u32, vp, vp, vp, vp, u32, vp]
+    L.llm_cuda_pack_allowed.restype = i32
+    L.llm_cuda_pack_allowed.argtypes = [vp, vp, u32, vp, vp]
+    L.llm_cuda_last_launch_info.restype = i32
+    L.llm_cuda_last_launch_info.argtypes = [vp, C.POINTER(u32), C.POINTER(u32)]
+    if L.llm_cuda_abi_version() != ABI_VERSION:
+        raise RuntimeError("libllm_cuda.so ABI version mismatch")
+    _lib = L
+    return L

@@ -1,0 +1,498 @@
+// Device-side building blocks of the B200 token sampler (sm_100a).
+//
+// Everything here reproduces, per row, the arithmetic of the reference's
+// `sample_with` (crates/llm-core/src/generate.rs:325-420): each f32 operation
+// of the reference is one explicitly rounded operation here (__fadd_rn,
+// __fmul_rn, __fdiv_rn, ...), in the same order, so no multiply-add is fused and
+// no sum is reassociated.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/llm_cuda.h"
+#include "sampler_kernels.h"
+
+namespace llmc {
+
+constexpr int THREADS = 256;             // threads per CTA of the streaming kernel
+constexpr int WARPS = THREADS / 32;
+constexpr uint32_t TILE_ELEMS = 4096;    // logits one CTA consumes between two capacity checks
+constexpr unsigned FULL_MASK = 0xffffffffu;
+constexpr uint32_t EMPTY_KEY = 0xffffffffu;
+constexpr uint32_t MAX_KCAP = 2048;      // largest top_k handled by exact selection; above: window mode
+
+// Window mode (top_k == 0 or beyond MAX_KCAP): the reference's left-to-right
+// f32 sums over the descending ordering stop changing once exp(q - max) < 2^-25
+// (the running sum is >= 1 after the leader, so such a term is below half an
+// ulp), so only values with fl(q - max) >= WINDOW_EXACT can influence any sum,
+// cut or probability. The streaming filter uses the wider WINDOW_STREAM bound.
+constexpr float WINDOW_EXACT = -17.4f;
+constexpr float WINDOW_STREAM = 17.5f;
+
+// Internal row flag: the candidate window could not decide the row; the
+// full-sort kernel resolves it. Never visible to the caller.
+constexpr uint32_t ROW_NEEDS_FULL = 0x80000000u;
+
+
+struct RowCfg {
+    float T, top_p, min_p, pen;
+    uint32_t k_eff;     // rank cut: min(top_k, vocab), vocab when top_k == 0, 1 when greedy
+    uint32_t hlen;
+    uint32_t greedy, windowed, invalid, has_pen;
+};
+
+// ---------------------------------------------------------------------------
+// ordered keys: u32 keys whose unsigned order is the numeric order of the
+// floats, with -0.0 folded onto +0.0 (the reference compares numerically,
+// generate.rs:366, so the two zeros tie and the lower index wins).
+__device__ __forceinline__ uint32_t okey(float x) {
+    x = __fadd_rn(x, 0.0f);
+    uint32_t b = __float_as_uint(x);
+    return b ^ ((uint32_t)((int32_t)b >> 31) | 0x80000000u);
+}
+__device__ __forceinline__ float okey_to_float(uint32_t k) {
+    uint32_t b = (k & 0x80000000u) ? (k ^ 0x80000000u) : ~k;
+    return __uint_as_float(b);
+}
+// composite ordering key: larger = earlier in the reference's ordering
+// (value descending, index ascending).
+__device__ __forceinline__ uint64_t composite(float q, uint32_t idx) {
+    return ((uint64_t)okey(q) << 32) | (uint64_t)(~idx);
+}
+// true when (qa, ia) comes before (qb, ib) in the reference's ordering
+__device__ __forceinline__ bool before(float qa, uint32_t ia, float qb, uint32_t ib) {
+    return composite(qa, ia) > composite(qb, ib);
+}
+
+__device__ __forceinline__ float neg_inf() { return __uint_as_float(0xff800000u); }
+__device__ __forceinline__ float pos_inf() { return __uint_as_float(0x7f800000u); }
+
+// SplitMix64 output number n (1-based) of Rng::seed_from_u64(seed)
+// (crates/llm-core/src/rng.rs:16-22): the state after n steps is seed + n*gamma.
+__device__ __forceinline__ uint64_t splitmix_output(uint64_t seed, uint64_t n) {
+    uint64_t z = seed + n * 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+// next_f32 (rng.rs:31-34): top 24 bits over 2^24, exact in f32.
+__device__ __forceinline__ float u24_to_f32(uint64_t out) {
+    return __fmul_rn((float)(uint32_t)(out >> 40), 1.0f / 16777216.0f);
+}
+
+// exp as the reference sees it (generate.rs:373): the double-precision exp
+// rounded once to f32, i.e. the correctly rounded f32 exp except when the double
+// result lies within a double ulp of a rounding boundary.
+__device__ __forceinline__ float exp_f32(float x) { return __double2float_rn(exp((double)x)); }
+
+__device__ __forceinline__ float penalize(float x, float pen, uint32_t times) {
+    // generate.rs:343-352: once per history occurrence, each step rounded.
+    for (uint32_t i = 0; i < times; ++i) x = (x > 0.0f) ? __fdiv_rn(x, pen) : __fmul_rn(x, pen);
+    return x;
+}
+
+__device__ __forceinline__ float load_logit(const float* p) { return __ldg(p); }
+__device__ __forceinline__ float load_logit(const uint16_t* p) {
+    return __uint_as_float((uint32_t)__ldg(p) << 16);  // bf16.rs:22-25
+}
+
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void resolve_row(const KParams& P, uint32_t b, RowCfg& rc) {
+    float T = P.t_rows ? P.t_rows[b] : P.temperature;
+    uint32_t k = P.k_rows ? P.k_rows[b] : P.top_k;
+    rc.top_p = P.p_rows ? P.p_rows[b] : P.top_p;
+    rc.min_p = P.m_rows ? P.m_rows[b] : P.min_p;
+    rc.pen = P.r_rows ? P.r_rows[b] : P.penalty;
+    rc.hlen = P.history ? (P.hist_len_rows ? min(P.hist_len_rows[b], P.hist_stride) : P.hist_len) : 0u;
+    rc.invalid = (T != T) || (rc.pen != rc.pen);
+    rc.greedy = (!rc.invalid && T <= 0.0f) ? 1u : 0u;           // generate.rs:354
+    rc.T = rc.greedy ? 1.0f : T;
+    const uint32_t vg = P.vocab_global;
+    rc.k_eff = rc.greedy ? 1u : ((k == 0u || k >= vg) ? vg : k);  // generate.rs:368-370
+    rc.windowed = (!rc.greedy && rc.k_eff > P.kcap) ? 1u : 0u;
+    rc.has_pen = (rc.pen != 1.0f && rc.hlen > 0u) ? 1u : 0u;      // generate.rs:343
+}
+
+// Lower bound, in the pre-temperature domain, for "x / T >= tq": fl(tq * T)
+// lowered by four floats. A superset filter; exact selection happens on q.
+__device__ __forceinline__ uint32_t raw_threshold_key(float tq, float T) {
+    float tx = (T == 1.0f) ? tq : __fmul_rn(tq, T);
+    const uint32_t lowest = 0x007fffffu;  // okey(-inf); smaller keys would decode to NaN
+    if (tx != tx) return lowest;          // NaN (0 * inf): filter nothing
+    const uint32_t k = okey(tx);
+    return k > lowest + 4u ? k - 4u : lowest;
+}
+
+// ---------------------------------------------------------------------------
+// shared-memory hash of the history ids that fall into this CTA's columns:
+// id -> number of occurrences.
+__device__ __forceinline__ uint32_t hash_slot(uint32_t id, uint32_t mask) { return ((id * 0x9E3779B1u) >> 11) & mask; }
+
+__device__ __forceinline__ void hash_insert(uint32_t* hkeys, uint32_t* hcnt, uint32_t slots, uint32_t id) {
+    const uint32_t mask = slots - 1u;
+    uint32_t h = hash_slot(id, mask);
+    for (uint32_t probe = 0; probe < slots; ++probe) {
+        uint32_t prev = atomicCAS(&hkeys[h], EMPTY_KEY, id);
+        if (prev == EMPTY_KEY || prev == id) {
+            atomicAdd(&hcnt[h], 1u);
+            return;
+        }
+        h = (h + 1u) & mask;
+    }
+}
+__device__ __forceinline__ uint32_t hash_count(const uint32_t* hkeys, const uint32_t* hcnt, uint32_t slots, uint32_t id) {
+    const uint32_t mask = slots - 1u;
+    uint32_t h = hash_slot(id, mask);
+    for (uint32_t probe = 0; probe < slots; ++probe) {
+        uint32_t k = hkeys[h];
+        if (k == id) return hcnt[h];
+        if (k == EMPTY_KEY) return 0u;
+        h = (h + 1u) & mask;
+    }
+    return 0u;
+}
+
+// allowed(id) of generate.rs:333-341: EOS always, ids past the mask always.
+__device__ __forceinline__ bool id_blocked(const KParams& P, uint32_t gid) {
+    if (!P.allowed_bits || gid == P.eos_id || gid >= P.allowed_len) return false;
+    return ((__ldg(&P.allowed_bits[gid >> 5]) >> (gid & 31u)) & 1u) == 0u;
+}
+
+// ---------------------------------------------------------------------------
+// Block-wide state of one row's candidate buffer.
+struct Shared {
+    RowCfg rc;
+    uint32_t count;        // candidates in the buffer
+    uint32_t tau_key;      // ordered key of the streaming threshold (pre-temperature domain)
+    uint32_t max_key;      // ordered key of the largest pre-temperature value seen
+    uint32_t newcount;
+    uint32_t minkey;
+    uint32_t sel_digit, sel_need, sel_bucket;
+    uint32_t keep;
+    uint32_t error;        // internal consistency failures (buffer overrun guard)
+    uint32_t last;         // this CTA merges the row
+    uint32_t wsum[WARPS];
+    uint32_t hist[256];
+    float f_sum, f_total, f_u, f_r, f_thr;
+    uint32_t token, out_flags, kept_n, walk_end;
+};
+
+// Warp-collective append of passing lanes to the candidate buffer. `end` tracks
+// the highest slot handed out so far as seen by this warp.
+__device__ __forceinline__ void warp_append(bool pass, float q, uint32_t idx, Shared& S, float* cand_q, uint32_t* cand_i,
+                                            uint32_t ccap, uint32_t& end) {
+    const unsigned m = __ballot_sync(FULL_MASK, pass);
+    if (m == 0u) return;
+    const unsigned lane = threadIdx.x & 31u;
+    const int leader = __ffs(m) - 1;
+    uint32_t base = 0;
+    if ((int)lane == leader) base = atomicAdd(&S.count, (uint32_t)__popc(m));
+    base = __shfl_sync(FULL_MASK, base, leader);
+    if (pass) {
+        const uint32_t slot = base + (uint32_t)__popc(m & ((1u << lane) - 1u));
+        if (slot < ccap) {
+            cand_q[slot] = q;
+            cand_i[slot] = idx;
+        } else {
+            S.error = 1u;
+        }
+    }
+    end = max(end, base + (uint32_t)__popc(m));
+}
+
+// In-place compaction of cand[0..n) to the entries `keep` accepts; returns the
+// new count (order not preserved) and leaves the smallest kept ordered key in
+// S.minkey. Round r reads slots [r*THREADS, (r+1)*THREADS) and, after a
+// barrier, writes below the number kept so far, which never exceeds the slots
+// already read.
+template <class Pred>
+__device__ __forceinline__ uint32_t compact_inplace(uint32_t n, Pred keep, Shared& S, float* cand_q, uint32_t* cand_i) {
+    if (threadIdx.x == 0) {
+        S.newcount = 0u;
+        S.minkey = 0xffffffffu;
+    }
+    __syncthreads();
+    const unsigned lane = threadIdx.x & 31u;
+    for (uint32_t base = 0; base < n; base += THREADS) {
+        const uint32_t i = base + threadIdx.x;
+        bool k = false;
+        float q = 0.f;
+        uint32_t id = 0u;
+        if (i < n) {
+            q = cand_q[i];
+            id = cand_i[i];
+            k = keep(q, id);
+        }
+        __syncthreads();
+        const unsigned m = __ballot_sync(FULL_MASK, k);
+        if (m) {
+            const int leader = __ffs(m) - 1;
+            const uint32_t mk = __reduce_min_sync(FULL_MASK, k ? okey(q) : 0xffffffffu);
+            uint32_t dst = 0;
+            if ((int)lane == leader) {
+                dst = atomicAdd(&S.newcount, (uint32_t)__popc(m));
+                atomicMin(&S.minkey, mk);
+            }
+            dst = __shfl_sync(FULL_MASK, dst, leader);
+            if (k) {
+                const uint32_t slot = dst + (uint32_t)__popc(m & ((1u << lane) - 1u));
+                cand_q[slot] = q;
+                cand_i[slot] = id;
+            }
+        }
+    }
+    __syncthreads();
+    return S.newcount;
+}
+
+// Radix select over the 64-bit composite keys of cand[0..n): finds (shift, thr)
+// such that exactly k entries satisfy (composite >> shift) >= thr. Requires
+// 1 <= k < n. Eight bits per pass from the top; stops as soon as the bucket that
+// holds the k-th entry is wanted whole.
+__device__ __forceinline__ void radix_select(uint32_t n, uint32_t k, Shared& S, const float* cand_q, const uint32_t* cand_i,
+                                             uint64_t& thr, int& shift) {
+    uint64_t prefix = 0ull;
+    uint32_t need = k;
+    const unsigned lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    for (int p = 0; p < 8; ++p) {
+        const int sh = 56 - 8 * p;
+        S.hist[threadIdx.x] = 0u;  // THREADS == 256 bins
+        __syncthreads();
+        for (uint32_t i = threadIdx.x; i < n; i += THREADS) {
+            const uint64_t c = composite(cand_q[i], cand_i[i]);
+            if (p == 0 || (c >> (sh + 8)) == prefix) atomicAdd(&S.hist[(uint32_t)(c >> sh) & 255u], 1u);
+        }
+        __syncthreads();
+        const uint32_t v = S.hist[threadIdx.x];
+        uint32_t x = v;  // becomes the sum of bins lane..31 of this warp
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t y = __shfl_down_sync(FULL_MASK, x, o);
+            if (lane + o < 32u) x += y;
+        }
+        if (lane == 0) S.wsum[warp] = x;
+        __syncthreads();
+        uint32_t higher = 0u;
+        for (unsigned w = warp + 1; w < WARPS; ++w) higher += S.wsum[w];
+        const uint32_t suffix = x + higher;        // entries in bins >= threadIdx.x
+        const uint32_t above = suffix - v;         // entries in bins > threadIdx.x
+        if (suffix >= need && above < need) {
+            S.sel_digit = threadIdx.x;
+            S.sel_need = need - above;
+            S.sel_bucket = v;
+        }
+        __syncthreads();
+        prefix = (prefix << 8) | (uint64_t)S.sel_digit;
+        need = S.sel_need;
+        const uint32_t bucket = S.sel_bucket;
+        if (bucket == need || p == 7) {
+            shift = sh;
+            thr = prefix;
+            return;
+        }
+    }
+}
+
+// Keeps the best k entries of cand[0..n) (reference ordering); returns the new count.
+__device__ __forceinline__ uint32_t keep_top_k(uint32_t n, uint32_t k, Shared& S, float* cand_q, uint32_t* cand_i) {
+    if (n <= k) return n;
+    uint64_t thr;
+    int shift;
+    radix_select(n, k, S, cand_q, cand_i, thr, shift);
+    return compact_inplace(
+        n, [=](float q, uint32_t id) { return (composite(q, id) >> shift) >= thr; }, S, cand_q, cand_i);
+}
+
+// Bitonic sort of cand[0..n) into the reference ordering; slots [n, m) (m the
+// next power of two) are filled with entries that sort last.
+__device__ __forceinline__ void sort_candidates(uint32_t n, float* cand_q, uint32_t* cand_i) {
+    uint32_t m = 1u;
+    while (m < n) m <<= 1;
+    for (uint32_t i = n + threadIdx.x; i < m; i += THREADS) {
+        cand_q[i] = neg_inf();
+        cand_i[i] = 0xffffffffu;
+    }
+    __syncthreads();
+    for (uint32_t size = 2u; size <= m; size <<= 1) {
+        for (uint32_t stride = size >> 1; stride > 0u; stride >>= 1) {
+            for (uint32_t t = threadIdx.x; t < (m >> 1); t += THREADS) {
+                const uint32_t lo = ((t & ~(stride - 1u)) << 1) | (t & (stride - 1u));
+                const uint32_t hi = lo + stride;
+                const bool descending_block = ((lo & size) == 0u);  // first-in-order at the low slot
+                const float ql = cand_q[lo], qh = cand_q[hi];
+                const uint32_t il = cand_i[lo], ih = cand_i[hi];
+                const bool hi_first = before(qh, ih, ql, il);
+                if (hi_first == descending_block) {
+                    cand_q[lo] = qh;
+                    cand_i[lo] = ih;
+                    cand_q[hi] = ql;
+                    cand_i[hi] = il;
+                }
+            }
+            __syncthreads();
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// The ordered tail of sample_with (generate.rs:372-419) over the sorted
+// candidates cand[0..n). `probs` is scratch for n floats. `truncated` says that
+// the reference's ordering continues past these n entries with values outside
+// the significance window (window mode only). Thread 0 owns the sequential
+// chains; everything else is data parallel. Returns through S: token, flags,
+// kept_n and the stage statistics.
+__device__ __forceinline__ void ordered_tail(const KParams& P, uint32_t b, const RowCfg& rc, uint32_t n, bool truncated,
+                                             uint32_t k_total, Shared& S, const float* cand_q, const uint32_t* cand_i,
+                                             float* probs) {
+    const float mx = cand_q[0];  // generate.rs:372 (the ordering is NaN-free, so the fold is its first element)
+    for (uint32_t i = threadIdx.x; i < n; i += THREADS) probs[i] = exp_f32(__fsub_rn(cand_q[i], mx));  // :373
+    if (threadIdx.x == 0) {
+        S.keep = n;
+        S.out_flags = 0u;
+        S.f_thr = 0.f;
+        S.f_total = 0.f;
+        S.f_u = 0.f;
+        S.f_r = 0.f;
+        S.kept_n = 0u;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        // :374 left-to-right f32 sum. Once the sum is >= 1 a term below 2^-24 is under
+        // half an ulp and leaves it unchanged, and the terms only get smaller.
+        float s = 0.0f;
+        for (uint32_t i = 0; i < n; ++i) {
+            const float e = probs[i];
+            if (e < 5.9604644775390625e-08f && s >= 1.0f) break;
+            s = __fadd_rn(s, e);
+        }
+        S.f_sum = s;
+    }
+    __syncthreads();
+    const float sum = S.f_sum;
+    const bool degenerate = (sum <= 0.0f) || !(fabsf(sum) <= 3.402823466e38f);  // :375 (catches NaN and inf)
+    if (degenerate) {
+        if (threadIdx.x == 0) {
+            S.token = cand_i[0];
+            S.out_flags = LLM_CUDA_ROW_DEGENERATE;
+        }
+        __syncthreads();
+        return;
+    }
+    for (uint32_t i = threadIdx.x; i < n; i += THREADS) probs[i] = __fdiv_rn(probs[i], sum);  // :378-380
+    __syncthreads();
+    // :384-395 min-p: leading run with p >= min_p * p[0], never empty
+    bool unknown_tail = false;  // kept set may reach past the window in a way the window cannot settle
+    if (rc.min_p > 0.0f) {
+        const float thr = __fmul_rn(rc.min_p, probs[0]);
+        uint32_t first_fail = n;
+        for (uint32_t i = threadIdx.x; i < n; i += THREADS) {
+            if (!(probs[i] >= thr)) {
+                first_fail = i;
+                break;
+            }
+        }
+        if (first_fail < n) atomicMin(&S.keep, first_fail);
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            S.f_thr = thr;
+            if (S.keep < 1u) S.keep = 1u;
+        }
+        __syncthreads();
+        // every window entry passed and more entries follow: whether those pass is
+        // only certain when the threshold is at least 2^-24 of the leader
+        if (truncated && S.keep == n && rc.min_p < 5.9604644775390625e-08f) unknown_tail = true;
+    }
+    const uint32_t keep_minp = S.keep;
+    const bool open_tail = truncated && keep_minp == n && !(rc.min_p > 0.0f);  // kept set continues past the window
+    if (threadIdx.x == 0) {
+        uint32_t keep = keep_minp;
+        float total = 0.0f;
+        bool reached = false;
+        if (rc.top_p < 1.0f) {
+            // :397-409; the later re-summation of the kept prefix (:411) repeats the same additions
+            float cum = 0.0f;
+            for (uint32_t i = 0; i < keep_minp; ++i) {
+                cum = __fadd_rn(cum, probs[i]);
+                if (cum >= rc.top_p) {
+                    keep = i + 1u;
+                    reached = true;
+                    break;
+                }
+            }
+            total = cum;
+        } else {
+            for (uint32_t i = 0; i < keep_minp; ++i) total = __fadd_rn(total, probs[i]);
+        }
+        // entries past the window add less than half an ulp to `cum`/`total`, so both are final
+        const bool tail_kept = open_tail && !reached;
+        float u;
+        if (P.uniforms) {
+            u = P.uniforms[b];
+        } else {
+            const uint64_t seed = P.seeds ? P.seeds[b] : P.seed_base + (uint64_t)b;
+            const uint64_t done = P.draw_index ? P.draw_index[b] : 0ull;
+            u = u24_to_f32(splitmix_output(seed, done + 1ull));  // rng.rs:31-34
+        }
+        float r = __fmul_rn(u, total);  // :412
+        S.f_total = total;
+        S.f_u = u;
+        S.f_r = r;
+        uint32_t flags = LLM_CUDA_ROW_DRAW_CONSUMED;
+        uint32_t token = 0u;
+        bool found = false;
+        for (uint32_t i = 0; i < keep; ++i) {  // :413-418
+            const float p = probs[i];
+            if (r < p) {
+                token = cand_i[i];
+                found = true;
+                break;
+            }
+            r = __fsub_rn(r, p);
+        }
+        if (!found) {
+            if (tail_kept || unknown_tail) {
+                flags = ROW_NEEDS_FULL;  // the walk continues into entries the window dropped
+            } else {
+                token = cand_i[keep - 1u];  // :419
+                flags |= LLM_CUDA_ROW_FALLBACK_LAST;
+            }
+        } else if (unknown_tail) {
+            flags = ROW_NEEDS_FULL;
+        }
+        S.token = token;
+        S.out_flags = flags;
+        S.keep = keep;
+        S.kept_n = tail_kept ? k_total : keep;
+    }
+    __syncthreads();
+}
+
+// Writes the row's results. `listed` = how many kept entries cand/probs hold.
+__device__ __forceinline__ void write_row_outputs(const KParams& P, uint32_t b, uint32_t extra_flags, const Shared& S,
+                                                  float mx, const uint32_t* cand_i, const float* probs, uint32_t listed) {
+    const uint32_t flags = S.out_flags | extra_flags;
+    if (threadIdx.x == 0) {
+        P.tokens[b] = S.token;
+        if (P.row_flags) P.row_flags[b] = flags;
+        if (P.kept_count) P.kept_count[b] = S.kept_n;
+        if (P.row_stats) {
+            float* st = P.row_stats + (size_t)b * LLM_CUDA_ROW_STATS;
+            st[0] = mx;
+            st[1] = S.f_sum;
+            st[2] = S.f_total;
+            st[3] = S.f_u;
+            st[4] = S.f_thr;
+            st[5] = S.f_r;
+        }
+    }
+    if (P.kept_cap && (flags & LLM_CUDA_ROW_DRAW_CONSUMED)) {
+        const uint32_t m = min(listed, P.kept_cap);
+        for (uint32_t i = threadIdx.x; i < m; i += THREADS) {
+            if (P.kept_ids) P.kept_ids[(size_t)b * P.kept_cap + i] = cand_i[i];
+            if (P.kept_probs) P.kept_probs[(size_t)b * P.kept_cap + i] = probs[i];
+        }
+    }
+}
+
+}  // namespace llmc

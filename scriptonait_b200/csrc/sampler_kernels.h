@@ -1,0 +1,89 @@
+// Host-visible declarations of the sampler kernels: the parameter block every
+// kernel receives, the launch plan, and the launchers the C ABI calls.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace llmc {
+
+struct KParams {
+    const void* logits;
+    uint64_t row_stride;
+    uint32_t batch, vocab, dtype;
+    float temperature, top_p, min_p, penalty;
+    uint32_t top_k;
+    const float* t_rows;
+    const uint32_t* k_rows;
+    const float* p_rows;
+    const float* m_rows;
+    const float* r_rows;
+    const uint32_t* history;
+    uint32_t hist_stride, hist_len;
+    const uint32_t* hist_len_rows;
+    const uint32_t* allowed_bits;
+    uint32_t allowed_len, eos_id;
+    const uint64_t* seeds;
+    const uint64_t* draw_index;
+    uint64_t seed_base;
+    const float* uniforms;
+    uint32_t* tokens;
+    uint32_t* row_flags;
+    uint32_t* kept_count;
+    uint32_t* kept_ids;
+    float* kept_probs;
+    uint32_t kept_cap;
+    float* row_stats;
+    uint32_t col_offset, vocab_global;
+    // launch geometry
+    uint32_t split, shard_cols;
+    uint32_t kcap, ccap;            // kcap: candidates carried across compactions; ccap = 2*kcap + TILE_ELEMS
+    uint32_t hash_slots, bitmap_words;
+    // scratch shared by the CTAs of one row when split > 1 (also the input of merge_draw)
+    float* sc_q;                    // [shard][row][sc_stride]   (element (s, b, i) at (s*sc_rows + b)*sc_stride + i)
+    uint32_t* sc_i;
+    uint32_t* sc_cnt;               // [shard][row]
+    uint32_t* sc_maxkey;            // [shard][row] ordered key of the shard's maximum q
+    uint32_t* sc_ticket;            // [row]
+    uint32_t sc_stride, sc_rows;
+    // candidate lists out (vocabulary sharding step 1); NULL = draw a token
+    float* out_q;
+    uint32_t* out_i;
+    uint32_t* out_cnt;
+    uint32_t out_stride;
+    // rows handed to the full-sort kernel
+    uint32_t* full_list;
+    uint32_t* full_count;
+    uint32_t force_full;
+};
+
+struct DeviceInfo {
+    uint32_t sm_count;
+    size_t max_dyn_smem;  // opt-in dynamic shared memory per CTA
+};
+
+struct LaunchPlan {
+    uint32_t split, shard_cols, kcap, ccap, hash_slots, bitmap_words;
+    size_t smem;
+    bool bits;  // mask or penalty tables needed
+};
+
+// Raises the dynamic shared-memory limit of every kernel; once per device.
+cudaError_t configure_kernels(size_t max_dyn_smem);
+
+// Chooses candidate capacity, CTAs per row and shared-memory layout. Returns 0, or -1
+// when the layout does not fit in shared memory.
+int plan_launch(const DeviceInfo& dev, const KParams& base, bool top_k_known, uint32_t top_k_hint, uint32_t max_top_k,
+                uint32_t max_history, uint32_t requested_split, uint32_t max_lists, LaunchPlan* plan);
+
+cudaError_t launch_stream_select(const KParams& P, const LaunchPlan& plan, cudaStream_t stream);
+cudaError_t launch_merge_draw(const KParams& P, const LaunchPlan& plan, cudaStream_t stream);
+cudaError_t launch_full_sort(const KParams& P, uint32_t hash_slots, uint32_t nslots, uint64_t* keys, float* vals, uint32_t vpad,
+                             uint32_t* ticket, cudaStream_t stream);
+cudaError_t launch_advance_rows(uint32_t batch, const uint32_t* tokens, const uint32_t* row_flags, uint32_t* history,
+                                uint32_t history_stride, uint32_t window, uint32_t* history_len, uint32_t* history_pos,
+                                uint64_t* draw_index, uint8_t* finished, uint32_t eos_id, cudaStream_t stream);
+cudaError_t launch_pack_allowed(const uint8_t* allowed_dev, uint32_t n, uint32_t* bits, cudaStream_t stream);
+
+}  // namespace llmc
