@@ -77,6 +77,21 @@ class SampleResult:
     row_stats: Optional["object"] = None
 
 
+class PreparedCall:
+    """A fully marshalled llm_cuda_sample_batch call over fixed device buffers."""
+
+    def __init__(self, sampler: "Sampler", args: "N.SampleArgs", result: SampleResult):
+        self.sampler, self.args, self.result = sampler, args, result
+        self._fn = sampler._lib.llm_cuda_sample_batch
+        self._ref = C.byref(args)
+
+    def launch(self) -> SampleResult:
+        rc = self._fn(self.sampler._h, self._ref)
+        if rc != N.OK:
+            self.sampler._check(rc)
+        return self.result
+
+
 def _torch():
     import torch  # deferred: importing the package must not require a GPU
     return torch
@@ -201,10 +216,13 @@ class Sampler:
                      allowed_bits=None, allowed_len: Optional[int] = None, eos_id: int = EOS, seeds=None,
                      draw_index=None, seed_base: int = 0, uniforms=None, batch: Optional[int] = None,
                      row_stride: Optional[int] = None, trace: bool = False, kept_capacity: int = 64, split: int = 0,
-                     force_full_sort: bool = False, out_tokens=None, stream=None) -> SampleResult:
+                     force_full_sort: bool = False, out_tokens=None, stream=None, prepare_only: bool = False):
         """Row r of `logits` ([B, V] CUDA tensor, float32 / bfloat16 / uint16 bf16 bits) is one
         `sample_with` call with Rng::seed_from_u64(seeds[r]) advanced by draw_index[r] outputs.
-        Parameters are scalars or per-row arrays. Asynchronous on the current (or given) stream."""
+        Parameters are scalars or per-row arrays. Asynchronous on the current (or given) stream.
+        With `prepare_only` nothing is launched: the returned PreparedCall re-issues the same call
+        (same buffers, same stream) with one C-ABI call per `launch()`, which is what a decode
+        loop over fixed buffers wants."""
         torch = _torch()
         assert logits.is_cuda and logits.dim() == 2 and logits.stride(1) == 1, "logits: [B, V] CUDA tensor, unit column stride"
         if logits.dtype == torch.float32:
@@ -225,8 +243,11 @@ class Sampler:
                             draw_index=draw_index, seed_base=seed_base, uniforms=uniforms, split=split,
                             force_full_sort=force_full_sort, stream=st, keep=keep)
         res = self._outputs(a, B, trace, kept_capacity, out_tokens, logits.device)
-        self._check(self._lib.llm_cuda_sample_batch(self._h, C.byref(a)))
         res._keepalive = keep  # inputs must outlive the asynchronous launch
+        call = PreparedCall(self, a, res)
+        if prepare_only:
+            return call
+        call.launch()
         return res
 
     def _outputs(self, a: N.SampleArgs, B: int, trace: bool, kept_capacity: int, out_tokens, device) -> SampleResult:

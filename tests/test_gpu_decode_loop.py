@@ -1,0 +1,58 @@
+"""Device-side decode-loop glue (Generator::step / recent_tokens,
+crates/llm-core/src/generate.rs:157-182): sampling, history-window append, EOS stop and
+draw counting stay on the GPU across steps, and reproduce a host loop that calls the
+oracle's sample_with with the last `window` tokens each step."""
+import numpy as np
+import pytest
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def test_batched_decode_loop_matches_a_host_loop_of_sample_with(sampler):
+    import torch
+    g = np.random.default_rng(21)
+    B, V, steps, window = 12, 600, 40, 16
+    table = g.normal(0, 2, (steps, B, V)).astype(np.float32)  # stand-in for the LM head's output per step
+    table[:, :, 258] += 2.5  # make EOS reachable
+    prompt = g.integers(0, V, size=(B, 5), dtype=np.uint32)
+    cfg = oracle.SamplingConfig(temperature=0.9, top_k=20, top_p=0.95, min_p=0.0, repetition_penalty=1.3)
+    # host reference loop
+    expect = []
+    for r in range(B):
+        rng = oracle.Rng(1000 + r)
+        toks = list(prompt[r])
+        out = []
+        for t in range(steps):
+            nxt = oracle.sample_with(table[t, r], cfg, toks[-window:], rng, exp_mode=oracle.EXP_CR)
+            if nxt == 258:
+                out.append(None)
+                break
+            toks.append(nxt)
+            out.append(nxt)
+        expect.append(out)
+    # device loop
+    dev = "cuda:0"
+    hist = torch.zeros((B, window), dtype=torch.int32, device=dev)
+    hist[:, :5] = torch.from_numpy(prompt.view(np.int32)).to(dev)
+    hlen = torch.full((B,), 5, dtype=torch.int32, device=dev)
+    hpos = torch.full((B,), 5, dtype=torch.int32, device=dev)
+    draws = torch.zeros(B, dtype=torch.int64, device=dev)
+    finished = torch.zeros(B, dtype=torch.uint8, device=dev)
+    seeds = torch.arange(1000, 1000 + B, dtype=torch.int64, device=dev)
+    got = [[] for _ in range(B)]
+    tbl = torch.from_numpy(table).to(dev)
+    for t in range(steps):
+        res = sampler.sample_batch(tbl[t], temperature=0.9, top_k=20, top_p=0.95, repetition_penalty=1.3, history=hist,
+                                   history_len=hlen, seeds=seeds, draw_index=draws, trace=True)
+        was_finished = finished.clone()
+        sampler.advance_rows(res.tokens, res.row_flags, history=hist, window=window, history_len=hlen, history_pos=hpos,
+                             draw_index=draws, finished=finished)
+        torch.cuda.synchronize()
+        tk, wf, nf = res.tokens.cpu().numpy().view(np.uint32), was_finished.cpu().numpy(), finished.cpu().numpy()
+        for r in range(B):
+            if wf[r]:
+                continue
+            got[r].append(None if nf[r] else int(tk[r]))
+    assert got == expect
