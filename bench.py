@@ -217,6 +217,8 @@ def run_ours(args, rank, world, local_rank):
 
     first = timed_region()  # already the max over ranks, so every rank derives the same region count
     n_more = min(2000, max(4, int(1500.0 / max(first, 1e-3))))
+    if args.regions > 0:
+        n_more = args.regions - 1
     regions = [first] + [timed_region() for _ in range(n_more)]
     ms_region = statistics.median(regions)
     ms_per_step = ms_region / args.steps
@@ -304,6 +306,9 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--regions", type=int, default=0,
+                    help="timed regions of K steps to run (0 = as many as keep the GPU loaded for ~1.5 s); "
+                         "profiling runs use a small number")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

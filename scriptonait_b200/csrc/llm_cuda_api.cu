@@ -6,6 +6,7 @@
 #include <stdarg.h>
 #include <stdio.h>
 #include <string.h>
+#include <stdlib.h>
 
 #include <new>
 #include <vector>
@@ -17,7 +18,6 @@ using namespace llmc;
 
 namespace {
 
-constexpr uint32_t kTileElems = 4096;         // must match TILE_ELEMS of the kernels
 constexpr uint32_t kMaxKcap = 2048;           // must match MAX_KCAP
 constexpr uint64_t kScratchEntries = 1u << 22;  // candidate entries shared by the CTAs of split rows (32 MiB)
 constexpr uint64_t kGamma = 0x9E3779B97F4A7C15ull;
@@ -50,6 +50,8 @@ struct llm_cuda_sampler {
     uint64_t* full_keys = nullptr;
     float* full_vals = nullptr;
     uint32_t vpad = 0, nslots = 0, hash_slots = 0;
+    uint32_t* device_errors = nullptr;  // bit 0: a bulk copy timed out in some launch
+    unsigned long long* phase_ns = nullptr;  // development aid: per-CTA phase timestamps, set by llm_cuda_debug_phase_buffer
     // staging for the host-buffer entry points (grown on demand)
     unsigned char* arena = nullptr;
     size_t arena_bytes = 0;
@@ -84,6 +86,7 @@ void free_all(llm_cuda_sampler* s) {
     cudaFree(s->full_ticket);
     cudaFree(s->full_keys);
     cudaFree(s->full_vals);
+    cudaFree(s->device_errors);
     cudaFree(s->arena);
 }
 
@@ -158,6 +161,9 @@ int32_t fill_params(llm_cuda_sampler* s, const llm_cuda_sample_args* a, bool nee
     P->full_list = s->full_list;
     P->full_count = s->full_count;
     P->force_full = a->force_full_sort;
+    P->device_errors = s->device_errors;
+    P->phase_ns = s->phase_ns;
+    { const char* dm = getenv("LLM_CUDA_DEBUG_MODE"); P->debug_mode = dm ? (uint32_t)atoi(dm) : 0u; }
     return LLM_CUDA_OK;
 }
 
@@ -168,15 +174,15 @@ int32_t run_select(llm_cuda_sampler* s, const llm_cuda_sample_args* a, KParams& 
     LaunchPlan plan{};
     const bool k_known = (a->top_k_rows == nullptr);
     const uint32_t k_hint = scalar_greedy(a) ? 1u : a->top_k;
-    // lists the split scratch can hold at this launch's candidate capacity
-    uint32_t kcap_probe;
+    // lists the split scratch can hold at this launch's list length
+    uint32_t list_len;
     {
         LaunchPlan probe{};
         if (plan_launch(s->dev, P, k_known, k_hint, s->max_top_k, s->max_history, 1u, 1u, &probe) != 0)
             return fail(s, LLM_CUDA_ERR_CAPACITY, "shared-memory layout does not fit (history %u)", s->max_history);
-        kcap_probe = probe.kcap;
+        list_len = probe.limit;
     }
-    uint64_t max_lists = kScratchEntries / (2ull * kcap_probe);
+    uint64_t max_lists = kScratchEntries / list_len;
     if (max_lists > s->sc_lists) max_lists = s->sc_lists;
     if (plan_launch(s->dev, P, k_known, k_hint, s->max_top_k, s->max_history, a->split, (uint32_t)max_lists, &plan) != 0)
         return fail(s, LLM_CUDA_ERR_CAPACITY, "shared-memory layout does not fit (vocab %u, history %u)", a->vocab, s->max_history);
@@ -184,6 +190,7 @@ int32_t run_select(llm_cuda_sampler* s, const llm_cuda_sample_args* a, KParams& 
     P.shard_cols = plan.shard_cols;
     P.kcap = plan.kcap;
     P.ccap = plan.ccap;
+    P.limit = plan.limit;
     P.hash_slots = plan.hash_slots;
     P.bitmap_words = plan.bitmap_words;
     P.sc_q = s->sc_q;
@@ -191,7 +198,7 @@ int32_t run_select(llm_cuda_sampler* s, const llm_cuda_sample_args* a, KParams& 
     P.sc_cnt = s->sc_cnt;
     P.sc_maxkey = s->sc_maxkey;
     P.sc_ticket = s->sc_ticket;
-    P.sc_stride = 2u * plan.kcap;
+    P.sc_stride = plan.limit;
     P.sc_rows = P.batch;
     cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
     s->last_kernels = 0;
@@ -272,7 +279,7 @@ int32_t llm_cuda_sampler_create(int32_t device, uint32_t max_batch, uint32_t max
     s->max_history = max_history;
     s->max_top_k = max_top_k ? max_top_k : 1u;
     s->dev.sm_count = (uint32_t)prop.multiProcessorCount;
-    s->dev.max_dyn_smem = (size_t)prop.sharedMemPerBlockOptin - 2048u;  // room for the kernels' static shared memory
+    s->dev.max_dyn_smem = (size_t)prop.sharedMemPerBlockOptin - 4096u;  // room for the kernels' static shared memory
     auto bail = [&](const char* what, cudaError_t ce) {
         fail(nullptr, LLM_CUDA_ERR_CUDA, "%s: %s", what, cudaGetErrorString(ce));
         free_all(s);
@@ -305,6 +312,8 @@ int32_t llm_cuda_sampler_create(int32_t device, uint32_t max_batch, uint32_t max
     if ((e = cudaMemset(s->sc_ticket, 0, (size_t)max_batch * 4u)) != cudaSuccess) return bail("cudaMemset", e);
     if ((e = cudaMemset(s->full_count, 0, 4u)) != cudaSuccess) return bail("cudaMemset", e);
     if ((e = cudaMemset(s->full_ticket, 0, 4u)) != cudaSuccess) return bail("cudaMemset", e);
+    if ((e = cudaMalloc(&s->device_errors, 4u)) != cudaSuccess) return bail("cudaMalloc", e);
+    if ((e = cudaMemset(s->device_errors, 0, 4u)) != cudaSuccess) return bail("cudaMemset", e);
     if ((e = cudaDeviceSynchronize()) != cudaSuccess) return bail("cudaDeviceSynchronize", e);
     *out = s;
     return LLM_CUDA_OK;
@@ -323,6 +332,13 @@ int32_t llm_cuda_last_launch_info(const llm_cuda_sampler* s, uint32_t* kernels_l
     if (!s) return LLM_CUDA_ERR_BAD_ARGUMENT;
     if (kernels_launched) *kernels_launched = s->last_kernels;
     if (split_used) *split_used = s->last_split;
+    return LLM_CUDA_OK;
+}
+
+// Development aid (not part of the public header): per-CTA phase timestamps of the streaming kernel.
+int32_t llm_cuda_debug_phase_buffer(llm_cuda_sampler* s, unsigned long long* device_buffer) {
+    if (!s) return LLM_CUDA_ERR_BAD_ARGUMENT;
+    s->phase_ns = device_buffer;
     return LLM_CUDA_OK;
 }
 
@@ -376,12 +392,14 @@ int32_t llm_cuda_merge_draw(llm_cuda_sampler* s, const llm_cuda_sample_args* a, 
     const uint32_t k = scalar_greedy(a) ? 1u : a->top_k;
     const uint32_t k_eff = k >= P.vocab_global ? P.vocab_global : k;
     LaunchPlan plan{};
-    plan.kcap = pow2_ceil_u32(k_eff < 256u ? 256u : k_eff);
-    plan.ccap = 2u * plan.kcap + kTileElems;
+    plan.kcap = pow2_ceil_u32(k_eff < 64u ? 64u : k_eff);
+    plan.ccap = 2u * plan.kcap + 2048u;
+    plan.limit = 2u * plan.kcap;
     if (cand_stride > plan.ccap - plan.kcap)
         return fail(s, LLM_CUDA_ERR_CAPACITY, "cand_stride %u too large for the merge buffer (%u)", cand_stride, plan.ccap - plan.kcap);
     P.kcap = plan.kcap;
     P.ccap = plan.ccap;
+    P.limit = plan.limit;
     P.split = n_shards;
     P.sc_q = const_cast<float*>(cand_values);
     P.sc_i = const_cast<uint32_t*>(cand_ids);

@@ -17,7 +17,11 @@ namespace llmc {
 
 constexpr int THREADS = 256;             // threads per CTA of the streaming kernel
 constexpr int WARPS = THREADS / 32;
-constexpr uint32_t TILE_ELEMS = 4096;    // logits one CTA consumes between two capacity checks
+constexpr uint32_t STAGE_BYTES = 12288;  // one ring stage = one tile: the logits consumed between two capacity checks
+constexpr int RING_STAGES = 3;           // bulk copies in flight per CTA: up to RING_STAGES stages
+constexpr uint32_t WINDOW_CAP = 2048;    // candidate buffer of launches whose rows all run in window mode
+constexpr uint32_t MAX_SORT = 4096;      // most candidates the ordered tail takes (its scratch is the 32 KB ring)
+static_assert((size_t)THREADS * 8u + (size_t)MAX_SORT * 4u <= (size_t)RING_STAGES * STAGE_BYTES, "epilogue scratch");
 constexpr unsigned FULL_MASK = 0xffffffffu;
 constexpr uint32_t EMPTY_KEY = 0xffffffffu;
 constexpr uint32_t MAX_KCAP = 2048;      // largest top_k handled by exact selection; above: window mode
@@ -92,9 +96,9 @@ __device__ __forceinline__ float penalize(float x, float pen, uint32_t times) {
     return x;
 }
 
-__device__ __forceinline__ float load_logit(const float* p) { return __ldg(p); }
+__device__ __forceinline__ float load_logit(const float* p) { return *p; }
 __device__ __forceinline__ float load_logit(const uint16_t* p) {
-    return __uint_as_float((uint32_t)__ldg(p) << 16);  // bf16.rs:22-25
+    return __uint_as_float((uint32_t)(*p) << 16);  // bf16.rs:22-25
 }
 
 // ---------------------------------------------------------------------------
@@ -172,8 +176,9 @@ struct Shared {
     uint32_t keep;
     uint32_t error;        // internal consistency failures (buffer overrun guard)
     uint32_t last;         // this CTA merges the row
-    uint32_t wsum[WARPS];
-    uint32_t hist[256];
+    uint32_t wkth[WARPS];   // per-warp lower bounds for the first tile's threshold
+    uint32_t hit_cnt[WARPS];  // per-warp number of listed vectors of the current stage
+    uint32_t hist[2][256];  // radix-select histograms, alternated between passes
     float f_sum, f_total, f_u, f_r, f_thr;
     uint32_t token, out_flags, kept_n, walk_end;
 };
@@ -249,48 +254,80 @@ __device__ __forceinline__ uint32_t compact_inplace(uint32_t n, Pred keep, Share
 // Radix select over the 64-bit composite keys of cand[0..n): finds (shift, thr)
 // such that exactly k entries satisfy (composite >> shift) >= thr. Requires
 // 1 <= k < n. Eight bits per pass from the top; stops as soon as the bucket that
-// holds the k-th entry is wanted whole.
+// holds the k-th entry is wanted whole. Lanes that hit the same bin are combined
+// with match_any before the shared-memory atomic (the top bytes of float keys are
+// nearly constant, so a plain histogram would serialise on one address); the
+// 256-bin scan is done redundantly by every warp, so a pass costs two barriers.
 __device__ __forceinline__ void radix_select(uint32_t n, uint32_t k, Shared& S, const float* cand_q, const uint32_t* cand_i,
                                              uint64_t& thr, int& shift) {
     uint64_t prefix = 0ull;
     uint32_t need = k;
-    const unsigned lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const unsigned lane = threadIdx.x & 31u;
+    S.hist[0][threadIdx.x] = 0u;  // THREADS == 256 bins
+    __syncthreads();
+    const uint32_t n_up = (n + 31u) & ~31u;  // whole warps iterate together
     for (int p = 0; p < 8; ++p) {
         const int sh = 56 - 8 * p;
-        S.hist[threadIdx.x] = 0u;  // THREADS == 256 bins
-        __syncthreads();
-        for (uint32_t i = threadIdx.x; i < n; i += THREADS) {
-            const uint64_t c = composite(cand_q[i], cand_i[i]);
-            if (p == 0 || (c >> (sh + 8)) == prefix) atomicAdd(&S.hist[(uint32_t)(c >> sh) & 255u], 1u);
+        uint32_t* H = S.hist[p & 1];
+        for (uint32_t i = threadIdx.x; i < n_up; i += THREADS) {
+            bool act = false;
+            uint32_t digit = 0u;
+            if (i < n) {
+                const uint64_t c = composite(cand_q[i], cand_i[i]);
+                act = (p == 0) || ((c >> (sh + 8)) == prefix);
+                digit = (uint32_t)(c >> sh) & 255u;
+            }
+            const unsigned am = __ballot_sync(FULL_MASK, act);
+            if (act) {
+                const unsigned peers = __match_any_sync(am, digit);
+                if ((int)lane == __ffs(peers) - 1) atomicAdd(&H[digit], (uint32_t)__popc(peers));
+            }
         }
+        S.hist[(p + 1) & 1][threadIdx.x] = 0u;  // last read two barriers ago
         __syncthreads();
-        const uint32_t v = S.hist[threadIdx.x];
-        uint32_t x = v;  // becomes the sum of bins lane..31 of this warp
+        // every warp scans the 256 bins: lane l owns bins [8l, 8l+8)
+        uint32_t bins[8];
+        uint32_t mine = 0u;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            bins[j] = H[lane * 8u + j];
+            mine += bins[j];
+        }
+        uint32_t x = mine;  // becomes the number of entries in bins of lanes >= lane
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
             const uint32_t y = __shfl_down_sync(FULL_MASK, x, o);
             if (lane + o < 32u) x += y;
         }
-        if (lane == 0) S.wsum[warp] = x;
-        __syncthreads();
-        uint32_t higher = 0u;
-        for (unsigned w = warp + 1; w < WARPS; ++w) higher += S.wsum[w];
-        const uint32_t suffix = x + higher;        // entries in bins >= threadIdx.x
-        const uint32_t above = suffix - v;         // entries in bins > threadIdx.x
-        if (suffix >= need && above < need) {
-            S.sel_digit = threadIdx.x;
-            S.sel_need = need - above;
-            S.sel_bucket = v;
+        const uint32_t above_lane = x - mine;
+        const bool owner = (above_lane < need) && (need <= x);
+        uint32_t digit = 0u, newneed = 0u, bucket = 0u;
+        if (owner) {
+            uint32_t above = above_lane;
+#pragma unroll
+            for (int j = 7; j >= 0; --j) {
+                if (above < need && need <= above + bins[j]) {
+                    digit = lane * 8u + j;
+                    newneed = need - above;
+                    bucket = bins[j];
+                }
+                above += bins[j];
+            }
         }
-        __syncthreads();
-        prefix = (prefix << 8) | (uint64_t)S.sel_digit;
-        need = S.sel_need;
-        const uint32_t bucket = S.sel_bucket;
-        if (bucket == need || p == 7) {
+        const unsigned om = __ballot_sync(FULL_MASK, owner);
+        const int src = om ? __ffs(om) - 1 : 0;
+        digit = __shfl_sync(FULL_MASK, digit, src);
+        newneed = __shfl_sync(FULL_MASK, newneed, src);
+        bucket = __shfl_sync(FULL_MASK, bucket, src);
+        prefix = (prefix << 8) | (uint64_t)digit;
+        need = newneed;
+        if (bucket == need || p == 7 || om == 0u) {
             shift = sh;
             thr = prefix;
+            __syncthreads();  // histograms are free again
             return;
         }
+        __syncthreads();
     }
 }
 
@@ -304,9 +341,31 @@ __device__ __forceinline__ uint32_t keep_top_k(uint32_t n, uint32_t k, Shared& S
         n, [=](float q, uint32_t id) { return (composite(q, id) >> shift) >= thr; }, S, cand_q, cand_i);
 }
 
-// Bitonic sort of cand[0..n) into the reference ordering; slots [n, m) (m the
-// next power of two) are filled with entries that sort last.
-__device__ __forceinline__ void sort_candidates(uint32_t n, float* cand_q, uint32_t* cand_i) {
+// Sorts cand[0..n) into the reference ordering. Up to THREADS entries: every
+// thread ranks its entry against all others (composite keys staged in `keys64`,
+// which must hold n 64-bit words) and scatters - two barriers. Larger sets: bitonic
+// sort; slots [n, m) (m the next power of two) are filled with entries that sort last.
+__device__ __forceinline__ void sort_candidates(uint32_t n, float* cand_q, uint32_t* cand_i, uint64_t* keys64) {
+    if (n <= (uint32_t)THREADS) {
+        float q = 0.f;
+        uint32_t id = 0u;
+        uint64_t mine = 0ull;
+        if (threadIdx.x < n) {
+            q = cand_q[threadIdx.x];
+            id = cand_i[threadIdx.x];
+            mine = composite(q, id);
+            keys64[threadIdx.x] = mine;
+        }
+        __syncthreads();
+        if (threadIdx.x < n) {
+            uint32_t rank = 0u;
+            for (uint32_t j = 0; j < n; ++j) rank += (keys64[j] > mine) ? 1u : 0u;  // keys are distinct
+            cand_q[rank] = q;
+            cand_i[rank] = id;
+        }
+        __syncthreads();
+        return;
+    }
     uint32_t m = 1u;
     while (m < n) m <<= 1;
     for (uint32_t i = n + threadIdx.x; i < m; i += THREADS) {
@@ -361,10 +420,13 @@ __device__ __forceinline__ void ordered_tail(const KParams& P, uint32_t b, const
         // :374 left-to-right f32 sum. Once the sum is >= 1 a term below 2^-24 is under
         // half an ulp and leaves it unchanged, and the terms only get smaller.
         float s = 0.0f;
-        for (uint32_t i = 0; i < n; ++i) {
-            const float e = probs[i];
-            if (e < 5.9604644775390625e-08f && s >= 1.0f) break;
-            s = __fadd_rn(s, e);
+        for (uint32_t i0 = 0; i0 < n; i0 += 8u) {
+            float e[8];  // the loads of a batch do not depend on the running sum
+#pragma unroll
+            for (int j = 0; j < 8; ++j) e[j] = (i0 + j < n) ? probs[i0 + j] : 0.0f;
+            if (e[0] < 5.9604644775390625e-08f && s >= 1.0f) break;  // this and every later term is a no-op
+#pragma unroll
+            for (int j = 0; j < 8; ++j) s = __fadd_rn(s, e[j]);       // adding 0.0f past the end changes nothing
         }
         S.f_sum = s;
     }
@@ -410,19 +472,37 @@ __device__ __forceinline__ void ordered_tail(const KParams& P, uint32_t b, const
         float total = 0.0f;
         bool reached = false;
         if (rc.top_p < 1.0f) {
-            // :397-409; the later re-summation of the kept prefix (:411) repeats the same additions
+            // :397-409; the later re-summation of the kept prefix (:411) repeats the same additions.
+            // Batches of 8: the additions stay strictly sequential, only the loads and the
+            // comparisons are taken off the dependent chain.
             float cum = 0.0f;
-            for (uint32_t i = 0; i < keep_minp; ++i) {
-                cum = __fadd_rn(cum, probs[i]);
-                if (cum >= rc.top_p) {
-                    keep = i + 1u;
-                    reached = true;
-                    break;
+            for (uint32_t i0 = 0; i0 < keep_minp && !reached; i0 += 8u) {
+                float p[8], c[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) p[j] = (i0 + j < keep_minp) ? probs[i0 + j] : 0.0f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    cum = __fadd_rn(cum, p[j]);
+                    c[j] = cum;
                 }
+#pragma unroll
+                for (int j = 7; j >= 0; --j) {
+                    if (i0 + j < keep_minp && c[j] >= rc.top_p) {
+                        keep = i0 + j + 1u;  // ends as the first index that reaches top_p
+                        total = c[j];
+                        reached = true;
+                    }
+                }
+                if (!reached) total = cum;
             }
-            total = cum;
         } else {
-            for (uint32_t i = 0; i < keep_minp; ++i) total = __fadd_rn(total, probs[i]);
+            for (uint32_t i0 = 0; i0 < keep_minp; i0 += 8u) {
+                float p[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) p[j] = (i0 + j < keep_minp) ? probs[i0 + j] : 0.0f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) total = __fadd_rn(total, p[j]);
+            }
         }
         // entries past the window add less than half an ulp to `cum`/`total`, so both are final
         const bool tail_kept = open_tail && !reached;
@@ -441,14 +521,22 @@ __device__ __forceinline__ void ordered_tail(const KParams& P, uint32_t b, const
         uint32_t flags = LLM_CUDA_ROW_DRAW_CONSUMED;
         uint32_t token = 0u;
         bool found = false;
-        for (uint32_t i = 0; i < keep; ++i) {  // :413-418
-            const float p = probs[i];
-            if (r < p) {
-                token = cand_i[i];
-                found = true;
-                break;
+        for (uint32_t i0 = 0; i0 < keep && !found; i0 += 8u) {  // :413-418, in batches of 8
+            float p[8], rr[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) p[j] = (i0 + j < keep) ? probs[i0 + j] : 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                rr[j] = r;                 // r before entry i0+j is examined
+                r = __fsub_rn(r, p[j]);    // subtracting 0.0f past the end changes nothing
             }
-            r = __fsub_rn(r, p);
+#pragma unroll
+            for (int j = 7; j >= 0; --j) {
+                if (i0 + j < keep && rr[j] < p[j]) {  // ends as the first entry with r < p
+                    token = cand_i[i0 + j];
+                    found = true;
+                }
+            }
         }
         if (!found) {
             if (tail_kept || unknown_tail) {

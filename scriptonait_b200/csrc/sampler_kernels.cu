@@ -20,6 +20,8 @@
 
 #include <stdio.h>
 
+#include <cuda_bf16.h>
+
 #include "sampler_device.cuh"
 
 namespace llmc {
@@ -28,14 +30,12 @@ template <typename ElemT>
 struct Traits;
 template <>
 struct Traits<float> {
-    static constexpr int VEC = 4;  // elements per 16-byte load
-    static constexpr int U = 4;    // 16-byte loads per thread per tile
+    static constexpr int VEC = 4;  // elements per 16-byte vector
     static constexpr uint32_t NAN4 = 0x7fc00000u;
 };
 template <>
 struct Traits<uint16_t> {
     static constexpr int VEC = 8;
-    static constexpr int U = 2;
     static constexpr uint32_t NAN4 = 0x7fc07fc0u;
 };
 
@@ -61,45 +61,124 @@ __device__ __forceinline__ void unpack<uint16_t>(const uint4& v, float (&x)[8]) 
     x[7] = __uint_as_float(v.w & 0xffff0000u);
 }
 
+// Maximum of the elements of one 16-byte vector, NaN elements ignored.
+template <typename ElemT>
+__device__ __forceinline__ float vector_max(const uint4& v);
+template <>
+__device__ __forceinline__ float vector_max<float>(const uint4& v) {
+    return fmaxf(fmaxf(__uint_as_float(v.x), __uint_as_float(v.y)), fmaxf(__uint_as_float(v.z), __uint_as_float(v.w)));
+}
+template <>
+__device__ __forceinline__ float vector_max<uint16_t>(const uint4& v) {
+    // packed bf16 maxima: three 2-wide maxima, one across the halves, then the exact widening shift
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&v.x);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&v.y);
+    const __nv_bfloat162 c = *reinterpret_cast<const __nv_bfloat162*>(&v.z);
+    const __nv_bfloat162 d = *reinterpret_cast<const __nv_bfloat162*>(&v.w);
+    const __nv_bfloat162 m2 = __hmax2(__hmax2(a, b), __hmax2(c, d));
+    const __nv_bfloat16 m = __hmax(__low2bfloat16(m2), __high2bfloat16(m2));
+    return __uint_as_float((uint32_t)__bfloat16_as_ushort(m) << 16);
+}
+
 __device__ __forceinline__ uint32_t vol_load(const uint32_t* p) { return *(const volatile uint32_t*)p; }
+
+// ---- bulk-copy (TMA) ring: global -> shared, completion on an mbarrier -------------
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t arrivals) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(arrivals) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+// One elected thread: `bytes` (multiple of 16) from 16-byte aligned global memory to
+// 16-byte aligned shared memory of this CTA.
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_addr(smem_dst)),
+                 "l"(gmem_src), "r"(bytes), "r"(smem_addr(bar))
+                 : "memory");
+}
+// One poll with a suspend-time hint: the thread sleeps in hardware until the phase completes or
+// the hint (nanoseconds) runs out, so waiting warps do not flood the shared-memory pipeline with
+// polls that every other warp's loads, stores and atomics would queue behind.
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_addr(bar)), "r"(parity), "r"(20000u)
+        : "memory");
+    return ok != 0u;
+}
+// Bounded wait: gives up after WAIT_LIMIT polls (each poll blocks for up to 20 us, about a
+// second in all), records it, and lets the CTA run to its end.
+constexpr uint32_t WAIT_LIMIT = 1u << 16;
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(64);
+    }
+    return false;
+}
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define PHASE(slot)                                                                                              \
+    do {                                                                                                         \
+        if (P.phase_ns && threadIdx.x == 0)                                                                      \
+            P.phase_ns[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 8u + (slot)] = global_ns();              \
+    } while (0)
 
 __device__ __forceinline__ void push_full(const KParams& P, uint32_t b) {
     const uint32_t pos = atomicAdd(P.full_count, 1u);
     P.full_list[pos] = b;
 }
 
-// Streaming threshold (pre-temperature ordered key) of window mode for a given maximum.
+// Streaming threshold of window mode for a given maximum (both in the post-temperature domain).
 __device__ __forceinline__ float window_stream_bound(float qmax) {
     return __fsub_rn(__fsub_rn(qmax, WINDOW_STREAM), __fmul_rn(fabsf(qmax), 2.384185791015625e-07f));
 }
+#ifdef LLMC_EXPERIMENT_NO_DIV
+__device__ __forceinline__ float temper(float x, float T) { return x; }
+#else
 __device__ __forceinline__ float temper(float x, float T) { return (T == 1.0f) ? x : __fdiv_rn(x, T); }  // generate.rs:357-359
-
-// Mask and penalty for one element whose bitmap bit is set (generate.rs:333-352).
-__device__ __forceinline__ float edit_value(const KParams& P, const RowCfg& rc, float x, uint32_t gid, const uint32_t* hkeys,
-                                            const uint32_t* hcnt) {
-    if (id_blocked(P, gid)) x = neg_inf();
-    if (rc.has_pen) x = penalize(x, rc.pen, hash_count(hkeys, hcnt, P.hash_slots, gid));
-    return x;
-}
+#endif
 
 // After all candidates of a row are in cand[0..n): final selection, ordering
-// and either the ordered tail (token out) or the candidate list out.
+// and either the ordered tail (token out) or the candidate list out. `scratch`
+// is EPILOGUE_SCRATCH bytes of shared memory nothing else uses any more.
 __device__ void finish_row(const KParams& P, uint32_t b, const RowCfg& rc, uint32_t n, bool overflow, float qmax, Shared& S,
-                           float* cand_q, uint32_t* cand_i) {
-    const uint32_t limit = 2u * P.kcap;
+                           float* cand_q, uint32_t* cand_i, unsigned char* scratch) {
+    uint64_t* keys64 = reinterpret_cast<uint64_t*>(scratch);                     // THREADS 64-bit words
+    float* probs = reinterpret_cast<float*>(scratch + (size_t)THREADS * 8u);     // up to MAX_SORT floats
     if (!rc.windowed) {
         n = keep_top_k(n, rc.k_eff, S, cand_q, cand_i);
     } else if (!overflow) {
         // exact window: exactly the terms the reference's f32 sums can see
         n = compact_inplace(
             n, [=](float q, uint32_t) { return (__fsub_rn(q, qmax) >= WINDOW_EXACT) || (q == qmax); }, S, cand_q, cand_i);
-        if (n > limit) overflow = true;
+        uint32_t m = 1u;  // the sort pads to a power of two inside the buffer
+        while (m < n) m <<= 1;
+        if (m > P.ccap || n > MAX_SORT) overflow = true;
+    }
+    // ids blocked by the allowed mask are skipped by the stream. They only matter when the ordering
+    // runs out of other values (fewer unmasked values than the rank cut, or nothing finite at all):
+    // then the -inf entries belong to the kept set, and the full-sort kernel produces them.
+    if (P.allowed_bits && !P.out_q && !overflow) {
+        if (!rc.windowed && n < rc.k_eff) overflow = true;
+        if (rc.windowed && qmax == neg_inf()) overflow = true;
     }
     if (overflow) {
         if (threadIdx.x == 0) push_full(P, b);
         return;
     }
-    sort_candidates(n, cand_q, cand_i);
+    PHASE(3);
+    sort_candidates(n, cand_q, cand_i, keys64);
+    PHASE(4);
     const uint32_t n_use = min(n, rc.k_eff);
     const bool truncated = rc.windowed && (n_use < rc.k_eff);
     if (P.out_q) {  // vocabulary sharding, step 1: the ordered list is the result
@@ -110,7 +189,6 @@ __device__ void finish_row(const KParams& P, uint32_t b, const RowCfg& rc, uint3
         if (threadIdx.x == 0) P.out_cnt[b] = min(n_use, P.out_stride);
         return;
     }
-    float* probs = cand_q + limit;
     if (rc.greedy || n_use == 0u) {
         if (threadIdx.x == 0) {
             S.token = n_use ? cand_i[0] : 0u;  // ops/loss.rs:6-16: first index of the maximum; 0 when nothing compares greater than -inf
@@ -124,11 +202,13 @@ __device__ void finish_row(const KParams& P, uint32_t b, const RowCfg& rc, uint3
         return;
     }
     ordered_tail(P, b, rc, n_use, truncated, rc.k_eff, S, cand_q, cand_i, probs);
+    PHASE(5);
     if (S.out_flags & ROW_NEEDS_FULL) {
         if (threadIdx.x == 0) push_full(P, b);
         return;
     }
     write_row_outputs(P, b, rc.windowed ? LLM_CUDA_ROW_WINDOWED : 0u, S, cand_q[0], cand_i, probs, S.keep);
+    PHASE(6);
 }
 
 // Pulls the candidate lists of `nsh` shards of row b into cand[] (compacting
@@ -136,7 +216,6 @@ __device__ void finish_row(const KParams& P, uint32_t b, const RowCfg& rc, uint3
 // `qmax` as finish_row expects them.
 __device__ uint32_t merge_lists(const KParams& P, uint32_t b, const RowCfg& rc, uint32_t nsh, Shared& S, float* cand_q,
                                 uint32_t* cand_i, bool& overflow, float& qmax) {
-    const uint32_t limit = 2u * P.kcap;
     if (threadIdx.x == 0) {
         S.count = 0u;
         S.max_key = 0x007fffffu;
@@ -162,7 +241,6 @@ __device__ uint32_t merge_lists(const KParams& P, uint32_t b, const RowCfg& rc, 
             } else {
                 n = compact_inplace(
                     n, [=](float q, uint32_t) { return q >= tq; }, S, cand_q, cand_i);
-                if (n > limit) overflow = true;
             }
             if (n + cnt > P.ccap) overflow = true;
         }
@@ -170,7 +248,8 @@ __device__ uint32_t merge_lists(const KParams& P, uint32_t b, const RowCfg& rc, 
         const float* sq = P.sc_q + at * P.sc_stride;
         const uint32_t* si = P.sc_i + at * P.sc_stride;
         for (uint32_t i = threadIdx.x; i < cnt; i += THREADS) {
-            cand_q[n + i] = __ldcg(&sq[i]);
+            const float q = __ldcg(&sq[i]);
+            cand_q[n + i] = q;
             cand_i[n + i] = __ldcg(&si[i]);
         }
         __syncthreads();
@@ -180,14 +259,23 @@ __device__ uint32_t merge_lists(const KParams& P, uint32_t b, const RowCfg& rc, 
     return S.count;
 }
 
+// ---------------------------------------------------------------------------
+// The hot kernel. Grid (split, batch); one CTA streams the columns
+// [shard*shard_cols, ...) of one row through a ring of RING_STAGES shared-memory
+// stages filled by bulk copies, so RING_STAGES-1 stages (8 KB each) are always in
+// flight per CTA whatever the occupancy.
 template <typename ElemT, bool BITS>
 __global__ void __launch_bounds__(THREADS) stream_select_kernel(const __grid_constant__ KParams P) {
     constexpr int VEC = Traits<ElemT>::VEC;
-    constexpr int U = Traits<ElemT>::U;
-    static_assert(THREADS * U * VEC == (int)TILE_ELEMS, "tile geometry");
-    extern __shared__ __align__(16) unsigned char dyn[];
+    constexpr uint32_t VPS = STAGE_BYTES / 16u;      // 16-byte vectors per stage
+    constexpr int U = VPS / THREADS;                 // vectors per thread per stage
+    static_assert(VPS % THREADS == 0, "stage geometry");
+    extern __shared__ __align__(128) unsigned char dyn[];
     __shared__ Shared S;
-    float* cand_q = reinterpret_cast<float*>(dyn);
+    __shared__ __align__(8) uint64_t full_bar[RING_STAGES];
+    __shared__ uint16_t hit_list[WARPS][U * 32];  // per warp: stage-relative vector numbers that hold a passing value
+    unsigned char* ring = dyn;
+    float* cand_q = reinterpret_cast<float*>(dyn + RING_STAGES * STAGE_BYTES);
     uint32_t* cand_i = reinterpret_cast<uint32_t*>(cand_q + P.ccap);
     uint32_t* bitmap = cand_i + P.ccap;
     uint32_t* hkeys = bitmap + P.bitmap_words;
@@ -203,9 +291,13 @@ __global__ void __launch_bounds__(THREADS) stream_select_kernel(const __grid_con
         S.max_key = LOWEST;
         S.error = 0u;
         S.last = 0u;
+#pragma unroll
+        for (int i = 0; i < RING_STAGES; ++i) mbar_init(&full_bar[i], 1u);
+        mbar_fence_init();
     }
     __syncthreads();
     const RowCfg rc = S.rc;
+    PHASE(0);
     if (rc.invalid) {
         if (shard == 0 && tid == 0) {
             if (P.out_q) {
@@ -235,9 +327,24 @@ __global__ void __launch_bounds__(THREADS) stream_select_kernel(const __grid_con
     const uint32_t tail0 = head + nvi * VEC;                          // first trailing element (relative to c0)
     const uint32_t ntail = ncols - tail0;
     const uint32_t gid0 = P.col_offset + c0;                          // global id of column c0
-    const uint4* vbase = reinterpret_cast<const uint4*>(row + c0 + head);
+    const unsigned char* vbase = reinterpret_cast<const unsigned char*>(row + c0 + head);  // 16-byte aligned
     const float T = rc.T;
-    const uint32_t limit = 2u * P.kcap;  // compaction trigger; ccap - limit = TILE_ELEMS of headroom
+    const uint32_t ntiles = (nvi + VPS - 1u) / VPS;
+
+    // ---- start the ring before anything else: the copies run while the side tables are built
+    const uint32_t vtiles = rc.windowed ? 2u * ntiles : ntiles;  // window-mode rows are swept twice
+    auto issue = [&](uint32_t tt) {  // thread 0 only; tt counts stages over both sweeps
+        const uint32_t t = tt >= ntiles ? tt - ntiles : tt;
+        const uint32_t first = t * VPS;
+        const uint32_t nv = min(VPS, nvi - first);
+        uint64_t* bar = &full_bar[tt % RING_STAGES];
+        mbar_expect_tx(bar, nv * 16u);
+        bulk_load(ring + (size_t)(tt % RING_STAGES) * STAGE_BYTES, vbase + (size_t)first * 16u, nv * 16u, bar);
+    };
+    if (tid == 0) {
+        const uint32_t pre = min(vtiles, (uint32_t)RING_STAGES);
+        for (uint32_t tt = 0; tt < pre; ++tt) issue(tt);
+    }
 
     // ---- mask / penalty side tables
     if (BITS) {
@@ -267,24 +374,45 @@ __global__ void __launch_bounds__(THREADS) stream_select_kernel(const __grid_con
                 const uint32_t r0 = (uint32_t)(g0 & 31ll);
                 const uint32_t lo = (q0 >= 0 && q0 < (long long)nwords_mask) ? __ldg(&P.allowed_bits[q0]) : 0xffffffffu;
                 const uint32_t hi = (q0 + 1 >= 0 && q0 + 1 < (long long)nwords_mask) ? __ldg(&P.allowed_bits[q0 + 1]) : 0xffffffffu;
-                uint32_t allowed = __funnelshift_r(lo, hi, r0);
-                uint32_t blocked = ~allowed;
-                uint32_t valid = 0u;  // bits that are real columns, inside the mask, and not EOS
-                for (uint32_t jb = 0; jb < 32u; ++jb) {
-                    const long long g = g0 + (long long)jb;
-                    const uint32_t j2 = w * 32u + jb;
-                    if (j2 >= lead && j2 < lead + ncols && g >= 0 && g < (long long)P.allowed_len && (uint32_t)g != P.eos_id)
-                        valid |= 1u << jb;
+                uint32_t blocked = ~__funnelshift_r(lo, hi, r0);
+                if (blocked) {
+                    uint32_t valid = 0u;  // bits that are real columns, inside the mask, and not EOS
+                    for (uint32_t jb = 0; jb < 32u; ++jb) {
+                        const long long g = g0 + (long long)jb;
+                        const uint32_t j2 = w * 32u + jb;
+                        if (j2 >= lead && j2 < lead + ncols && g >= 0 && g < (long long)P.allowed_len && (uint32_t)g != P.eos_id)
+                            valid |= 1u << jb;
+                    }
+                    blocked &= valid;
+                    if (blocked) atomicOr(&bitmap[w], blocked);
                 }
-                blocked &= valid;
-                if (blocked) atomicOr(&bitmap[w], blocked);
             }
         }
         __syncthreads();
     }
 
     uint32_t end = 0u;  // highest candidate slot handed out, as seen by this warp
-    float tmax = neg_inf();
+    float tmax = neg_inf();  // largest value of the edited row this thread has seen
+    PHASE(1);
+
+    // ---- ids with a penalty: the stream never edits values. Every distinct history id of this
+    //      CTA's columns is read once here, masked, penalised and appended as a candidate; the
+    //      stream then skips all flagged ids (penalised or blocked by the mask).
+    if (BITS) {
+        for (uint32_t base = 0; base < P.hash_slots; base += THREADS) {
+            const uint32_t slot = base + tid;
+            const uint32_t id = slot < P.hash_slots ? hkeys[slot] : EMPTY_KEY;
+            const bool have = id != EMPTY_KEY;
+            float x = __uint_as_float(0x7fc00000u);
+            if (have) {
+                x = load_logit(row + (id - P.col_offset));
+                if (id_blocked(P, id)) x = neg_inf();
+                x = penalize(x, rc.pen, hcnt[slot]);
+                tmax = fmaxf(tmax, x);
+            }
+            warp_append(have && x >= neg_inf(), temper(x, T), id, S, cand_q, cand_i, P.ccap, end);
+        }
+    }
 
     // ---- leading / trailing elements that are not part of a whole aligned vector (warp 0)
     if (warp == 0) {
@@ -302,70 +430,154 @@ __global__ void __launch_bounds__(THREADS) stream_select_kernel(const __grid_con
             x = load_logit(row + c0 + rel);
             if (BITS) {
                 const uint32_t j2 = rel + lead;
-                if ((bitmap[j2 >> 5] >> (j2 & 31u)) & 1u) x = edit_value(P, rc, x, gid0 + rel, hkeys, hcnt);
+                if ((bitmap[j2 >> 5] >> (j2 & 31u)) & 1u) x = __uint_as_float(0x7fc00000u);  // handled above / blocked
             }
             tmax = fmaxf(tmax, x);
         }
         warp_append(valid && x >= neg_inf(), temper(x, T), gid0 + rel, S, cand_q, cand_i, P.ccap, end);
     }
 
-    // ---- the stream: tile t = vectors [t*THREADS*U, (t+1)*THREADS*U), prefetched one tile ahead
-    const uint32_t ntiles = (nvi + THREADS * U - 1) / (THREADS * U);
-    uint4 cur[U], nxt[U];
-    auto load_tile = [&](uint4(&dst)[U], uint32_t t) {
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const uint32_t v = (t * U + u) * THREADS + tid;
-            if (v < nvi) {
-                dst[u] = __ldcs(vbase + v);
-            } else {
-                dst[u] = make_uint4(Traits<ElemT>::NAN4, Traits<ElemT>::NAN4, Traits<ElemT>::NAN4, Traits<ElemT>::NAN4);
-            }
-        }
-    };
-    if (ntiles) load_tile(cur, 0);
-    uint32_t seen_max_key = LOWEST;
-    for (uint32_t t = 0; t <= ntiles; ++t) {
-        // iteration t == ntiles only publishes the maximum and settles the buffer
-        if (t < ntiles) {
-            if (t + 1 < ntiles) load_tile(nxt, t + 1);
-            const float tau = okey_to_float(vol_load(&S.tau_key));
+    // ---- the stream. Rows in window mode are streamed twice: a first sweep only finds the row's
+    //      maximum (the threshold max - 17.5 is then exact from the first candidate on, wherever in
+    //      the row the maximum sits), the second sweep - served from L2, which the first sweep has
+    //      just filled - collects. Other rows are streamed once.
+    //      Per stage of a collecting sweep: (A) every lane takes the maximum of each of its 16-byte
+    //      vectors (packed bf16 arithmetic for bf16 rows) and notes the vectors that reach the
+    //      threshold in its warp's list; (B) after a barrier all threads share out the listed vectors
+    //      element by element, so examining and appending candidates is parallel and free of divergence.
+    bool wait_failed = false;
+    for (uint32_t tt = 0; tt <= vtiles; ++tt) {
+        // iteration tt == vtiles only settles the buffer
+        const bool max_sweep = rc.windowed && tt < ntiles;  // first sweep of a window-mode row
+        const uint32_t t = (rc.windowed && tt >= ntiles) ? tt - ntiles : tt;  // tile within the row
+        if (tt < vtiles) {
+            const uint32_t stage = tt % RING_STAGES;
+            if (!mbar_wait_bounded(&full_bar[stage], (tt / RING_STAGES) & 1u)) wait_failed = true;
+            const uint4* sv = reinterpret_cast<const uint4*>(ring + (size_t)stage * STAGE_BYTES);
+            float vm[U];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
-                const uint32_t v = (t * U + u) * THREADS + tid;
-                float x[VEC];
-                unpack<ElemT>(cur[u], x);
-                const uint32_t rel0 = head + v * VEC;  // column (relative to c0) of x[0]
-                if (BITS) {
-                    if (v < nvi) {
-                        const uint32_t j2 = rel0 + lead;  // multiple of VEC: the VEC bits sit in one word
-                        uint32_t nib = (bitmap[j2 >> 5] >> (j2 & 31u)) & ((1u << VEC) - 1u);
+                const uint32_t j = u * THREADS + tid;
+                const uint32_t v = t * VPS + j;
+                float m = __uint_as_float(0x7fc00000u);  // NaN: an absent vector never passes and never raises a maximum
+                if (v < nvi && !wait_failed) m = vector_max<ElemT>(sv[j]);
+                vm[u] = m;  // of the raw values; NaN elements are ignored by the maxima
+                if (!BITS) tmax = fmaxf(tmax, m);
+            }
+            if (BITS && (max_sweep || (tt == 0 && !rc.windowed))) {
+                // a maximum of the edited row is wanted: flagged ids (penalised, blocked) must not count
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const uint32_t j = u * THREADS + tid;
+                    const uint32_t v = t * VPS + j;
+                    if (v < nvi && !wait_failed) {
+                        const uint32_t j2 = head + v * VEC + lead;
+                        const uint32_t nib = (bitmap[j2 >> 5] >> (j2 & 31u)) & ((1u << VEC) - 1u);
+                        float m = vm[u];
                         if (nib) {
+                            float x[VEC];
+                            unpack<ElemT>(sv[j], x);
+                            m = neg_inf();
 #pragma unroll
                             for (int e = 0; e < VEC; ++e)
-                                if ((nib >> e) & 1u) x[e] = edit_value(P, rc, x[e], gid0 + rel0 + e, hkeys, hcnt);
+                                if (!((nib >> e) & 1u)) m = fmaxf(m, x[e]);
                         }
+                        tmax = fmaxf(tmax, m);
                     }
                 }
-                float vm = x[0];
+            }
+            if (max_sweep) {
+                if (tt + 1u == ntiles) {  // end of the first sweep: the row's maximum fixes the threshold
+                    const uint32_t wk = __reduce_max_sync(FULL_MASK, okey(tmax));
+                    if (lane == 0) atomicMax(&S.max_key, wk);
+                    __syncthreads();
+                    if (tid == 0) {
+                        const float qmax = temper(okey_to_float(S.max_key), T);
+                        S.tau_key = raw_threshold_key(window_stream_bound(qmax), T);
+                    }
+                }
+            } else {
+                if (tt == 0) {
+                    // (top-k rows) bootstrap the threshold from the first stage, before anything of it is appended
+                    if (rc.k_eff <= (uint32_t)THREADS) {
+                        // each lane's maximum is an element of the edited row, so the r-th largest lane maximum
+                        // of a warp has >= r elements at or above it; the minimum over the warps of those
+                        // bounds has >= WARPS*r >= k elements at or above it: a valid lower bound for the
+                        // k-th largest value of the whole row
+                        const uint32_t r = (rc.k_eff + WARPS - 1u) / WARPS;
+                        const uint32_t mykey = okey(tmax);
+                        uint32_t rank = 0u;
+#pragma unroll 4
+                        for (int o = 1; o < 32; ++o) {
+                            const unsigned src = (lane + o) & 31u;
+                            const uint32_t other = __shfl_sync(FULL_MASK, mykey, src);
+                            rank += (other > mykey || (other == mykey && src < lane)) ? 1u : 0u;
+                        }
+                        if (rank == r - 1u) S.wkth[warp] = mykey;
+                        __syncthreads();
+                        if (tid == 0) {
+                            uint32_t lo = S.wkth[0];
 #pragma unroll
-                for (int e = 1; e < VEC; ++e) vm = fmaxf(vm, x[e]);
-                tmax = fmaxf(tmax, vm);
-                if (__any_sync(FULL_MASK, vm >= tau)) {
+                            for (int w = 1; w < WARPS; ++w) lo = min(lo, S.wkth[w]);
+                            S.tau_key = max(lo, LOWEST);
+                        }
+                        __syncthreads();
+                    }
+                }
+                const float tau = okey_to_float(vol_load(&S.tau_key));
+                // (A) this warp's list of vectors that hold a passing value
+                uint32_t wcnt = 0u;
 #pragma unroll
-                    for (int e = 0; e < VEC; ++e)
-                        warp_append(x[e] >= tau, temper(x[e], T), gid0 + rel0 + e, S, cand_q, cand_i, P.ccap, end);
+                for (int u = 0; u < U; ++u) {
+                    const bool hit = vm[u] >= tau;
+                    const unsigned pm = __ballot_sync(FULL_MASK, hit);
+                    if (hit) hit_list[warp][wcnt + (uint32_t)__popc(pm & ((1u << lane) - 1u))] = (uint16_t)(u * THREADS + tid);
+                    wcnt += (uint32_t)__popc(pm);
+                }
+                if (lane == 0) S.hit_cnt[warp] = wcnt;
+                __syncthreads();
+                // (B) element (g, e): entry g of the concatenated lists, element e of that vector
+                uint32_t pre[WARPS + 1];
+                pre[0] = 0u;
+#pragma unroll
+                for (int w = 0; w < WARPS; ++w) pre[w + 1] = pre[w] + S.hit_cnt[w];
+                const uint32_t items = pre[WARPS] * VEC;
+                for (uint32_t base = 0; base < items; base += THREADS) {
+                    const uint32_t i = base + tid;
+                    float x = __uint_as_float(0x7fc00000u);
+                    uint32_t rel = 0u;
+                    if (i < items) {
+                        const uint32_t g = i / VEC, e = i % VEC;
+                        uint32_t w = 0u, off = 0u;
+#pragma unroll
+                        for (int k = 1; k < WARPS; ++k) {
+                            if (g >= pre[k]) {
+                                w = (uint32_t)k;
+                                off = pre[k];
+                            }
+                        }
+                        const uint32_t j = hit_list[w][g - off];
+                        rel = head + (t * VPS + j) * VEC + e;
+                        x = load_logit(reinterpret_cast<const ElemT*>(sv) + (size_t)j * VEC + e);
+                        if (BITS) {
+                            const uint32_t j2 = rel + lead;
+                            if ((bitmap[j2 >> 5] >> (j2 & 31u)) & 1u) x = __uint_as_float(0x7fc00000u);  // flagged: not part of the stream
+                        }
+                    }
+                    const bool pass = x >= tau;
+                    warp_append(pass, pass ? temper(x, T) : 0.0f, gid0 + rel, S, cand_q, cand_i, P.ccap, end);
                 }
             }
         }
-        if (rc.windowed) {
-            const uint32_t mk = okey(tmax);
-            if (mk > seen_max_key) {
-                atomicMax(&S.max_key, mk);
-                seen_max_key = mk;
-            }
+        if (rc.windowed && tt == vtiles) {
+            // covers rows too short for a whole vector: only the leading / trailing elements exist
+            const uint32_t wk = __reduce_max_sync(FULL_MASK, okey(tmax));
+            if (lane == 0) atomicMax(&S.max_key, wk);
         }
-        const int over = __syncthreads_or(end > limit);
+        end = __reduce_max_sync(FULL_MASK, end);
+        const int over = __syncthreads_or(end > P.limit ? 1 : 0);
+        // every thread is done with this stage: refill it
+        if (tid == 0 && tt + RING_STAGES < vtiles) issue(tt + RING_STAGES);
         if (over) {
             uint32_t n = min(S.count, P.ccap);
             __syncthreads();
@@ -383,36 +595,34 @@ __global__ void __launch_bounds__(THREADS) stream_select_kernel(const __grid_con
                 n = compact_inplace(
                     n, [=](float q, uint32_t) { return q >= tq; }, S, cand_q, cand_i);
                 if (tid == 0) {
-                    if (n > limit) {  // the window does not fit: the full-sort kernel takes the row
+                    if (n > P.limit) {  // the window does not fit: the full-sort kernel takes the row
                         S.count = 0u;
-                        S.tau_key = 0xff800000u;  // okey(+inf)
+                        S.tau_key = 0xff800000u;  // okey(+inf): nothing finite passes any more
                         S.error |= 2u;
                     } else {
                         S.count = n;
-                        S.tau_key = max(S.tau_key, raw_threshold_key(tq, T));
                     }
                 }
             }
             __syncthreads();
             end = S.count;
-        } else if (rc.windowed && tid == 0) {
-            const float qmax = temper(okey_to_float(S.max_key), T);
-            const uint32_t tk = raw_threshold_key(window_stream_bound(qmax), T);
-            if (tk > S.tau_key) S.tau_key = tk;
-        }
-        if (t < ntiles) {
-#pragma unroll
-            for (int u = 0; u < U; ++u) cur[u] = nxt[u];
         }
     }
     __syncthreads();
+    PHASE(2);
+    if (wait_failed) atomicOr(&S.error, 4u);
+    __syncthreads();
 
     uint32_t n = min(S.count, P.ccap);
-    bool overflow = (S.error & 2u) != 0u;
+    bool overflow = (S.error & 3u) != 0u;  // window too large, or an append fell off the buffer
     float qmax = temper(okey_to_float(S.max_key), T);
+    if (S.error & 4u) {  // a bulk copy never completed: report, do not guess
+        if (tid == 0 && P.device_errors) atomicOr(P.device_errors, 1u);
+        overflow = true;
+    }
 
     if (P.split == 1u) {
-        finish_row(P, b, rc, n, overflow, qmax, S, cand_q, cand_i);
+        finish_row(P, b, rc, n, overflow, qmax, S, cand_q, cand_i, ring);
         return;
     }
 
@@ -451,14 +661,15 @@ __global__ void __launch_bounds__(THREADS) stream_select_kernel(const __grid_con
     if (tid == 0) P.sc_ticket[b] = 0u;  // re-armed for the next launch on this stream
     __threadfence();
     n = merge_lists(P, b, rc, P.split, S, cand_q, cand_i, overflow, qmax);
-    finish_row(P, b, rc, n, overflow, qmax, S, cand_q, cand_i);
+    finish_row(P, b, rc, n, overflow, qmax, S, cand_q, cand_i, ring);
 }
 
 // Ordered tail over gathered candidate lists: one CTA per row.
 __global__ void __launch_bounds__(THREADS) merge_draw_kernel(const __grid_constant__ KParams P) {
-    extern __shared__ __align__(16) unsigned char dyn[];
+    extern __shared__ __align__(128) unsigned char dyn[];
     __shared__ Shared S;
-    float* cand_q = reinterpret_cast<float*>(dyn);
+    unsigned char* scratch = dyn;  // epilogue scratch where the streaming kernel has its ring
+    float* cand_q = reinterpret_cast<float*>(dyn + RING_STAGES * STAGE_BYTES);
     uint32_t* cand_i = reinterpret_cast<uint32_t*>(cand_q + P.ccap);
     const uint32_t b = blockIdx.x;
     if (threadIdx.x == 0) {
@@ -478,7 +689,7 @@ __global__ void __launch_bounds__(THREADS) merge_draw_kernel(const __grid_consta
     bool overflow;
     float qmax;
     const uint32_t n = merge_lists(P, b, rc, P.split, S, cand_q, cand_i, overflow, qmax);
-    finish_row(P, b, rc, n, overflow, qmax, S, cand_q, cand_i);
+    finish_row(P, b, rc, n, overflow, qmax, S, cand_q, cand_i, scratch);
 }
 
 // ---------------------------------------------------------------------------
@@ -775,16 +986,35 @@ static uint32_t pow2_ceil(uint32_t x) {
 
 int plan_launch(const DeviceInfo& dev, const KParams& base, bool top_k_known, uint32_t top_k_hint, uint32_t max_top_k,
                 uint32_t max_history, uint32_t requested_split, uint32_t max_lists, LaunchPlan* plan) {
+    const uint32_t tile = STAGE_BYTES / (base.dtype == LLM_CUDA_DTYPE_BF16 ? 2u : 4u);  // logits per ring stage
     // candidate capacity
     uint32_t kcap;
+    bool window_only = false;  // every non-greedy row is known to run in window mode
     if (top_k_known) {
         const uint32_t k = (top_k_hint == 0u || top_k_hint >= base.vocab_global) ? base.vocab_global : top_k_hint;
-        kcap = (k <= MAX_KCAP) ? pow2_ceil(k < 256u ? 256u : k) : 1024u;
+        if (k <= MAX_KCAP) {
+            kcap = pow2_ceil(k < 64u ? 64u : k);
+        } else {
+            kcap = 64u;  // only greedy rows (k = 1) are selected exactly in such a launch
+            window_only = true;
+        }
     } else {
-        kcap = pow2_ceil(max_top_k < 256u ? 256u : (max_top_k > MAX_KCAP ? MAX_KCAP : max_top_k));
+        kcap = pow2_ceil(max_top_k < 64u ? 64u : (max_top_k > MAX_KCAP ? MAX_KCAP : max_top_k));
     }
     plan->kcap = kcap;
-    plan->ccap = 2u * kcap + TILE_ELEMS;
+    if (window_only) {
+        // no per-tile headroom: an append that falls off the buffer sends the row to the full-sort kernel
+        plan->ccap = WINDOW_CAP;
+        plan->limit = WINDOW_CAP / 2u;
+    } else {
+        // a tile can append at most `tile` entries, so the buffer never overflows between two checks
+        // ... on top of the compaction trigger and of the penalised ids, which are appended before the stream
+        uint32_t hist = 0u;
+        if (base.history != nullptr) hist = base.hist_len_rows ? base.hist_stride : base.hist_len;
+        plan->limit = 2u * kcap;
+        plan->ccap = (2u * kcap > hist ? 2u * kcap : hist) + 32u + tile;
+        if (plan->ccap < WINDOW_CAP) plan->ccap = WINDOW_CAP;  // rows with top_k 0 may be mixed in
+    }
     plan->bits = (base.allowed_bits != nullptr) || (base.history != nullptr && (base.r_rows != nullptr || base.penalty != 1.0f) &&
                                                     (base.hist_len_rows != nullptr || base.hist_len > 0u));
     // split: fill the machine when the batch is small, keep shards long enough to stream
@@ -792,7 +1022,7 @@ int plan_launch(const DeviceInfo& dev, const KParams& base, bool top_k_known, ui
     if (split == 0u) {
         const uint32_t target = 4u * dev.sm_count;
         split = target / (base.batch ? base.batch : 1u);
-        const uint32_t by_len = base.vocab / 8192u;
+        const uint32_t by_len = base.vocab / (4u * tile);
         if (split > by_len) split = by_len;
     }
     if (split < 1u) split = 1u;
@@ -814,7 +1044,8 @@ int plan_launch(const DeviceInfo& dev, const KParams& base, bool top_k_known, ui
         plan->bitmap_words = 0u;
         plan->hash_slots = 0u;
     }
-    plan->smem = (size_t)plan->ccap * 8u + (size_t)plan->bitmap_words * 4u + (size_t)plan->hash_slots * 8u;
+    plan->smem = (size_t)RING_STAGES * STAGE_BYTES + (size_t)plan->ccap * 8u + (size_t)plan->bitmap_words * 4u +
+                 (size_t)plan->hash_slots * 8u;
     if (plan->smem > dev.max_dyn_smem) return -1;
     return 0;
 }
@@ -847,7 +1078,7 @@ cudaError_t launch_stream_select(const KParams& P, const LaunchPlan& plan, cudaS
 }
 
 cudaError_t launch_merge_draw(const KParams& P, const LaunchPlan& plan, cudaStream_t stream) {
-    const size_t smem = (size_t)plan.ccap * 8u;
+    const size_t smem = (size_t)RING_STAGES * STAGE_BYTES + (size_t)plan.ccap * 8u;
     merge_draw_kernel<<<P.batch, THREADS, smem, stream>>>(P);
     return cudaGetLastError();
 }

@@ -38,7 +38,7 @@ struct KParams {
     uint32_t col_offset, vocab_global;
     // launch geometry
     uint32_t split, shard_cols;
-    uint32_t kcap, ccap;            // kcap: candidates carried across compactions; ccap = 2*kcap + TILE_ELEMS
+    uint32_t kcap, ccap, limit;     // kcap: exact-selection capacity; ccap: buffer entries; limit: compaction trigger
     uint32_t hash_slots, bitmap_words;
     // scratch shared by the CTAs of one row when split > 1 (also the input of merge_draw)
     float* sc_q;                    // [shard][row][sc_stride]   (element (s, b, i) at (s*sc_rows + b)*sc_stride + i)
@@ -56,6 +56,9 @@ struct KParams {
     uint32_t* full_list;
     uint32_t* full_count;
     uint32_t force_full;
+    uint32_t* device_errors;        // bit 0: a bulk copy did not complete within the wait limit
+    unsigned long long* phase_ns;   // optional [CTAs][8] phase timestamps (development aid), or NULL
+    uint32_t debug_mode;            // development aid: 1 = skip pass B, 2 = skip pass A and B, 3 = stream only then exit
 };
 
 struct DeviceInfo {
@@ -64,7 +67,7 @@ struct DeviceInfo {
 };
 
 struct LaunchPlan {
-    uint32_t split, shard_cols, kcap, ccap, hash_slots, bitmap_words;
+    uint32_t split, shard_cols, kcap, ccap, limit, hash_slots, bitmap_words;
     size_t smem;
     bool bits;  // mask or penalty tables needed
 };
