@@ -134,6 +134,12 @@ __device__ __forceinline__ unsigned long long global_ns() {
     } while (0)
 
 __device__ __forceinline__ void push_full(const KParams& P, uint32_t b) {
+    if (!P.full_list) {  // a caller without a full-sort stage: the row is reported, not guessed
+        P.tokens[b] = 0u;
+        if (P.row_flags) P.row_flags[b] = LLM_CUDA_ROW_INVALID;
+        if (P.kept_count) P.kept_count[b] = 0u;
+        return;
+    }
     const uint32_t pos = atomicAdd(P.full_count, 1u);
     P.full_list[pos] = b;
 }
@@ -446,13 +452,23 @@ __global__ void __launch_bounds__(THREADS) stream_select_kernel(const __grid_con
     //      threshold in its warp's list; (B) after a barrier all threads share out the listed vectors
     //      element by element, so examining and appending candidates is parallel and free of divergence.
     bool wait_failed = false;
+    long long acc[6] = {0, 0, 0, 0, 0, 0};
+    long long c_a = clock64(), c_b;
+#define TICK(k)                      \
+    do {                             \
+        c_b = clock64();             \
+        acc[k] += c_b - c_a;         \
+        c_a = c_b;                   \
+    } while (0)
     for (uint32_t tt = 0; tt <= vtiles; ++tt) {
         // iteration tt == vtiles only settles the buffer
         const bool max_sweep = rc.windowed && tt < ntiles;  // first sweep of a window-mode row
         const uint32_t t = (rc.windowed && tt >= ntiles) ? tt - ntiles : tt;  // tile within the row
         if (tt < vtiles) {
             const uint32_t stage = tt % RING_STAGES;
+            TICK(5);
             if (!mbar_wait_bounded(&full_bar[stage], (tt / RING_STAGES) & 1u)) wait_failed = true;
+            TICK(0);
             const uint4* sv = reinterpret_cast<const uint4*>(ring + (size_t)stage * STAGE_BYTES);
             float vm[U];
 #pragma unroll
@@ -525,7 +541,7 @@ __global__ void __launch_bounds__(THREADS) stream_select_kernel(const __grid_con
                     }
                 }
                 const float tau = okey_to_float(vol_load(&S.tau_key));
-                // (A) this warp's list of vectors that hold a passing value
+                // this warp's list of vectors that hold a passing value ...
                 uint32_t wcnt = 0u;
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
@@ -534,39 +550,32 @@ __global__ void __launch_bounds__(THREADS) stream_select_kernel(const __grid_con
                     if (hit) hit_list[warp][wcnt + (uint32_t)__popc(pm & ((1u << lane) - 1u))] = (uint16_t)(u * THREADS + tid);
                     wcnt += (uint32_t)__popc(pm);
                 }
-                if (lane == 0) S.hit_cnt[warp] = wcnt;
-                __syncthreads();
-                // (B) element (g, e): entry g of the concatenated lists, element e of that vector
-                uint32_t pre[WARPS + 1];
-                pre[0] = 0u;
-#pragma unroll
-                for (int w = 0; w < WARPS; ++w) pre[w + 1] = pre[w] + S.hit_cnt[w];
-                const uint32_t items = pre[WARPS] * VEC;
-                for (uint32_t base = 0; base < items; base += THREADS) {
-                    const uint32_t i = base + tid;
-                    float x = __uint_as_float(0x7fc00000u);
-                    uint32_t rel = 0u;
-                    if (i < items) {
-                        const uint32_t g = i / VEC, e = i % VEC;
-                        uint32_t w = 0u, off = 0u;
-#pragma unroll
-                        for (int k = 1; k < WARPS; ++k) {
-                            if (g >= pre[k]) {
-                                w = (uint32_t)k;
-                                off = pre[k];
+                TICK(1);
+                if (wcnt) {
+                    // ... examined by the warp itself, 32/VEC vectors at a time: lane l looks at element
+                    // l % VEC of list entry l / VEC, so no lane runs a long divergent path and warps
+                    // without a passing value skip all of this
+                    __syncwarp();
+                    constexpr uint32_t G = 32u / VEC;
+                    for (uint32_t g0 = 0; g0 < wcnt; g0 += G) {
+                        const uint32_t g = g0 + lane / VEC, e = lane % VEC;
+                        float x = __uint_as_float(0x7fc00000u);
+                        uint32_t rel = 0u;
+                        if (g < wcnt) {
+                            const uint32_t j = hit_list[warp][g];
+                            rel = head + (t * VPS + j) * VEC + e;
+                            x = load_logit(reinterpret_cast<const ElemT*>(sv) + (size_t)j * VEC + e);
+                            if (BITS) {
+                                const uint32_t j2 = rel + lead;
+                                if ((bitmap[j2 >> 5] >> (j2 & 31u)) & 1u) x = __uint_as_float(0x7fc00000u);  // flagged: not part of the stream
                             }
                         }
-                        const uint32_t j = hit_list[w][g - off];
-                        rel = head + (t * VPS + j) * VEC + e;
-                        x = load_logit(reinterpret_cast<const ElemT*>(sv) + (size_t)j * VEC + e);
-                        if (BITS) {
-                            const uint32_t j2 = rel + lead;
-                            if ((bitmap[j2 >> 5] >> (j2 & 31u)) & 1u) x = __uint_as_float(0x7fc00000u);  // flagged: not part of the stream
-                        }
+                        const bool pass = x >= tau;
+                        warp_append(pass, pass ? temper(x, T) : 0.0f, gid0 + rel, S, cand_q, cand_i, P.ccap, end);
                     }
-                    const bool pass = x >= tau;
-                    warp_append(pass, pass ? temper(x, T) : 0.0f, gid0 + rel, S, cand_q, cand_i, P.ccap, end);
+                    __syncwarp();
                 }
+                TICK(3);
             }
         }
         if (rc.windowed && tt == vtiles) {
@@ -575,7 +584,9 @@ __global__ void __launch_bounds__(THREADS) stream_select_kernel(const __grid_con
             if (lane == 0) atomicMax(&S.max_key, wk);
         }
         end = __reduce_max_sync(FULL_MASK, end);
+        TICK(3);
         const int over = __syncthreads_or(end > P.limit ? 1 : 0);
+        TICK(4);
         // every thread is done with this stage: refill it
         if (tid == 0 && tt + RING_STAGES < vtiles) issue(tt + RING_STAGES);
         if (over) {
@@ -610,6 +621,11 @@ __global__ void __launch_bounds__(THREADS) stream_select_kernel(const __grid_con
     }
     __syncthreads();
     PHASE(2);
+    if (P.phase_ns && (tid == 0 || tid == 255)) {
+        unsigned long long* o = P.phase_ns + ((size_t)gridDim.x * gridDim.y + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 2u + (tid ? 1u : 0u)) * 8u;
+        for (int k = 0; k < 6; ++k) o[k] = acc[k];
+        o[6] = vtiles; o[7] = S.count;
+    }
     if (wait_failed) atomicOr(&S.error, 4u);
     __syncthreads();
 
@@ -1019,6 +1035,11 @@ int plan_launch(const DeviceInfo& dev, const KParams& base, bool top_k_known, ui
                                                     (base.hist_len_rows != nullptr || base.hist_len > 0u));
     // split: fill the machine when the batch is small, keep shards long enough to stream
     uint32_t split = requested_split;
+    if (split == 0u && window_only) {
+        // a window is measured from the row's maximum; a CTA that sees only part of the row
+        // would measure it from its own, lower maximum and keep far too much
+        split = 1u;
+    }
     if (split == 0u) {
         const uint32_t target = 4u * dev.sm_count;
         split = target / (base.batch ? base.batch : 1u);

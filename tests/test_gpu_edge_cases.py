@@ -166,7 +166,7 @@ def test_peaked_distribution_without_truncation_stays_on_the_window_path(sampler
     g = np.random.default_rng(8)
     B, V = 16, 30000
     x = g.normal(0, 4.0, (B, V)).astype(np.float32)
-    x[np.arange(B), g.integers(0, V, B)] += 25.0
+    x[np.arange(B), g.integers(0, V, B)] = 34.0  # the rest tops out near 16: a few dozen values fall inside the window
     w = _wl(x, temperature=1.0, top_k=0, top_p=1.0, min_p=0.0)
     gpu = parity.run_gpu(sampler, w)
     orc = parity.run_oracle(w, oracle.EXP_CR)
