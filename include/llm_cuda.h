@@ -215,6 +215,31 @@ int32_t llm_cuda_pack_allowed(llm_cuda_sampler* s, const uint8_t* allowed_host, 
  * kernels it launched and the CTAs-per-row split it chose. */
 int32_t llm_cuda_last_launch_info(const llm_cuda_sampler* s, uint32_t* kernels_launched, uint32_t* split_used);
 
+/* Limits of llm_cuda_sample_batch_static (the size of its fixed scratch follows from them:
+ * 256 candidate lists of 2*256 entries, about 1 MiB per GPU that loads the library). */
+#define LLM_CUDA_STATIC_MAX_BATCH 64u
+#define LLM_CUDA_STATIC_MAX_TOP_K 256u
+#define LLM_CUDA_STATIC_MAX_HISTORY 512u
+
+/* llm_cuda_sample_batch without a handle and without any allocation. It has no counterpart
+ * in the reference (whose sampler allocates two Vecs per call, generate.rs:331,364); it exists
+ * for callers that are not allowed to call cudaMalloc / cudaFree at all - a serving loop whose
+ * device memory is partitioned once and then frozen, a host framework that owns the allocator,
+ * a plugin that only ever receives device pointers and a stream. The scratch that rows split
+ * over several CTAs need lives in a fixed array inside the library image (every GPU that loads
+ * the library holds it until the process exits), so:
+ *   - sizes are capped: batch <= 64, 0 < top_k <= 256 (or greedy), history <= 512; no per-row
+ *     top_k / temperature arrays, no allowed mask, no vocabulary sharding - anything that could
+ *     need the window or full-sort stages returns LLM_CUDA_ERR_UNSUPPORTED / _CAPACITY;
+ *   - all calls share the one array: calls that overlap on the GPU race; serialise them
+ *     (one stream, or events between streams);
+ *   - the first call on a device looks up the array's device address and raises the kernels'
+ *     shared-memory limit; make that first call before any stream capture begins.
+ * Same arguments and results as llm_cuda_sample_batch otherwise (asynchronous on args->stream).
+ * Errors: llm_cuda_static_last_error(). */
+int32_t llm_cuda_sample_batch_static(int32_t device, const llm_cuda_sample_args* args);
+const char* llm_cuda_static_last_error(void);
+
 uint32_t llm_cuda_abi_version(void);
 
 #ifdef __cplusplus

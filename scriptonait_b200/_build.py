@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIBDIR = os.path.join(HERE, "lib")
 LIBRARY = os.path.join(LIBDIR, "libllm_cuda.so")
-SOURCES = ["sampler_kernels.cu", "llm_cuda_api.cu"]
+SOURCES = ["sampler_kernels.cu", "llm_cuda_api.cu", "no_alloc.cu"]
 HEADERS = ["sampler_kernels.h", "sampler_device.cuh", os.path.join("..", "..", "include", "llm_cuda.h")]
 
 NVCC_FLAGS = [

@@ -36,8 +36,9 @@ EXPORTS = [
     "llm_cuda_abi_version", "llm_cuda_sampling_config_default", "llm_cuda_sampler_create", "llm_cuda_sampler_destroy",
     "llm_cuda_last_error", "llm_cuda_sample_batch", "llm_cuda_sample_batch_host", "llm_cuda_sample_with",
     "llm_cuda_sample", "llm_cuda_shard_select", "llm_cuda_merge_draw", "llm_cuda_advance_rows",
-    "llm_cuda_pack_allowed", "llm_cuda_last_launch_info",
+    "llm_cuda_pack_allowed", "llm_cuda_last_launch_info", "llm_cuda_sample_batch_static", "llm_cuda_static_last_error",
 ]
+STATIC_MAX_BATCH, STATIC_MAX_TOP_K, STATIC_MAX_HISTORY = 64, 256, 512
 
 
 class SamplingConfigC(C.Structure):
@@ -119,6 +120,10 @@ def load() -> C.CDLL:
     L.llm_cuda_pack_allowed.argtypes = [vp, vp, u32, vp, vp]
     L.llm_cuda_last_launch_info.restype = i32
     L.llm_cuda_last_launch_info.argtypes = [vp, C.POINTER(u32), C.POINTER(u32)]
+    L.llm_cuda_sample_batch_static.restype = i32
+    L.llm_cuda_sample_batch_static.argtypes = [i32, C.POINTER(SampleArgs)]
+    L.llm_cuda_static_last_error.restype = C.c_char_p
+    L.llm_cuda_static_last_error.argtypes = []
     if L.llm_cuda_abi_version() != ABI_VERSION:
         raise RuntimeError("libllm_cuda.so ABI version mismatch")
     _lib = L
