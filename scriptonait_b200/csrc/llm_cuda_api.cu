@@ -56,6 +56,7 @@ struct llm_cuda_sampler {
     unsigned char* arena = nullptr;
     size_t arena_bytes = 0;
     uint32_t last_kernels = 0, last_split = 0;
+    bool host_full_sort = false;  // launch the full-sort kernel from the host after every call that may need it
     char err[512] = "";
 };
 
@@ -204,6 +205,16 @@ int32_t run_select(llm_cuda_sampler* s, const llm_cuda_sample_args* a, KParams& 
     s->last_kernels = 0;
     s->last_split = plan.split;
     if (P.batch == 0) return LLM_CUDA_OK;
+    // rows the window cannot decide are rare: the full-sort kernel is launched from the device, by
+    // the first CTA that needs it, instead of from here on every call (LLM_CUDA_HOST_FULL_SORT=1
+    // restores the host-side launch)
+    P.full_keys = reinterpret_cast<unsigned long long*>(s->full_keys);
+    P.full_vals = s->full_vals;
+    P.full_ticket = s->full_ticket;
+    P.full_vpad = s->vpad;
+    P.full_nslots = s->nslots;
+    P.full_hash_slots = s->hash_slots;
+    P.tail_launch = (s->host_full_sort || lists_out) ? 0u : 1u;
     CUDA_TRY(s, launch_stream_select(P, plan, stream));
     s->last_kernels++;
     bool may_need_full = false;
@@ -217,7 +228,7 @@ int32_t run_select(llm_cuda_sampler* s, const llm_cuda_sample_args* a, KParams& 
             may_need_full = k_eff > plan.kcap;
         }
     }
-    if (may_need_full) {
+    if (may_need_full && !P.tail_launch) {
         CUDA_TRY(s, launch_full_sort(P, s->hash_slots, s->nslots, s->full_keys, s->full_vals, s->vpad, s->full_ticket, stream));
         s->last_kernels++;
     }
@@ -278,6 +289,7 @@ int32_t llm_cuda_sampler_create(int32_t device, uint32_t max_batch, uint32_t max
     s->max_vocab = max_vocab;
     s->max_history = max_history;
     s->max_top_k = max_top_k ? max_top_k : 1u;
+    { const char* hf = getenv("LLM_CUDA_HOST_FULL_SORT"); s->host_full_sort = hf && hf[0] == '1'; }
     s->dev.sm_count = (uint32_t)prop.multiProcessorCount;
     s->dev.max_dyn_smem = (size_t)prop.sharedMemPerBlockOptin - 4096u;  // room for the kernels' static shared memory
     auto bail = [&](const char* what, cudaError_t ce) {

@@ -133,6 +133,10 @@ __device__ __forceinline__ unsigned long long global_ns() {
             P.phase_ns[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 8u + (slot)] = global_ns();              \
     } while (0)
 
+constexpr int FULL_THREADS = 1024;
+__global__ void full_sort_kernel(const __grid_constant__ KParams P, uint64_t* keys_all, float* vals_all, uint32_t vpad,
+                                 uint32_t* ticket);
+
 __device__ __forceinline__ void push_full(const KParams& P, uint32_t b) {
     if (!P.full_list) {  // a caller without a full-sort stage: the row is reported, not guessed
         P.tokens[b] = 0u;
@@ -142,6 +146,14 @@ __device__ __forceinline__ void push_full(const KParams& P, uint32_t b) {
     }
     const uint32_t pos = atomicAdd(P.full_count, 1u);
     P.full_list[pos] = b;
+    if (pos == 0u && P.tail_launch) {
+        // first row of this launch that needs the full ordering: queue the full-sort kernel behind
+        // this grid (it starts when every CTA of this grid has finished, so the list is complete)
+        KParams Q = P;
+        Q.hash_slots = P.full_hash_slots;
+        full_sort_kernel<<<P.full_nslots, FULL_THREADS, (size_t)P.full_hash_slots * 8u, cudaStreamTailLaunch>>>(
+            Q, reinterpret_cast<uint64_t*>(P.full_keys), P.full_vals, P.full_vpad, P.full_ticket);
+    }
 }
 
 // Streaming threshold of window mode for a given maximum (both in the post-temperature domain).
@@ -271,7 +283,7 @@ __device__ uint32_t merge_lists(const KParams& P, uint32_t b, const RowCfg& rc, 
 // stages filled by bulk copies, so RING_STAGES-1 stages (8 KB each) are always in
 // flight per CTA whatever the occupancy.
 template <typename ElemT, bool BITS>
-__global__ void __launch_bounds__(THREADS) stream_select_kernel(const __grid_constant__ KParams P) {
+__global__ void __launch_bounds__(THREADS, 3) stream_select_kernel(const __grid_constant__ KParams P) {
     constexpr int VEC = Traits<ElemT>::VEC;
     constexpr uint32_t VPS = STAGE_BYTES / 16u;      // 16-byte vectors per stage
     constexpr int U = VPS / THREADS;                 // vectors per thread per stage
@@ -286,6 +298,7 @@ __global__ void __launch_bounds__(THREADS) stream_select_kernel(const __grid_con
     uint32_t* bitmap = cand_i + P.ccap;
     uint32_t* hkeys = bitmap + P.bitmap_words;
     uint32_t* hcnt = hkeys + P.hash_slots;
+    uint32_t* grp_max = hcnt + P.hash_slots;  // window-mode rows: ordered key of each 32-vector group's maximum
 
     const uint32_t b = blockIdx.y, shard = blockIdx.x, tid = threadIdx.x;
     const unsigned lane = tid & 31u, warp = tid >> 5;
@@ -338,9 +351,9 @@ __global__ void __launch_bounds__(THREADS) stream_select_kernel(const __grid_con
     const uint32_t ntiles = (nvi + VPS - 1u) / VPS;
 
     // ---- start the ring before anything else: the copies run while the side tables are built
-    const uint32_t vtiles = rc.windowed ? 2u * ntiles : ntiles;  // window-mode rows are swept twice
-    auto issue = [&](uint32_t tt) {  // thread 0 only; tt counts stages over both sweeps
-        const uint32_t t = tt >= ntiles ? tt - ntiles : tt;
+    const uint32_t vtiles = ntiles;
+    auto issue = [&](uint32_t tt) {  // thread 0 only
+        const uint32_t t = tt;
         const uint32_t first = t * VPS;
         const uint32_t nv = min(VPS, nvi - first);
         uint64_t* bar = &full_bar[tt % RING_STAGES];
@@ -443,14 +456,14 @@ __global__ void __launch_bounds__(THREADS) stream_select_kernel(const __grid_con
         warp_append(valid && x >= neg_inf(), temper(x, T), gid0 + rel, S, cand_q, cand_i, P.ccap, end);
     }
 
-    // ---- the stream. Rows in window mode are streamed twice: a first sweep only finds the row's
-    //      maximum (the threshold max - 17.5 is then exact from the first candidate on, wherever in
-    //      the row the maximum sits), the second sweep - served from L2, which the first sweep has
-    //      just filled - collects. Other rows are streamed once.
-    //      Per stage of a collecting sweep: (A) every lane takes the maximum of each of its 16-byte
-    //      vectors (packed bf16 arithmetic for bf16 rows) and notes the vectors that reach the
-    //      threshold in its warp's list; (B) after a barrier all threads share out the listed vectors
-    //      element by element, so examining and appending candidates is parallel and free of divergence.
+    // ---- the stream.
+    //      Window-mode rows: one sweep that only takes maxima - per thread for the row's maximum,
+    //      per group of 32 vectors (one warp step, 512 bytes) into `grp_max`. When the sweep ends
+    //      the threshold max - 17.5 is exact wherever in the row the maximum sat, and only the
+    //      groups whose maximum reaches it (a few per cent of the row) are read again, from L2.
+    //      Other rows: per stage, (A) every lane takes the maximum of each of its 16-byte vectors
+    //      (packed bf16 arithmetic for bf16 rows) and notes the vectors that reach the threshold in
+    //      its warp's list, (B) the warp examines its listed vectors 32/VEC at a time.
     bool wait_failed = false;
     long long acc[6] = {0, 0, 0, 0, 0, 0};
     long long c_a = clock64(), c_b;
@@ -462,8 +475,8 @@ __global__ void __launch_bounds__(THREADS) stream_select_kernel(const __grid_con
     } while (0)
     for (uint32_t tt = 0; tt <= vtiles; ++tt) {
         // iteration tt == vtiles only settles the buffer
-        const bool max_sweep = rc.windowed && tt < ntiles;  // first sweep of a window-mode row
-        const uint32_t t = (rc.windowed && tt >= ntiles) ? tt - ntiles : tt;  // tile within the row
+        const bool max_sweep = rc.windowed != 0u;  // window-mode rows only take maxima here
+        const uint32_t t = tt;
         if (tt < vtiles) {
             const uint32_t stage = tt % RING_STAGES;
             TICK(5);
@@ -499,18 +512,16 @@ __global__ void __launch_bounds__(THREADS) stream_select_kernel(const __grid_con
                                 if (!((nib >> e) & 1u)) m = fmaxf(m, x[e]);
                         }
                         tmax = fmaxf(tmax, m);
+                        vm[u] = m;
                     }
                 }
             }
             if (max_sweep) {
-                if (tt + 1u == ntiles) {  // end of the first sweep: the row's maximum fixes the threshold
-                    const uint32_t wk = __reduce_max_sync(FULL_MASK, okey(tmax));
-                    if (lane == 0) atomicMax(&S.max_key, wk);
-                    __syncthreads();
-                    if (tid == 0) {
-                        const float qmax = temper(okey_to_float(S.max_key), T);
-                        S.tau_key = raw_threshold_key(window_stream_bound(qmax), T);
-                    }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    // vm[u] is the lane's maximum over unflagged elements when BITS (recomputed above)
+                    const uint32_t gk = __reduce_max_sync(FULL_MASK, (vm[u] == vm[u]) ? okey(vm[u]) : LOWEST);
+                    if (lane == 0) grp_max[(t * U + u) * WARPS + warp] = gk;
                 }
             } else {
                 if (tt == 0) {
@@ -620,6 +631,85 @@ __global__ void __launch_bounds__(THREADS) stream_select_kernel(const __grid_con
         }
     }
     __syncthreads();
+    if (rc.windowed) {
+        // the row's maximum fixes the threshold; every warp then revisits its share of the groups
+        // that can hold a value inside the window
+        if (tid == 0) {
+            const float qmax0 = temper(okey_to_float(S.max_key), T);
+            S.tau_key = raw_threshold_key(window_stream_bound(qmax0), T);
+        }
+        __syncthreads();
+        const uint32_t tau_key = S.tau_key;
+        const float tau = okey_to_float(tau_key);
+        const uint32_t ngroups = (nvi + 31u) / 32u;
+        const uint4* gv = reinterpret_cast<const uint4*>(vbase);
+        // list the qualifying groups (the warps' vector lists are free now and serve as storage)
+        uint16_t* glist = &hit_list[0][0];
+        constexpr uint32_t GLIST_CAP = WARPS * U * 32u;
+        const bool listable = ngroups <= 65536u;
+        if (tid == 0) S.keep = 0u;
+        __syncthreads();
+        if (listable) {
+            for (uint32_t g = tid; g < ngroups; g += THREADS) {
+                if (grp_max[g] >= tau_key) {
+                    const uint32_t pos = atomicAdd(&S.keep, 1u);
+                    if (pos < GLIST_CAP) glist[pos] = (uint16_t)g;
+                }
+            }
+        }
+        __syncthreads();
+        const uint32_t nq = S.keep;
+        auto examine = [&](const uint4& raw, uint32_t v) {
+            float x[VEC];
+            unpack<ElemT>(raw, x);
+            uint32_t nib = 0u;
+            const uint32_t rel0 = head + v * VEC;
+            if (BITS) {
+                const uint32_t j2 = rel0 + lead;
+                nib = (bitmap[j2 >> 5] >> (j2 & 31u)) & ((1u << VEC) - 1u);  // flagged: handled before the stream
+            }
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) {
+                if (x[e] >= tau && !((nib >> e) & 1u)) {
+                    const uint32_t slot = atomicAdd(&S.count, 1u);
+                    if (slot < P.ccap) {
+                        cand_q[slot] = temper(x[e], T);
+                        cand_i[slot] = gid0 + rel0 + e;
+                    } else {
+                        S.error = 1u;
+                    }
+                }
+            }
+        };
+        if (listable && nq <= GLIST_CAP) {
+            // four groups per warp step: the four L2 reads are in flight together
+            for (uint32_t i0 = warp * 4u; i0 < nq; i0 += WARPS * 4u) {
+                uint4 raw[4];
+                uint32_t vv[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    vv[k] = 0xffffffffu;
+                    if (i0 + k < nq) {
+                        const uint32_t v = (uint32_t)glist[i0 + k] * 32u + lane;
+                        if (v < nvi) {
+                            vv[k] = v;
+                            raw[k] = __ldg(gv + v);
+                        }
+                    }
+                }
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    if (vv[k] != 0xffffffffu) examine(raw[k], vv[k]);
+            }
+        } else {
+            for (uint32_t g = warp; g < ngroups; g += WARPS) {
+                if (grp_max[g] < tau_key) continue;  // same word for the whole warp
+                const uint32_t v = g * 32u + lane;
+                if (v < nvi) examine(__ldg(gv + v), v);
+            }
+        }
+        __syncthreads();
+    }
     PHASE(2);
     if (P.phase_ns && (tid == 0 || tid == 255)) {
         unsigned long long* o = P.phase_ns + ((size_t)gridDim.x * gridDim.y + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 2u + (tid ? 1u : 0u)) * 8u;
@@ -712,8 +802,6 @@ __global__ void __launch_bounds__(THREADS) merge_draw_kernel(const __grid_consta
 // Full ordering of a row in global scratch (bitonic sort of 64-bit keys), then
 // the ordered tail exactly as the reference walks it. Slow and rarely needed:
 // rows whose window overflowed or whose kept set / walk left the window.
-constexpr int FULL_THREADS = 1024;
-
 struct FullShared {
     RowCfg rc;
     uint32_t nvalid, keep, token, flags, kept_n;
@@ -1065,8 +1153,11 @@ int plan_launch(const DeviceInfo& dev, const KParams& base, bool top_k_known, ui
         plan->bitmap_words = 0u;
         plan->hash_slots = 0u;
     }
+    // window-mode rows keep one word per group of 32 vectors of the shard
+    const uint32_t vec_elems = 16u / (base.dtype == LLM_CUDA_DTYPE_BF16 ? 2u : 4u);
+    plan->groups = (window_only || !top_k_known) ? (shard_cols / vec_elems + 31u) / 32u + WARPS * (STAGE_BYTES / 16u / THREADS) : 0u;
     plan->smem = (size_t)RING_STAGES * STAGE_BYTES + (size_t)plan->ccap * 8u + (size_t)plan->bitmap_words * 4u +
-                 (size_t)plan->hash_slots * 8u;
+                 (size_t)plan->hash_slots * 8u + (size_t)plan->groups * 4u;
     if (plan->smem > dev.max_dyn_smem) return -1;
     return 0;
 }

@@ -56,6 +56,12 @@ struct KParams {
     uint32_t* full_list;
     uint32_t* full_count;
     uint32_t force_full;
+    // full-sort stage, launched from the device (tail launch) by the first CTA that hands a row over
+    unsigned long long* full_keys;
+    float* full_vals;
+    uint32_t* full_ticket;
+    uint32_t full_vpad, full_nslots, full_hash_slots;
+    uint32_t tail_launch;           // 1: the streaming kernel launches the full-sort kernel itself when a row needs it
     uint32_t* device_errors;        // bit 0: a bulk copy did not complete within the wait limit
     unsigned long long* phase_ns;   // optional [CTAs][8] phase timestamps (development aid), or NULL
     uint32_t debug_mode;            // development aid: 1 = skip pass B, 2 = skip pass A and B, 3 = stream only then exit
@@ -67,7 +73,7 @@ struct DeviceInfo {
 };
 
 struct LaunchPlan {
-    uint32_t split, shard_cols, kcap, ccap, limit, hash_slots, bitmap_words;
+    uint32_t split, shard_cols, kcap, ccap, limit, hash_slots, bitmap_words, groups;
     size_t smem;
     bool bits;  // mask or penalty tables needed
 };
