@@ -282,7 +282,9 @@ __device__ uint32_t merge_lists(const KParams& P, uint32_t b, const RowCfg& rc, 
 // [shard*shard_cols, ...) of one row through a ring of RING_STAGES shared-memory
 // stages filled by bulk copies, so RING_STAGES-1 stages (8 KB each) are always in
 // flight per CTA whatever the occupancy.
-template <typename ElemT, bool BITS>
+// MODE trims the code to what a launch can need (the hot loop must stay small enough for the
+// instruction cache): 0 = rows of either kind, 1 = every row runs in window mode, 2 = no row does.
+template <typename ElemT, bool BITS, int MODE>
 __global__ void __launch_bounds__(THREADS, 3) stream_select_kernel(const __grid_constant__ KParams P) {
     constexpr int VEC = Traits<ElemT>::VEC;
     constexpr uint32_t VPS = STAGE_BYTES / 16u;      // 16-byte vectors per stage
@@ -315,7 +317,9 @@ __global__ void __launch_bounds__(THREADS, 3) stream_select_kernel(const __grid_
         mbar_fence_init();
     }
     __syncthreads();
-    const RowCfg rc = S.rc;
+    RowCfg rc = S.rc;
+    if (MODE == 1) rc.windowed = 1u;  // lets the compiler drop the exact-selection code
+    if (MODE == 2) rc.windowed = 0u;  // ... or the window code
     PHASE(0);
     if (rc.invalid) {
         if (shard == 0 && tid == 0) {
@@ -1106,6 +1110,10 @@ int plan_launch(const DeviceInfo& dev, const KParams& base, bool top_k_known, ui
         kcap = pow2_ceil(max_top_k < 64u ? 64u : (max_top_k > MAX_KCAP ? MAX_KCAP : max_top_k));
     }
     plan->kcap = kcap;
+    // 1: every row is known to run in window mode (scalar temperature > 0, so no greedy row either);
+    // 2: no row can; 0: decided per row in the kernel
+    const bool may_be_greedy = base.t_rows != nullptr || base.temperature <= 0.0f;
+    plan->mode = (window_only && !may_be_greedy) ? 1 : ((top_k_known && !window_only) ? 2 : 0);
     if (window_only) {
         // no per-tile headroom: an append that falls off the buffer sends the row to the full-sort kernel
         plan->ccap = WINDOW_CAP;
@@ -1162,31 +1170,46 @@ int plan_launch(const DeviceInfo& dev, const KParams& base, bool top_k_known, ui
     return 0;
 }
 
+template <typename ElemT, bool BITS>
+static cudaError_t configure_stream(int v) {
+    cudaError_t e;
+    if ((e = cudaFuncSetAttribute(stream_select_kernel<ElemT, BITS, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, v)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(stream_select_kernel<ElemT, BITS, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, v)) != cudaSuccess) return e;
+    return cudaFuncSetAttribute(stream_select_kernel<ElemT, BITS, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, v);
+}
+
 cudaError_t configure_kernels(size_t max_dyn_smem) {
     const int v = (int)max_dyn_smem;
     cudaError_t e;
-    if ((e = cudaFuncSetAttribute(stream_select_kernel<float, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, v)) != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute(stream_select_kernel<float, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, v)) != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute(stream_select_kernel<uint16_t, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, v)) != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute(stream_select_kernel<uint16_t, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, v)) != cudaSuccess) return e;
+    if ((e = configure_stream<float, false>(v)) != cudaSuccess) return e;
+    if ((e = configure_stream<float, true>(v)) != cudaSuccess) return e;
+    if ((e = configure_stream<uint16_t, false>(v)) != cudaSuccess) return e;
+    if ((e = configure_stream<uint16_t, true>(v)) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(merge_draw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, v)) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(full_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, v)) != cudaSuccess) return e;
     return cudaSuccess;
 }
 
-template <typename ElemT, bool BITS>
+template <typename ElemT, bool BITS, int MODE>
 static cudaError_t launch_stream_t(const KParams& P, const LaunchPlan& plan, cudaStream_t stream) {
-    auto kern = stream_select_kernel<ElemT, BITS>;
+    auto kern = stream_select_kernel<ElemT, BITS, MODE>;
     dim3 grid(plan.split, P.batch, 1);
     kern<<<grid, THREADS, plan.smem, stream>>>(P);
     return cudaGetLastError();
 }
 
+template <typename ElemT, bool BITS>
+static cudaError_t launch_stream_m(const KParams& P, const LaunchPlan& plan, cudaStream_t stream) {
+    if (plan.mode == 1) return launch_stream_t<ElemT, BITS, 1>(P, plan, stream);
+    if (plan.mode == 2) return launch_stream_t<ElemT, BITS, 2>(P, plan, stream);
+    return launch_stream_t<ElemT, BITS, 0>(P, plan, stream);
+}
+
 cudaError_t launch_stream_select(const KParams& P, const LaunchPlan& plan, cudaStream_t stream) {
     if (P.dtype == LLM_CUDA_DTYPE_BF16) {
-        return plan.bits ? launch_stream_t<uint16_t, true>(P, plan, stream) : launch_stream_t<uint16_t, false>(P, plan, stream);
+        return plan.bits ? launch_stream_m<uint16_t, true>(P, plan, stream) : launch_stream_m<uint16_t, false>(P, plan, stream);
     }
-    return plan.bits ? launch_stream_t<float, true>(P, plan, stream) : launch_stream_t<float, false>(P, plan, stream);
+    return plan.bits ? launch_stream_m<float, true>(P, plan, stream) : launch_stream_m<float, false>(P, plan, stream);
 }
 
 cudaError_t launch_merge_draw(const KParams& P, const LaunchPlan& plan, cudaStream_t stream) {

@@ -76,6 +76,7 @@ struct LaunchPlan {
     uint32_t split, shard_cols, kcap, ccap, limit, hash_slots, bitmap_words, groups;
     size_t smem;
     bool bits;  // mask or penalty tables needed
+    int mode;   // kernel variant: 0 rows of either kind, 1 window-mode rows only, 2 exact-selection rows only
 };
 
 // Raises the dynamic shared-memory limit of every kernel; once per device.
