@@ -164,7 +164,6 @@ int32_t fill_params(llm_cuda_sampler* s, const llm_cuda_sample_args* a, bool nee
     P->force_full = a->force_full_sort;
     P->device_errors = s->device_errors;
     P->phase_ns = s->phase_ns;
-    { const char* dm = getenv("LLM_CUDA_DEBUG_MODE"); P->debug_mode = dm ? (uint32_t)atoi(dm) : 0u; }
     return LLM_CUDA_OK;
 }
 

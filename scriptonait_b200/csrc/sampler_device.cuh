@@ -39,6 +39,19 @@ constexpr float WINDOW_STREAM = 17.5f;
 constexpr uint32_t ROW_NEEDS_FULL = 0x80000000u;
 
 
+// Barrier over the THREADS consumer threads of a CTA (named barrier 1). The streaming kernel
+// runs one extra warp that only issues bulk copies and never joins these barriers.
+__device__ __forceinline__ void cta_sync() { asm volatile("bar.sync 1, %0;" ::"n"(THREADS) : "memory"); }
+__device__ __forceinline__ int cta_sync_or(int pred) {
+    int r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\tsetp.ne.s32 p, %1, 0;\n\tbar.red.or.pred q, 1, %2, p;\n\tselp.s32 %0, 1, 0, q;\n\t}"
+        : "=r"(r)
+        : "r"(pred), "n"(THREADS)
+        : "memory");
+    return r;
+}
+
 struct RowCfg {
     float T, top_p, min_p, pen;
     uint32_t k_eff;     // rank cut: min(top_k, vocab), vocab when top_k == 0, 1 when greedy
@@ -217,7 +230,7 @@ __device__ __forceinline__ uint32_t compact_inplace(uint32_t n, Pred keep, Share
         S.newcount = 0u;
         S.minkey = 0xffffffffu;
     }
-    __syncthreads();
+    cta_sync();
     const unsigned lane = threadIdx.x & 31u;
     for (uint32_t base = 0; base < n; base += THREADS) {
         const uint32_t i = base + threadIdx.x;
@@ -229,7 +242,7 @@ __device__ __forceinline__ uint32_t compact_inplace(uint32_t n, Pred keep, Share
             id = cand_i[i];
             k = keep(q, id);
         }
-        __syncthreads();
+        cta_sync();
         const unsigned m = __ballot_sync(FULL_MASK, k);
         if (m) {
             const int leader = __ffs(m) - 1;
@@ -247,7 +260,7 @@ __device__ __forceinline__ uint32_t compact_inplace(uint32_t n, Pred keep, Share
             }
         }
     }
-    __syncthreads();
+    cta_sync();
     return S.newcount;
 }
 
@@ -264,7 +277,7 @@ __device__ __forceinline__ void radix_select(uint32_t n, uint32_t k, Shared& S, 
     uint32_t need = k;
     const unsigned lane = threadIdx.x & 31u;
     S.hist[0][threadIdx.x] = 0u;  // THREADS == 256 bins
-    __syncthreads();
+    cta_sync();
     const uint32_t n_up = (n + 31u) & ~31u;  // whole warps iterate together
     for (int p = 0; p < 8; ++p) {
         const int sh = 56 - 8 * p;
@@ -284,7 +297,7 @@ __device__ __forceinline__ void radix_select(uint32_t n, uint32_t k, Shared& S, 
             }
         }
         S.hist[(p + 1) & 1][threadIdx.x] = 0u;  // last read two barriers ago
-        __syncthreads();
+        cta_sync();
         // every warp scans the 256 bins: lane l owns bins [8l, 8l+8)
         uint32_t bins[8];
         uint32_t mine = 0u;
@@ -324,10 +337,10 @@ __device__ __forceinline__ void radix_select(uint32_t n, uint32_t k, Shared& S, 
         if (bucket == need || p == 7 || om == 0u) {
             shift = sh;
             thr = prefix;
-            __syncthreads();  // histograms are free again
+            cta_sync();  // histograms are free again
             return;
         }
-        __syncthreads();
+        cta_sync();
     }
 }
 
@@ -356,14 +369,14 @@ __device__ __forceinline__ void sort_candidates(uint32_t n, float* cand_q, uint3
             mine = composite(q, id);
             keys64[threadIdx.x] = mine;
         }
-        __syncthreads();
+        cta_sync();
         if (threadIdx.x < n) {
             uint32_t rank = 0u;
             for (uint32_t j = 0; j < n; ++j) rank += (keys64[j] > mine) ? 1u : 0u;  // keys are distinct
             cand_q[rank] = q;
             cand_i[rank] = id;
         }
-        __syncthreads();
+        cta_sync();
         return;
     }
     uint32_t m = 1u;
@@ -372,7 +385,7 @@ __device__ __forceinline__ void sort_candidates(uint32_t n, float* cand_q, uint3
         cand_q[i] = neg_inf();
         cand_i[i] = 0xffffffffu;
     }
-    __syncthreads();
+    cta_sync();
     for (uint32_t size = 2u; size <= m; size <<= 1) {
         for (uint32_t stride = size >> 1; stride > 0u; stride >>= 1) {
             for (uint32_t t = threadIdx.x; t < (m >> 1); t += THREADS) {
@@ -389,7 +402,7 @@ __device__ __forceinline__ void sort_candidates(uint32_t n, float* cand_q, uint3
                     cand_i[hi] = il;
                 }
             }
-            __syncthreads();
+            cta_sync();
         }
     }
 }
@@ -415,7 +428,7 @@ __device__ __forceinline__ void ordered_tail(const KParams& P, uint32_t b, const
         S.f_r = 0.f;
         S.kept_n = 0u;
     }
-    __syncthreads();
+    cta_sync();
     if (threadIdx.x == 0) {
         // :374 left-to-right f32 sum. Once the sum is >= 1 a term below 2^-24 is under
         // half an ulp and leaves it unchanged, and the terms only get smaller.
@@ -430,7 +443,7 @@ __device__ __forceinline__ void ordered_tail(const KParams& P, uint32_t b, const
         }
         S.f_sum = s;
     }
-    __syncthreads();
+    cta_sync();
     const float sum = S.f_sum;
     const bool degenerate = (sum <= 0.0f) || !(fabsf(sum) <= 3.402823466e38f);  // :375 (catches NaN and inf)
     if (degenerate) {
@@ -438,11 +451,11 @@ __device__ __forceinline__ void ordered_tail(const KParams& P, uint32_t b, const
             S.token = cand_i[0];
             S.out_flags = LLM_CUDA_ROW_DEGENERATE;
         }
-        __syncthreads();
+        cta_sync();
         return;
     }
     for (uint32_t i = threadIdx.x; i < n; i += THREADS) probs[i] = __fdiv_rn(probs[i], sum);  // :378-380
-    __syncthreads();
+    cta_sync();
     // :384-395 min-p: leading run with p >= min_p * p[0], never empty
     bool unknown_tail = false;  // kept set may reach past the window in a way the window cannot settle
     if (rc.min_p > 0.0f) {
@@ -455,12 +468,12 @@ __device__ __forceinline__ void ordered_tail(const KParams& P, uint32_t b, const
             }
         }
         if (first_fail < n) atomicMin(&S.keep, first_fail);
-        __syncthreads();
+        cta_sync();
         if (threadIdx.x == 0) {
             S.f_thr = thr;
             if (S.keep < 1u) S.keep = 1u;
         }
-        __syncthreads();
+        cta_sync();
         // every window entry passed and more entries follow: whether those pass is
         // only certain when the threshold is at least 2^-24 of the leader
         if (truncated && S.keep == n && rc.min_p < 5.9604644775390625e-08f) unknown_tail = true;
@@ -553,7 +566,7 @@ __device__ __forceinline__ void ordered_tail(const KParams& P, uint32_t b, const
         S.keep = keep;
         S.kept_n = tail_kept ? k_total : keep;
     }
-    __syncthreads();
+    cta_sync();
 }
 
 // Writes the row's results. `listed` = how many kept entries cand/probs hold.

@@ -91,6 +91,9 @@ __device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
 // One elected thread: `bytes` (multiple of 16) from 16-byte aligned global memory to
 // 16-byte aligned shared memory of this CTA.
 __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
@@ -146,6 +149,7 @@ __device__ __forceinline__ void push_full(const KParams& P, uint32_t b) {
     }
     const uint32_t pos = atomicAdd(P.full_count, 1u);
     P.full_list[pos] = b;
+#ifndef LLMC_NO_TAIL_LAUNCH
     if (pos == 0u && P.tail_launch) {
         // first row of this launch that needs the full ordering: queue the full-sort kernel behind
         // this grid (it starts when every CTA of this grid has finished, so the list is complete)
@@ -154,6 +158,7 @@ __device__ __forceinline__ void push_full(const KParams& P, uint32_t b) {
         full_sort_kernel<<<P.full_nslots, FULL_THREADS, (size_t)P.full_hash_slots * 8u, cudaStreamTailLaunch>>>(
             Q, reinterpret_cast<uint64_t*>(P.full_keys), P.full_vals, P.full_vpad, P.full_ticket);
     }
+#endif
 }
 
 // Streaming threshold of window mode for a given maximum (both in the post-temperature domain).
@@ -170,15 +175,16 @@ __device__ __forceinline__ float temper(float x, float T) { return (T == 1.0f) ?
 // and either the ordered tail (token out) or the candidate list out. `scratch`
 // is EPILOGUE_SCRATCH bytes of shared memory nothing else uses any more.
 __device__ void finish_row(const KParams& P, uint32_t b, const RowCfg& rc, uint32_t n, bool overflow, float qmax, Shared& S,
-                           float* cand_q, uint32_t* cand_i, unsigned char* scratch) {
+                           float* cand_q, uint32_t* cand_i, unsigned char* scratch, bool window_filtered = false) {
     uint64_t* keys64 = reinterpret_cast<uint64_t*>(scratch);                     // THREADS 64-bit words
     float* probs = reinterpret_cast<float*>(scratch + (size_t)THREADS * 8u);     // up to MAX_SORT floats
     if (!rc.windowed) {
         n = keep_top_k(n, rc.k_eff, S, cand_q, cand_i);
     } else if (!overflow) {
         // exact window: exactly the terms the reference's f32 sums can see
-        n = compact_inplace(
-            n, [=](float q, uint32_t) { return (__fsub_rn(q, qmax) >= WINDOW_EXACT) || (q == qmax); }, S, cand_q, cand_i);
+        if (!window_filtered)
+            n = compact_inplace(
+                n, [=](float q, uint32_t) { return (__fsub_rn(q, qmax) >= WINDOW_EXACT) || (q == qmax); }, S, cand_q, cand_i);
         uint32_t m = 1u;  // the sort pads to a power of two inside the buffer
         while (m < n) m <<= 1;
         if (m > P.ccap || n > MAX_SORT) overflow = true;
@@ -215,7 +221,7 @@ __device__ void finish_row(const KParams& P, uint32_t b, const RowCfg& rc, uint3
             S.kept_n = 0u;
             S.f_sum = S.f_total = S.f_u = S.f_thr = S.f_r = 0.f;
         }
-        __syncthreads();
+        cta_sync();
         write_row_outputs(P, b, 0u, S, n_use ? cand_q[0] : 0.f, cand_i, probs, 0u);
         return;
     }
@@ -239,13 +245,13 @@ __device__ uint32_t merge_lists(const KParams& P, uint32_t b, const RowCfg& rc, 
         S.max_key = 0x007fffffu;
         S.keep = 0u;  // overflow marker seen
     }
-    __syncthreads();
+    cta_sync();
     for (uint32_t s = threadIdx.x; s < nsh; s += THREADS) {
         const size_t at = (size_t)s * P.sc_rows + b;
         if (P.sc_maxkey) atomicMax(&S.max_key, __ldcg(&P.sc_maxkey[at]));
         if (__ldcg(&P.sc_cnt[at]) == 0xffffffffu) S.keep = 1u;
     }
-    __syncthreads();
+    cta_sync();
     overflow = S.keep != 0u;
     qmax = okey_to_float(S.max_key);
     const float tq = window_stream_bound(qmax);
@@ -270,9 +276,9 @@ __device__ uint32_t merge_lists(const KParams& P, uint32_t b, const RowCfg& rc, 
             cand_q[n + i] = q;
             cand_i[n + i] = __ldcg(&si[i]);
         }
-        __syncthreads();
+        cta_sync();
         if (threadIdx.x == 0) S.count = n + cnt;
-        __syncthreads();
+        cta_sync();
     }
     return S.count;
 }
@@ -284,15 +290,17 @@ __device__ uint32_t merge_lists(const KParams& P, uint32_t b, const RowCfg& rc, 
 // flight per CTA whatever the occupancy.
 // MODE trims the code to what a launch can need (the hot loop must stay small enough for the
 // instruction cache): 0 = rows of either kind, 1 = every row runs in window mode, 2 = no row does.
+constexpr int STREAM_THREADS = THREADS + 32;  // THREADS consumers + one warp that only issues the bulk copies
 template <typename ElemT, bool BITS, int MODE>
-__global__ void __launch_bounds__(THREADS, 3) stream_select_kernel(const __grid_constant__ KParams P) {
+__global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const __grid_constant__ KParams P) {
     constexpr int VEC = Traits<ElemT>::VEC;
     constexpr uint32_t VPS = STAGE_BYTES / 16u;      // 16-byte vectors per stage
     constexpr int U = VPS / THREADS;                 // vectors per thread per stage
     static_assert(VPS % THREADS == 0, "stage geometry");
     extern __shared__ __align__(128) unsigned char dyn[];
     __shared__ Shared S;
-    __shared__ __align__(8) uint64_t full_bar[RING_STAGES];
+    __shared__ __align__(8) uint64_t full_bar[RING_STAGES];   // a stage's bytes have landed
+    __shared__ __align__(8) uint64_t empty_bar[RING_STAGES];  // all consumer warps are done with a stage
     __shared__ uint16_t hit_list[WARPS][U * 32];  // per warp: stage-relative vector numbers that hold a passing value
     unsigned char* ring = dyn;
     float* cand_q = reinterpret_cast<float*>(dyn + RING_STAGES * STAGE_BYTES);
@@ -313,10 +321,13 @@ __global__ void __launch_bounds__(THREADS, 3) stream_select_kernel(const __grid_
         S.error = 0u;
         S.last = 0u;
 #pragma unroll
-        for (int i = 0; i < RING_STAGES; ++i) mbar_init(&full_bar[i], 1u);
+        for (int i = 0; i < RING_STAGES; ++i) {
+            mbar_init(&full_bar[i], 1u);
+            mbar_init(&empty_bar[i], (uint32_t)WARPS);
+        }
         mbar_fence_init();
     }
-    __syncthreads();
+    __syncthreads();  // the one barrier all STREAM_THREADS threads share
     RowCfg rc = S.rc;
     if (MODE == 1) rc.windowed = 1u;  // lets the compiler drop the exact-selection code
     if (MODE == 2) rc.windowed = 0u;  // ... or the window code
@@ -364,9 +375,20 @@ __global__ void __launch_bounds__(THREADS, 3) stream_select_kernel(const __grid_
         mbar_expect_tx(bar, nv * 16u);
         bulk_load(ring + (size_t)(tt % RING_STAGES) * STAGE_BYTES, vbase + (size_t)first * 16u, nv * 16u, bar);
     };
-    if (tid == 0) {
-        const uint32_t pre = min(vtiles, (uint32_t)RING_STAGES);
-        for (uint32_t tt = 0; tt < pre; ++tt) issue(tt);
+    if (warp == (unsigned)WARPS) {
+        // the producer warp: keeps the ring full, refilling a stage as soon as every consumer warp
+        // has released it; it takes no part in the consumers' barriers and leaves when all is issued
+        if (lane == 0) {
+            for (uint32_t tt = 0; tt < vtiles; ++tt) {
+                if (tt >= (uint32_t)RING_STAGES &&
+                    !mbar_wait_bounded(&empty_bar[tt % RING_STAGES], ((tt / RING_STAGES) - 1u) & 1u)) {
+                    atomicOr(&S.error, 4u);  // consumers will time out on the stage as well and report it
+                    break;
+                }
+                issue(tt);
+            }
+        }
+        return;
     }
 
     // ---- mask / penalty side tables
@@ -376,7 +398,7 @@ __global__ void __launch_bounds__(THREADS, 3) stream_select_kernel(const __grid_
             hkeys[i] = EMPTY_KEY;
             hcnt[i] = 0u;
         }
-        __syncthreads();
+        cta_sync();
         if (rc.has_pen) {
             const uint32_t* hist = P.history + (size_t)b * P.hist_stride;
             for (uint32_t j = tid; j < rc.hlen; j += THREADS) {
@@ -411,7 +433,7 @@ __global__ void __launch_bounds__(THREADS, 3) stream_select_kernel(const __grid_
                 }
             }
         }
-        __syncthreads();
+        cta_sync();
     }
 
     uint32_t end = 0u;  // highest candidate slot handed out, as seen by this warp
@@ -469,23 +491,13 @@ __global__ void __launch_bounds__(THREADS, 3) stream_select_kernel(const __grid_
     //      (packed bf16 arithmetic for bf16 rows) and notes the vectors that reach the threshold in
     //      its warp's list, (B) the warp examines its listed vectors 32/VEC at a time.
     bool wait_failed = false;
-    long long acc[6] = {0, 0, 0, 0, 0, 0};
-    long long c_a = clock64(), c_b;
-#define TICK(k)                      \
-    do {                             \
-        c_b = clock64();             \
-        acc[k] += c_b - c_a;         \
-        c_a = c_b;                   \
-    } while (0)
     for (uint32_t tt = 0; tt <= vtiles; ++tt) {
         // iteration tt == vtiles only settles the buffer
         const bool max_sweep = rc.windowed != 0u;  // window-mode rows only take maxima here
         const uint32_t t = tt;
         if (tt < vtiles) {
             const uint32_t stage = tt % RING_STAGES;
-            TICK(5);
             if (!mbar_wait_bounded(&full_bar[stage], (tt / RING_STAGES) & 1u)) wait_failed = true;
-            TICK(0);
             const uint4* sv = reinterpret_cast<const uint4*>(ring + (size_t)stage * STAGE_BYTES);
             float vm[U];
 #pragma unroll
@@ -521,12 +533,36 @@ __global__ void __launch_bounds__(THREADS, 3) stream_select_kernel(const __grid_
                 }
             }
             if (max_sweep) {
+                // the running maximum gives a running threshold; each group of 32 vectors (one warp
+                // step) records which of its vectors reach it - a superset of those that will reach
+                // the final threshold, since the maximum only rises
+                const uint32_t wk = __reduce_max_sync(FULL_MASK, okey(tmax));
+                if (tt == 0) {
+                    if (lane == 0) atomicMax(&S.max_key, wk);
+                    cta_sync();
+                    if (tid == 0) {
+                        const float qmax0 = temper(okey_to_float(S.max_key), T);
+                        S.tau_key = raw_threshold_key(window_stream_bound(qmax0), T);
+                    }
+                    cta_sync();
+                } else if (lane == 0 && wk > vol_load(&S.max_key)) {
+                    // the maximum rose: this warp tightens the shared threshold itself (monotone, so
+                    // warps that still read the old value only keep a superset)
+                    const uint32_t prev = atomicMax(&S.max_key, wk);
+                    const float qmax1 = temper(okey_to_float(max(prev, wk)), T);
+                    atomicMax(&S.tau_key, raw_threshold_key(window_stream_bound(qmax1), T));
+                }
+                const float tau_run = okey_to_float(vol_load(&S.tau_key));
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
                     // vm[u] is the lane's maximum over unflagged elements when BITS (recomputed above)
-                    const uint32_t gk = __reduce_max_sync(FULL_MASK, (vm[u] == vm[u]) ? okey(vm[u]) : LOWEST);
-                    if (lane == 0) grp_max[(t * U + u) * WARPS + warp] = gk;
+                    const unsigned gm = __ballot_sync(FULL_MASK, vm[u] >= tau_run);
+                    if (lane == 0) grp_max[(t * U + u) * WARPS + warp] = gm;
                 }
+                // window rows run the sweep without CTA barriers: the warp releases the stage and goes on
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty_bar[stage]);
+                continue;
             } else {
                 if (tt == 0) {
                     // (top-k rows) bootstrap the threshold from the first stage, before anything of it is appended
@@ -545,14 +581,14 @@ __global__ void __launch_bounds__(THREADS, 3) stream_select_kernel(const __grid_
                             rank += (other > mykey || (other == mykey && src < lane)) ? 1u : 0u;
                         }
                         if (rank == r - 1u) S.wkth[warp] = mykey;
-                        __syncthreads();
+                        cta_sync();
                         if (tid == 0) {
                             uint32_t lo = S.wkth[0];
 #pragma unroll
                             for (int w = 1; w < WARPS; ++w) lo = min(lo, S.wkth[w]);
                             S.tau_key = max(lo, LOWEST);
                         }
-                        __syncthreads();
+                        cta_sync();
                     }
                 }
                 const float tau = okey_to_float(vol_load(&S.tau_key));
@@ -565,7 +601,6 @@ __global__ void __launch_bounds__(THREADS, 3) stream_select_kernel(const __grid_
                     if (hit) hit_list[warp][wcnt + (uint32_t)__popc(pm & ((1u << lane) - 1u))] = (uint16_t)(u * THREADS + tid);
                     wcnt += (uint32_t)__popc(pm);
                 }
-                TICK(1);
                 if (wcnt) {
                     // ... examined by the warp itself, 32/VEC vectors at a time: lane l looks at element
                     // l % VEC of list entry l / VEC, so no lane runs a long divergent path and warps
@@ -590,7 +625,8 @@ __global__ void __launch_bounds__(THREADS, 3) stream_select_kernel(const __grid_
                     }
                     __syncwarp();
                 }
-                TICK(3);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty_bar[stage]);  // this warp is done with the stage
             }
         }
         if (rc.windowed && tt == vtiles) {
@@ -599,14 +635,10 @@ __global__ void __launch_bounds__(THREADS, 3) stream_select_kernel(const __grid_
             if (lane == 0) atomicMax(&S.max_key, wk);
         }
         end = __reduce_max_sync(FULL_MASK, end);
-        TICK(3);
-        const int over = __syncthreads_or(end > P.limit ? 1 : 0);
-        TICK(4);
-        // every thread is done with this stage: refill it
-        if (tid == 0 && tt + RING_STAGES < vtiles) issue(tt + RING_STAGES);
+        const int over = cta_sync_or(end > P.limit ? 1 : 0);
         if (over) {
             uint32_t n = min(S.count, P.ccap);
-            __syncthreads();
+            cta_sync();
             if (!rc.windowed) {
                 if (n > rc.k_eff) {
                     n = keep_top_k(n, rc.k_eff, S, cand_q, cand_i);
@@ -630,98 +662,121 @@ __global__ void __launch_bounds__(THREADS, 3) stream_select_kernel(const __grid_
                     }
                 }
             }
-            __syncthreads();
+            cta_sync();
             end = S.count;
         }
     }
-    __syncthreads();
+    cta_sync();
+    bool window_filtered = false;  // the candidates already are exactly the window
+    PHASE(7);
     if (rc.windowed) {
-        // the row's maximum fixes the threshold; every warp then revisits its share of the groups
-        // that can hold a value inside the window
+        // the row's maximum fixes the threshold; the vectors noted during the sweep are read again
+        // (from L2) and their elements tested against the exact window
+        const uint32_t unfiltered = S.count;  // leading / trailing elements and penalised ids, appended before the sweep
         if (tid == 0) {
-            const float qmax0 = temper(okey_to_float(S.max_key), T);
-            S.tau_key = raw_threshold_key(window_stream_bound(qmax0), T);
+            S.keep = 0u;
+            S.last = 0u;
         }
-        __syncthreads();
-        const uint32_t tau_key = S.tau_key;
-        const float tau = okey_to_float(tau_key);
+        cta_sync();
+        // every thread derives the final threshold from the row's maximum itself
+        const float qmaxf = temper(okey_to_float(S.max_key), T);
+        const float tau = okey_to_float(raw_threshold_key(window_stream_bound(qmaxf), T));
         const uint32_t ngroups = (nvi + 31u) / 32u;
         const uint4* gv = reinterpret_cast<const uint4*>(vbase);
-        // list the qualifying groups (the warps' vector lists are free now and serve as storage)
-        uint16_t* glist = &hit_list[0][0];
-        constexpr uint32_t GLIST_CAP = WARPS * U * 32u;
-        const bool listable = ngroups <= 65536u;
-        if (tid == 0) S.keep = 0u;
-        __syncthreads();
-        if (listable) {
-            for (uint32_t g = tid; g < ngroups; g += THREADS) {
-                if (grp_max[g] >= tau_key) {
-                    const uint32_t pos = atomicAdd(&S.keep, 1u);
-                    if (pos < GLIST_CAP) glist[pos] = (uint16_t)g;
-                }
+        uint32_t* vlist = reinterpret_cast<uint32_t*>(ring);  // the ring is idle now
+        constexpr uint32_t VLIST_CAP = RING_STAGES * STAGE_BYTES / 4u;
+        // list the noted vectors: one shared-memory atomic per warp step (prefix sums inside the warp)
+        for (uint32_t g0 = 0; g0 < ngroups; g0 += THREADS) {
+            const uint32_t g = g0 + tid;
+            unsigned m = g < ngroups ? grp_max[g] : 0u;
+            const uint32_t c = (uint32_t)__popc(m);
+            uint32_t incl = c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t y = __shfl_up_sync(FULL_MASK, incl, o);
+                if (lane >= (unsigned)o) incl += y;
+            }
+            const uint32_t total = __shfl_sync(FULL_MASK, incl, 31);
+            if (total == 0u) continue;
+            uint32_t base = 0u;
+            if (lane == 31) base = atomicAdd(&S.keep, total);
+            base = __shfl_sync(FULL_MASK, base, 31);
+            uint32_t at = base + incl - c;
+            while (m) {
+                const uint32_t bit = (uint32_t)__ffs(m) - 1u;
+                m &= m - 1u;
+                if (at < VLIST_CAP) vlist[at] = g * 32u + bit;
+                ++at;
             }
         }
-        __syncthreads();
+        cta_sync();
         const uint32_t nq = S.keep;
-        auto examine = [&](const uint4& raw, uint32_t v) {
+        // read a noted vector again (L2) and append the elements inside the exact window; the
+        // appends of a warp step share one atomic
+        auto examine = [&](bool have, uint32_t v) {
             float x[VEC];
-            unpack<ElemT>(raw, x);
-            uint32_t nib = 0u;
+            uint32_t em = 0u;
             const uint32_t rel0 = head + v * VEC;
-            if (BITS) {
-                const uint32_t j2 = rel0 + lead;
-                nib = (bitmap[j2 >> 5] >> (j2 & 31u)) & ((1u << VEC) - 1u);  // flagged: handled before the stream
+            if (have) {
+                unpack<ElemT>(__ldg(gv + v), x);
+                uint32_t nib = 0u;
+                if (BITS) {
+                    const uint32_t j2 = rel0 + lead;
+                    nib = (bitmap[j2 >> 5] >> (j2 & 31u)) & ((1u << VEC) - 1u);  // flagged: handled before the stream
+                }
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) {
+                    if (x[e] >= tau && !((nib >> e) & 1u)) {
+                        x[e] = temper(x[e], T);
+                        if ((__fsub_rn(x[e], qmaxf) >= WINDOW_EXACT) || (x[e] == qmaxf)) em |= 1u << e;  // exactly the terms the reference's sums can see
+                    }
+                }
             }
+            const uint32_t c = (uint32_t)__popc(em);
+            uint32_t incl = c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t y = __shfl_up_sync(FULL_MASK, incl, o);
+                if (lane >= (unsigned)o) incl += y;
+            }
+            const uint32_t total = __shfl_sync(FULL_MASK, incl, 31);
+            if (total == 0u) return;
+            uint32_t base = 0u;
+            if (lane == 31) base = atomicAdd(&S.count, total);
+            base = __shfl_sync(FULL_MASK, base, 31);
+            uint32_t slot = base + incl - c;
 #pragma unroll
             for (int e = 0; e < VEC; ++e) {
-                if (x[e] >= tau && !((nib >> e) & 1u)) {
-                    const uint32_t slot = atomicAdd(&S.count, 1u);
+                if ((em >> e) & 1u) {
                     if (slot < P.ccap) {
-                        cand_q[slot] = temper(x[e], T);
+                        cand_q[slot] = x[e];
                         cand_i[slot] = gid0 + rel0 + e;
                     } else {
                         S.error = 1u;
                     }
+                    ++slot;
                 }
             }
         };
-        if (listable && nq <= GLIST_CAP) {
-            // four groups per warp step: the four L2 reads are in flight together
-            for (uint32_t i0 = warp * 4u; i0 < nq; i0 += WARPS * 4u) {
-                uint4 raw[4];
-                uint32_t vv[4];
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    vv[k] = 0xffffffffu;
-                    if (i0 + k < nq) {
-                        const uint32_t v = (uint32_t)glist[i0 + k] * 32u + lane;
-                        if (v < nvi) {
-                            vv[k] = v;
-                            raw[k] = __ldg(gv + v);
-                        }
-                    }
-                }
-#pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    if (vv[k] != 0xffffffffu) examine(raw[k], vv[k]);
+        if (nq <= VLIST_CAP) {
+            for (uint32_t i0 = 0; i0 < nq; i0 += THREADS) {
+                const uint32_t i = i0 + tid;
+                const uint32_t v = i < nq ? vlist[i] : 0xffffffffu;
+                examine(v < nvi, v);
             }
         } else {
             for (uint32_t g = warp; g < ngroups; g += WARPS) {
-                if (grp_max[g] < tau_key) continue;  // same word for the whole warp
+                const unsigned m = grp_max[g];  // same word for the whole warp
                 const uint32_t v = g * 32u + lane;
-                if (v < nvi) examine(__ldg(gv + v), v);
+                examine(((m >> lane) & 1u) && v < nvi, v);
             }
         }
-        __syncthreads();
+        cta_sync();
+        window_filtered = (unfiltered == 0u) && P.split == 1u;
     }
     PHASE(2);
-    if (P.phase_ns && (tid == 0 || tid == 255)) {
-        unsigned long long* o = P.phase_ns + ((size_t)gridDim.x * gridDim.y + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 2u + (tid ? 1u : 0u)) * 8u;
-        for (int k = 0; k < 6; ++k) o[k] = acc[k];
-        o[6] = vtiles; o[7] = S.count;
-    }
     if (wait_failed) atomicOr(&S.error, 4u);
-    __syncthreads();
+    cta_sync();
 
     uint32_t n = min(S.count, P.ccap);
     bool overflow = (S.error & 3u) != 0u;  // window too large, or an append fell off the buffer
@@ -732,7 +787,7 @@ __global__ void __launch_bounds__(THREADS, 3) stream_select_kernel(const __grid_
     }
 
     if (P.split == 1u) {
-        finish_row(P, b, rc, n, overflow, qmax, S, cand_q, cand_i, ring);
+        finish_row(P, b, rc, n, overflow, qmax, S, cand_q, cand_i, ring, window_filtered);
         return;
     }
 
@@ -761,12 +816,12 @@ __global__ void __launch_bounds__(THREADS, 3) stream_select_kernel(const __grid_
         }
     }
     __threadfence();
-    __syncthreads();
+    cta_sync();
     if (tid == 0) {
         const uint32_t ticket = atomicAdd(&P.sc_ticket[b], 1u);
         S.last = (ticket == P.split - 1u) ? 1u : 0u;
     }
-    __syncthreads();
+    cta_sync();
     if (!S.last) return;
     if (tid == 0) P.sc_ticket[b] = 0u;  // re-armed for the next launch on this stream
     __threadfence();
@@ -786,7 +841,7 @@ __global__ void __launch_bounds__(THREADS) merge_draw_kernel(const __grid_consta
         resolve_row(P, b, S.rc);
         S.error = 0u;
     }
-    __syncthreads();
+    cta_sync();
     const RowCfg rc = S.rc;
     if (rc.invalid) {
         if (threadIdx.x == 0) {
@@ -1194,7 +1249,7 @@ template <typename ElemT, bool BITS, int MODE>
 static cudaError_t launch_stream_t(const KParams& P, const LaunchPlan& plan, cudaStream_t stream) {
     auto kern = stream_select_kernel<ElemT, BITS, MODE>;
     dim3 grid(plan.split, P.batch, 1);
-    kern<<<grid, THREADS, plan.smem, stream>>>(P);
+    kern<<<grid, STREAM_THREADS, plan.smem, stream>>>(P);
     return cudaGetLastError();
 }
 

@@ -64,7 +64,6 @@ struct KParams {
     uint32_t tail_launch;           // 1: the streaming kernel launches the full-sort kernel itself when a row needs it
     uint32_t* device_errors;        // bit 0: a bulk copy did not complete within the wait limit
     unsigned long long* phase_ns;   // optional [CTAs][8] phase timestamps (development aid), or NULL
-    uint32_t debug_mode;            // development aid: 1 = skip pass B, 2 = skip pass A and B, 3 = stream only then exit
 };
 
 struct DeviceInfo {
