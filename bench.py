@@ -167,11 +167,21 @@ def run_ours(args, rank, world, local_rank):
     dev_logits = [torch.from_numpy(b.logits.view(np.int16)).to(dev).view(torch.bfloat16) for b in batches]
     seeds = torch.from_numpy(w0.seeds.view(np.int64)).to(dev)
     tokens = torch.empty(BATCH, dtype=torch.int32, device=dev)
+    tokens_per_buffer = [torch.empty(BATCH, dtype=torch.int32, device=dev) for _ in range(N_BUFFERS)]
     params = w0.params()
     alg_bytes = w0.algorithmic_bytes()
 
     # one marshalled call per buffer: a step is then a single C-ABI call (as a decode loop over fixed buffers issues it)
-    calls = [sampler.sample_batch(lg, seeds=seeds, out_tokens=tokens, prepare_only=True, **params) for lg in dev_logits]
+    # Consecutive steps are independent batches (own logits, own token output), so each launch may
+    # begin streaming its logits while the previous one is still in its ordering / draw phase
+    # (overlap_previous: programmatic dependent launch; every write still follows stream order).
+    # --strict-order turns that off; the strict figure is measured and reported beside it either way.
+    def prepared(overlap):
+        return [sampler.sample_batch(lg, seeds=seeds, out_tokens=tk, prepare_only=True, overlap_previous=overlap, **params)
+                for lg, tk in zip(dev_logits, tokens_per_buffer)]
+
+    calls_strict = prepared(False)
+    calls = calls_strict if args.strict_order else prepared(True)
 
     def step(i):
         calls[i % N_BUFFERS].launch()
@@ -200,12 +210,16 @@ def run_ours(args, rank, world, local_rank):
 
     # ---- timed regions: exactly K steps each, CUDA events on the launching stream, max over ranks;
     #      repeated until the GPU has been under load for about a second so the clock samples mean something
-    def timed_region():
+    def timed_region(which=None):
         sync_all()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for i in range(args.steps):
-            step(i)
+        if which is None:
+            for i in range(args.steps):
+                step(i)
+        else:
+            for i in range(args.steps):
+                which[i % N_BUFFERS].launch()
         e1.record()
         sync_all()
         ms = e0.elapsed_time(e1)
@@ -223,6 +237,15 @@ def run_ours(args, rank, world, local_rank):
     ms_region = statistics.median(regions)
     ms_per_step = ms_region / args.steps
     value = world * BATCH / (ms_per_step * 1e-3)
+    overlapped_tokens = [t.clone() for t in tokens_per_buffer]  # what the overlapped launches left, per buffer
+    # the same steps in strict stream order (no launch overlaps its predecessor), for comparison
+    strict_regions = [timed_region(calls_strict) for _ in range(min(len(regions), 20))]
+    ms_per_step_strict = statistics.median(strict_regions) / args.steps
+    # every buffer's tokens from the overlapped launches must equal those of a strict-order launch (untimed)
+    for c in calls_strict:
+        c.launch()
+    torch.cuda.synchronize()
+    overlap_same = all(bool(torch.equal(a, b)) for a, b in zip(overlapped_tokens, tokens_per_buffer))
 
     # ---- end to end: host logits (pinned) -> device, sample, token ids -> host, every step
     host_logits = [torch.from_numpy(b.logits.view(np.int16)).pin_memory() for b in batches[:2]]
@@ -280,6 +303,11 @@ def run_ours(args, rank, world, local_rank):
                        "l2": f"inputs rotate over {N_BUFFERS} distinct {alg_bytes / 1e6:.1f} MB batches "
                              f"({N_BUFFERS * alg_bytes / 1e6:.0f} MB > 126 MB L2)",
                        "ctas_per_row": split, "timed_regions": len(regions),
+                       "step_overlap": "strict stream order" if args.strict_order else
+                                       "each launch may start streaming while the previous step's launch finishes "
+                                       "(programmatic dependent launch); independent batches with their own outputs",
+                       "ms_per_step_strict_order": ms_per_step_strict,
+                       "overlapped_tokens_equal_strict_order": overlap_same,
                        "region_ms_min_median_max": [min(regions), ms_region, max(regions)]},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS, "peak_source": peak_src,
@@ -306,6 +334,8 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--strict-order", action="store_true",
+                    help="launch every step in strict stream order (no overlap with the previous step's launch)")
     ap.add_argument("--regions", type=int, default=0,
                     help="timed regions of K steps to run (0 = as many as keep the GPU loaded for ~1.5 s); "
                          "profiling runs use a small number")

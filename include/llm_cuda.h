@@ -88,7 +88,10 @@ typedef struct llm_cuda_sample_args {
     float top_p;
     float min_p;
     float repetition_penalty;
-    uint32_t reserved0;
+    uint32_t overlap_previous;  /* nonzero: this launch may start reading its inputs while the previous
+                                 * llm_cuda_sample_batch launch on the same stream is still finishing (its
+                                 * writes still come after that launch has completed). Only for a call whose
+                                 * input arrays are not outputs of that previous call; 0 = strict stream order */
     const float* temperature_rows;        /* device [batch] or NULL */
     const uint32_t* top_k_rows;           /* device [batch] or NULL */
     const float* top_p_rows;              /* device [batch] or NULL */

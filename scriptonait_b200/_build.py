@@ -22,7 +22,6 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-fmad=false", "-prec-div=true", "-prec-sqrt=true", "-ftz=false",
     "-Xcompiler", "-fPIC", "-shared", "-cudart", "shared",
-    "-rdc=true", "-lcudadevrt",  # the streaming kernel launches the full-sort kernel from the device (tail launch)
 ]
 
 

@@ -54,7 +54,7 @@ class SampleArgs(C.Structure):
         ("struct_size", C.c_uint32), ("logits_dtype", C.c_uint32), ("logits", C.c_void_p),
         ("batch", C.c_uint32), ("vocab", C.c_uint32), ("row_stride_elems", C.c_uint64),
         ("temperature", C.c_float), ("top_k", C.c_uint32), ("top_p", C.c_float), ("min_p", C.c_float),
-        ("repetition_penalty", C.c_float), ("reserved0", C.c_uint32),
+        ("repetition_penalty", C.c_float), ("overlap_previous", C.c_uint32),
         ("temperature_rows", C.c_void_p), ("top_k_rows", C.c_void_p), ("top_p_rows", C.c_void_p),
         ("min_p_rows", C.c_void_p), ("repetition_penalty_rows", C.c_void_p),
         ("history", C.c_void_p), ("history_stride", C.c_uint32), ("history_len", C.c_uint32),

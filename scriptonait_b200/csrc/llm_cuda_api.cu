@@ -44,19 +44,16 @@ struct llm_cuda_sampler {
     uint32_t* sc_ticket = nullptr;
     uint32_t sc_lists = 0;  // capacity of sc_cnt / sc_maxkey
     // full-sort scratch
-    uint32_t* full_list = nullptr;
-    uint32_t* full_count = nullptr;
-    uint32_t* full_ticket = nullptr;
+    uint32_t* full_slots = nullptr;
     uint64_t* full_keys = nullptr;
     float* full_vals = nullptr;
-    uint32_t vpad = 0, nslots = 0, hash_slots = 0;
+    uint32_t vpad = 0, nslots = 0;
     uint32_t* device_errors = nullptr;  // bit 0: a bulk copy timed out in some launch
     unsigned long long* phase_ns = nullptr;  // development aid: per-CTA phase timestamps, set by llm_cuda_debug_phase_buffer
     // staging for the host-buffer entry points (grown on demand)
     unsigned char* arena = nullptr;
     size_t arena_bytes = 0;
     uint32_t last_kernels = 0, last_split = 0;
-    bool host_full_sort = false;  // launch the full-sort kernel from the host after every call that may need it
     char err[512] = "";
 };
 
@@ -82,9 +79,7 @@ void free_all(llm_cuda_sampler* s) {
     cudaFree(s->sc_cnt);
     cudaFree(s->sc_maxkey);
     cudaFree(s->sc_ticket);
-    cudaFree(s->full_list);
-    cudaFree(s->full_count);
-    cudaFree(s->full_ticket);
+    cudaFree(s->full_slots);
     cudaFree(s->full_keys);
     cudaFree(s->full_vals);
     cudaFree(s->device_errors);
@@ -159,8 +154,6 @@ int32_t fill_params(llm_cuda_sampler* s, const llm_cuda_sample_args* a, bool nee
     P->row_stats = a->row_stats;
     P->col_offset = a->column_offset;
     P->vocab_global = a->vocab_global ? a->vocab_global : a->vocab;
-    P->full_list = s->full_list;
-    P->full_count = s->full_count;
     P->force_full = a->force_full_sort;
     P->device_errors = s->device_errors;
     P->phase_ns = s->phase_ns;
@@ -204,33 +197,15 @@ int32_t run_select(llm_cuda_sampler* s, const llm_cuda_sample_args* a, KParams& 
     s->last_kernels = 0;
     s->last_split = plan.split;
     if (P.batch == 0) return LLM_CUDA_OK;
-    // rows the window cannot decide are rare: the full-sort kernel is launched from the device, by
-    // the first CTA that needs it, instead of from here on every call (LLM_CUDA_HOST_FULL_SORT=1
-    // restores the host-side launch)
+    // rows the stream cannot decide are ordered in full by their own CTA, in one of these slots
     P.full_keys = reinterpret_cast<unsigned long long*>(s->full_keys);
     P.full_vals = s->full_vals;
-    P.full_ticket = s->full_ticket;
+    P.full_slots = s->full_slots;
     P.full_vpad = s->vpad;
     P.full_nslots = s->nslots;
-    P.full_hash_slots = s->hash_slots;
-    P.tail_launch = (s->host_full_sort || lists_out) ? 0u : 1u;
-    CUDA_TRY(s, launch_stream_select(P, plan, stream));
+    (void)lists_out;
+    CUDA_TRY(s, launch_stream_select(P, plan, stream, a->overlap_previous != 0u));
     s->last_kernels++;
-    bool may_need_full = false;
-    if (!lists_out) {
-        if (a->force_full_sort) {
-            may_need_full = true;
-        } else if (!k_known) {
-            may_need_full = true;  // a row may ask for top_k 0 or beyond the exact-selection capacity
-        } else if (!scalar_greedy(a)) {
-            const uint32_t k_eff = (k_hint == 0u || k_hint >= P.vocab_global) ? P.vocab_global : k_hint;
-            may_need_full = k_eff > plan.kcap;
-        }
-    }
-    if (may_need_full && !P.tail_launch) {
-        CUDA_TRY(s, launch_full_sort(P, s->hash_slots, s->nslots, s->full_keys, s->full_vals, s->vpad, s->full_ticket, stream));
-        s->last_kernels++;
-    }
     return LLM_CUDA_OK;
 }
 
@@ -288,7 +263,6 @@ int32_t llm_cuda_sampler_create(int32_t device, uint32_t max_batch, uint32_t max
     s->max_vocab = max_vocab;
     s->max_history = max_history;
     s->max_top_k = max_top_k ? max_top_k : 1u;
-    { const char* hf = getenv("LLM_CUDA_HOST_FULL_SORT"); s->host_full_sort = hf && hf[0] == '1'; }
     s->dev.sm_count = (uint32_t)prop.multiProcessorCount;
     s->dev.max_dyn_smem = (size_t)prop.sharedMemPerBlockOptin - 4096u;  // room for the kernels' static shared memory
     auto bail = [&](const char* what, cudaError_t ce) {
@@ -301,28 +275,20 @@ int32_t llm_cuda_sampler_create(int32_t device, uint32_t max_batch, uint32_t max
     if ((e = configure_kernels(s->dev.max_dyn_smem)) != cudaSuccess) return bail("cudaFuncSetAttribute", e);
     s->sc_lists = max_batch > 4096u ? max_batch : 4096u;
     s->vpad = pow2_ceil_u32(max_vocab);
-    s->nslots = s->dev.sm_count < 64u ? s->dev.sm_count : 64u;
+    // one slot per CTA that can be resident at a time would never make a row wait; two per SM is close
+    // to that and rows that need the full ordering are rare
+    s->nslots = 2u * s->dev.sm_count;
     if (s->nslots > max_batch) s->nslots = max_batch;
-    s->hash_slots = pow2_ceil_u32(2u * (max_history ? max_history : 1u));
-    if (s->hash_slots < 64u) s->hash_slots = 64u;
-    if ((size_t)s->hash_slots * 8u > s->dev.max_dyn_smem / 2u) {
-        fail(nullptr, LLM_CUDA_ERR_CAPACITY, "max_history %u too large for the shared-memory history table", max_history);
-        delete s;
-        return LLM_CUDA_ERR_CAPACITY;
-    }
     if ((e = cudaMalloc(&s->sc_q, kScratchEntries * 4u)) != cudaSuccess) return bail("cudaMalloc", e);
     if ((e = cudaMalloc(&s->sc_i, kScratchEntries * 4u)) != cudaSuccess) return bail("cudaMalloc", e);
     if ((e = cudaMalloc(&s->sc_cnt, (size_t)s->sc_lists * 4u)) != cudaSuccess) return bail("cudaMalloc", e);
     if ((e = cudaMalloc(&s->sc_maxkey, (size_t)s->sc_lists * 4u)) != cudaSuccess) return bail("cudaMalloc", e);
     if ((e = cudaMalloc(&s->sc_ticket, (size_t)max_batch * 4u)) != cudaSuccess) return bail("cudaMalloc", e);
-    if ((e = cudaMalloc(&s->full_list, (size_t)max_batch * 4u)) != cudaSuccess) return bail("cudaMalloc", e);
-    if ((e = cudaMalloc(&s->full_count, 4u)) != cudaSuccess) return bail("cudaMalloc", e);
-    if ((e = cudaMalloc(&s->full_ticket, 4u)) != cudaSuccess) return bail("cudaMalloc", e);
+    if ((e = cudaMalloc(&s->full_slots, (size_t)s->nslots * 4u)) != cudaSuccess) return bail("cudaMalloc", e);
     if ((e = cudaMalloc(&s->full_keys, (size_t)s->nslots * s->vpad * 8u)) != cudaSuccess) return bail("cudaMalloc", e);
     if ((e = cudaMalloc(&s->full_vals, (size_t)s->nslots * s->vpad * 4u)) != cudaSuccess) return bail("cudaMalloc", e);
     if ((e = cudaMemset(s->sc_ticket, 0, (size_t)max_batch * 4u)) != cudaSuccess) return bail("cudaMemset", e);
-    if ((e = cudaMemset(s->full_count, 0, 4u)) != cudaSuccess) return bail("cudaMemset", e);
-    if ((e = cudaMemset(s->full_ticket, 0, 4u)) != cudaSuccess) return bail("cudaMemset", e);
+    if ((e = cudaMemset(s->full_slots, 0, (size_t)s->nslots * 4u)) != cudaSuccess) return bail("cudaMemset", e);
     if ((e = cudaMalloc(&s->device_errors, 4u)) != cudaSuccess) return bail("cudaMalloc", e);
     if ((e = cudaMemset(s->device_errors, 0, 4u)) != cudaSuccess) return bail("cudaMemset", e);
     if ((e = cudaDeviceSynchronize()) != cudaSuccess) return bail("cudaDeviceSynchronize", e);

@@ -159,7 +159,7 @@ int32_t llm_cuda_sample_batch_static(int32_t device, const llm_cuda_sample_args*
     P.kept_cap = (a->kept_ids || a->kept_probs) ? a->kept_capacity : 0u;
     P.row_stats = a->row_stats;
     P.vocab_global = a->vocab;
-    // no full-sort stage here: full_list stays NULL and such a row would be flagged, but the
+    // no full-sort stage here: full_keys stays NULL and such a row would be flagged, but the
     // checks above leave only rows that exact selection always resolves
 
     LaunchPlan plan{};
@@ -167,12 +167,15 @@ int32_t llm_cuda_sample_batch_static(int32_t device, const llm_cuda_sample_args*
     const uint32_t max_lists = kMaxLists;
     if (plan_launch(d->info, P, true, k_hint, kMaxTopK, kMaxHistory, a->split, max_lists, &plan) != 0)
         return fail(LLM_CUDA_ERR_CAPACITY, "shared-memory layout does not fit%s");
-    if (plan.limit > kListLen) return fail(LLM_CUDA_ERR_CAPACITY, "candidate lists exceed the static scratch%s");
+    // the fixed lists are shorter than the handle's; a lower compaction trigger is always valid
+    // as long as it leaves room for the kept set
+    const uint32_t limit = plan.limit < kListLen ? plan.limit : kListLen;
+    if (limit < 2u * plan.kcap) return fail(LLM_CUDA_ERR_CAPACITY, "candidate lists exceed the static scratch%s");
     P.split = plan.split;
     P.shard_cols = plan.shard_cols;
     P.kcap = plan.kcap;
     P.ccap = plan.ccap;
-    P.limit = plan.limit;
+    P.limit = limit;
     P.hash_slots = plan.hash_slots;
     P.bitmap_words = plan.bitmap_words;
     P.sc_q = reinterpret_cast<float*>(d->scratch + kOffValues);
@@ -180,7 +183,7 @@ int32_t llm_cuda_sample_batch_static(int32_t device, const llm_cuda_sample_args*
     P.sc_cnt = reinterpret_cast<uint32_t*>(d->scratch + kOffCounts);
     P.sc_maxkey = reinterpret_cast<uint32_t*>(d->scratch + kOffMaxima);
     P.sc_ticket = reinterpret_cast<uint32_t*>(d->scratch + kOffTickets);
-    P.sc_stride = plan.limit;
+    P.sc_stride = limit;
     P.sc_rows = P.batch;
     cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
     // the tickets are the one part of the shared array that must start at zero

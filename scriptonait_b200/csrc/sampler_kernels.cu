@@ -9,7 +9,8 @@
 //                        through the exact ordered tail of sample_with.
 // merge_draw_kernel      the ordered tail over candidate lists gathered from
 //                        several GPUs (vocabulary sharding).
-// full_sort_kernel       literal full ordering of a row, for the rare rows
+// full_sort_row          (device function of the streaming kernel) literal full
+//                        ordering of a row in global scratch, for the rare rows
 //                        whose kept set or draw reaches past the window.
 // advance_rows_kernel    decode-loop glue (history ring, EOS, draw counter).
 // pack_allowed_kernel    bool-per-id -> bit mask.
@@ -125,6 +126,10 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     return false;
 }
 
+// Programmatic dependent launch. Both are no-ops for a grid launched the ordinary way.
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ unsigned long long global_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -136,29 +141,16 @@ __device__ __forceinline__ unsigned long long global_ns() {
             P.phase_ns[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 8u + (slot)] = global_ns();              \
     } while (0)
 
-constexpr int FULL_THREADS = 1024;
-__global__ void full_sort_kernel(const __grid_constant__ KParams P, uint64_t* keys_all, float* vals_all, uint32_t vpad,
-                                 uint32_t* ticket);
-
-__device__ __forceinline__ void push_full(const KParams& P, uint32_t b) {
-    if (!P.full_list) {  // a caller without a full-sort stage: the row is reported, not guessed
-        P.tokens[b] = 0u;
-        if (P.row_flags) P.row_flags[b] = LLM_CUDA_ROW_INVALID;
-        if (P.kept_count) P.kept_count[b] = 0u;
+// A row that needs the full ordering where no full-sort scratch exists (the allocation-free
+// entry point, candidate lists gathered from other GPUs): reported, not guessed.
+__device__ __forceinline__ void report_unresolved(const KParams& P, uint32_t b) {
+    if (P.out_q) {
+        P.out_cnt[b] = 0u;
         return;
     }
-    const uint32_t pos = atomicAdd(P.full_count, 1u);
-    P.full_list[pos] = b;
-#ifndef LLMC_NO_TAIL_LAUNCH
-    if (pos == 0u && P.tail_launch) {
-        // first row of this launch that needs the full ordering: queue the full-sort kernel behind
-        // this grid (it starts when every CTA of this grid has finished, so the list is complete)
-        KParams Q = P;
-        Q.hash_slots = P.full_hash_slots;
-        full_sort_kernel<<<P.full_nslots, FULL_THREADS, (size_t)P.full_hash_slots * 8u, cudaStreamTailLaunch>>>(
-            Q, reinterpret_cast<uint64_t*>(P.full_keys), P.full_vals, P.full_vpad, P.full_ticket);
-    }
-#endif
+    P.tokens[b] = 0u;
+    if (P.row_flags) P.row_flags[b] = LLM_CUDA_ROW_INVALID;
+    if (P.kept_count) P.kept_count[b] = 0u;
 }
 
 // Streaming threshold of window mode for a given maximum (both in the post-temperature domain).
@@ -171,10 +163,33 @@ __device__ __forceinline__ float temper(float x, float T) { return x; }
 __device__ __forceinline__ float temper(float x, float T) { return (T == 1.0f) ? x : __fdiv_rn(x, T); }  // generate.rs:357-359
 #endif
 
+// The r-th largest of the 32 lanes' keys (1 <= r <= 32), returned to every lane. Keys are ordered
+// keys of floats, all above 0, so 0 serves as "taken".
+__device__ __forceinline__ uint32_t warp_rth_largest(uint32_t key, uint32_t r, unsigned lane) {
+    if (r <= 8u) {
+        uint32_t cur = key, res = 0u;
+        for (uint32_t i = 0; i < r; ++i) {
+            res = __reduce_max_sync(FULL_MASK, cur);
+            const unsigned who = __ballot_sync(FULL_MASK, cur == res);
+            if ((int)lane == __ffs(who) - 1) cur = 0u;  // take one holder of the maximum out
+        }
+        return res;
+    }
+    uint32_t rank = 0u;
+#pragma unroll 4
+    for (int o = 1; o < 32; ++o) {
+        const unsigned src = (lane + o) & 31u;
+        const uint32_t other = __shfl_sync(FULL_MASK, key, src);
+        rank += (other > key || (other == key && src < lane)) ? 1u : 0u;
+    }
+    const unsigned holder = __ballot_sync(FULL_MASK, rank == r - 1u);
+    return __shfl_sync(FULL_MASK, key, __ffs(holder) - 1);
+}
+
 // After all candidates of a row are in cand[0..n): final selection, ordering
 // and either the ordered tail (token out) or the candidate list out. `scratch`
 // is EPILOGUE_SCRATCH bytes of shared memory nothing else uses any more.
-__device__ void finish_row(const KParams& P, uint32_t b, const RowCfg& rc, uint32_t n, bool overflow, float qmax, Shared& S,
+__device__ bool finish_row(const KParams& P, uint32_t b, const RowCfg& rc, uint32_t n, bool overflow, float qmax, Shared& S,
                            float* cand_q, uint32_t* cand_i, unsigned char* scratch, bool window_filtered = false) {
     uint64_t* keys64 = reinterpret_cast<uint64_t*>(scratch);                     // THREADS 64-bit words
     float* probs = reinterpret_cast<float*>(scratch + (size_t)THREADS * 8u);     // up to MAX_SORT floats
@@ -196,10 +211,7 @@ __device__ void finish_row(const KParams& P, uint32_t b, const RowCfg& rc, uint3
         if (!rc.windowed && n < rc.k_eff) overflow = true;
         if (rc.windowed && qmax == neg_inf()) overflow = true;
     }
-    if (overflow) {
-        if (threadIdx.x == 0) push_full(P, b);
-        return;
-    }
+    if (overflow) return true;
     PHASE(3);
     sort_candidates(n, cand_q, cand_i, keys64);
     PHASE(4);
@@ -211,7 +223,7 @@ __device__ void finish_row(const KParams& P, uint32_t b, const RowCfg& rc, uint3
             P.out_i[(size_t)b * P.out_stride + i] = cand_i[i];
         }
         if (threadIdx.x == 0) P.out_cnt[b] = min(n_use, P.out_stride);
-        return;
+        return false;
     }
     if (rc.greedy || n_use == 0u) {
         if (threadIdx.x == 0) {
@@ -223,16 +235,14 @@ __device__ void finish_row(const KParams& P, uint32_t b, const RowCfg& rc, uint3
         }
         cta_sync();
         write_row_outputs(P, b, 0u, S, n_use ? cand_q[0] : 0.f, cand_i, probs, 0u);
-        return;
+        return false;
     }
     ordered_tail(P, b, rc, n_use, truncated, rc.k_eff, S, cand_q, cand_i, probs);
     PHASE(5);
-    if (S.out_flags & ROW_NEEDS_FULL) {
-        if (threadIdx.x == 0) push_full(P, b);
-        return;
-    }
+    if (S.out_flags & ROW_NEEDS_FULL) return true;
     write_row_outputs(P, b, rc.windowed ? LLM_CUDA_ROW_WINDOWED : 0u, S, cand_q[0], cand_i, probs, S.keep);
     PHASE(6);
+    return false;
 }
 
 // Pulls the candidate lists of `nsh` shards of row b into cand[] (compacting
@@ -291,6 +301,280 @@ __device__ uint32_t merge_lists(const KParams& P, uint32_t b, const RowCfg& rc, 
 // MODE trims the code to what a launch can need (the hot loop must stay small enough for the
 // instruction cache): 0 = rows of either kind, 1 = every row runs in window mode, 2 = no row does.
 constexpr int STREAM_THREADS = THREADS + 32;  // THREADS consumers + one warp that only issues the bulk copies
+// ---------------------------------------------------------------------------
+// Full ordering of a row in global scratch (bitonic sort of 64-bit keys), then
+// the ordered tail exactly as the reference walks it. Slow and rarely needed:
+// rows whose window overflowed or whose kept set / walk left the window. Run by
+// the 256 consumer threads of the CTA that found the row undecided, in one of
+// P.full_nslots scratch slots; `hkeys/hcnt` is the CTA's id->count table
+// (P.hash_slots entries, rebuilt here for the whole vocabulary).
+struct FullShared {
+    RowCfg rc;
+    uint32_t nvalid, keep, token, flags, kept_n, slot;
+    float sum, total, u, r, thr;
+};
+
+constexpr uint32_t FULL_SLOT_ROUNDS = 1u << 14;
+
+// Claims a free scratch slot. Every holder is a running CTA of this same grid that releases its
+// slot without waiting for anyone, so a bounded poll is enough; 0xffffffff when the bound runs out.
+__device__ uint32_t acquire_full_slot(const KParams& P) {
+    const uint32_t n = P.full_nslots;
+    if (!P.full_slots || n == 0u) return 0xffffffffu;
+    uint32_t i = (blockIdx.y * gridDim.x + blockIdx.x) % n;
+    for (uint32_t round = 0; round < FULL_SLOT_ROUNDS; ++round) {
+        for (uint32_t k = 0; k < n; ++k) {
+            if (atomicCAS(&P.full_slots[i], 0u, 1u) == 0u) return i;
+            i = (i + 1u == n) ? 0u : i + 1u;
+        }
+        __nanosleep(4000);
+    }
+    return 0xffffffffu;
+}
+
+__device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullShared& F, uint32_t* hkeys, uint32_t* hcnt) {
+    const uint32_t tid = threadIdx.x;
+    const uint32_t V = P.vocab;
+    uint32_t m = 1u;
+    while (m < V) m <<= 1;
+    if (!P.full_keys) {
+        if (tid == 0) report_unresolved(P, b);
+        return;
+    }
+    cta_sync();  // whatever used this shared memory before is finished
+    if (tid == 0) {
+        resolve_row(P, b, F.rc);
+        F.slot = acquire_full_slot(P);
+        F.nvalid = 0u;
+        F.keep = 0u;
+        F.flags = 0u;
+        F.kept_n = 0u;
+        F.token = 0u;
+        F.sum = F.total = F.u = F.r = F.thr = 0.f;
+    }
+    for (uint32_t i = tid; i < P.hash_slots; i += THREADS) {
+        hkeys[i] = EMPTY_KEY;
+        hcnt[i] = 0u;
+    }
+    cta_sync();
+    const RowCfg rc = F.rc;
+    if (F.slot == 0xffffffffu) {  // no scratch slot came free within the bound: reported, not guessed
+        if (tid == 0) {
+            report_unresolved(P, b);
+            if (P.device_errors) atomicOr(P.device_errors, 2u);
+        }
+        return;
+    }
+    uint64_t* keys = reinterpret_cast<uint64_t*>(P.full_keys) + (size_t)F.slot * P.full_vpad;
+    float* vals = P.full_vals + (size_t)F.slot * P.full_vpad;
+    if (rc.has_pen) {
+        const uint32_t* hist = P.history + (size_t)b * P.hist_stride;
+        for (uint32_t j = tid; j < rc.hlen; j += THREADS) {
+            const uint32_t id = __ldg(&hist[j]);
+            if (id >= P.col_offset && id - P.col_offset < V) hash_insert(hkeys, hcnt, P.hash_slots, id);
+        }
+    }
+    cta_sync();
+    // ---- keys: ascending u64 order == value descending, index ascending
+    uint32_t myvalid = 0u;
+    for (uint32_t c = tid; c < m; c += THREADS) {
+        uint64_t key = ~0ull;
+        if (c < V) {
+            float x;
+            if (P.dtype == LLM_CUDA_DTYPE_BF16)
+                x = load_logit(reinterpret_cast<const uint16_t*>(P.logits) + (size_t)b * P.row_stride + c);
+            else
+                x = load_logit(reinterpret_cast<const float*>(P.logits) + (size_t)b * P.row_stride + c);
+            const uint32_t gid = P.col_offset + c;
+            if (id_blocked(P, gid)) x = neg_inf();
+            if (rc.has_pen) x = penalize(x, rc.pen, hash_count(hkeys, hcnt, P.hash_slots, gid));
+            const float q = temper(x, rc.T);
+            if (q == q) {
+                key = ((uint64_t)(~okey(q)) << 32) | (uint64_t)c;
+                ++myvalid;
+            }
+        }
+        __stcg(&keys[c], key);
+    }
+    if (myvalid) atomicAdd(&F.nvalid, myvalid);
+    cta_sync();
+    const uint32_t half = m >> 1;
+    for (uint32_t size = 2u; size <= m; size <<= 1) {
+        for (uint32_t stride = size >> 1; stride > 0u; stride >>= 1) {
+            // the pairs of one pass are disjoint: four of them in flight per thread
+            for (uint32_t t0 = tid; t0 < half; t0 += 4u * THREADS) {
+                uint32_t lo[4];
+                uint64_t a[4], c[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const uint32_t t = t0 + (uint32_t)u * THREADS;
+                    lo[u] = ((t & ~(stride - 1u)) << 1) | (t & (stride - 1u));
+                    if (t < half) {
+                        a[u] = __ldcg(&keys[lo[u]]);
+                        c[u] = __ldcg(&keys[lo[u] + stride]);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const uint32_t t = t0 + (uint32_t)u * THREADS;
+                    if (t < half) {
+                        const bool ascending = ((lo[u] & size) == 0u);
+                        if ((a[u] > c[u]) == ascending) {
+                            __stcg(&keys[lo[u]], c[u]);
+                            __stcg(&keys[lo[u] + stride], a[u]);
+                        }
+                    }
+                }
+            }
+            cta_sync();
+        }
+    }
+    const uint32_t n = min(F.nvalid, rc.k_eff);
+    auto q_at = [&](uint32_t i) { return okey_to_float(~(uint32_t)(__ldcg(&keys[i]) >> 32)); };
+    auto id_at = [&](uint32_t i) { return P.col_offset + (uint32_t)(__ldcg(&keys[i]) & 0xffffffffull); };
+    float mx = 0.f;
+    bool done = false;
+    if (rc.greedy || n == 0u) {
+        if (tid == 0) {
+            F.token = n ? id_at(0) : 0u;
+            if (n && q_at(0) == neg_inf()) F.token = 0u;
+            F.flags = rc.greedy ? LLM_CUDA_ROW_GREEDY : LLM_CUDA_ROW_DEGENERATE;
+        }
+        done = true;
+    }
+    if (!done) {
+        mx = q_at(0);
+        for (uint32_t i = tid; i < n; i += THREADS) __stcg(&vals[i], exp_f32(__fsub_rn(q_at(i), mx)));
+        cta_sync();
+        if (tid == 0) {
+            float s = 0.0f;
+            for (uint32_t i = 0; i < n; ++i) {
+                const float e = __ldcg(&vals[i]);
+                if (e < 5.9604644775390625e-08f && s >= 1.0f) break;
+                s = __fadd_rn(s, e);
+            }
+            F.sum = s;
+            F.keep = n;
+        }
+        cta_sync();
+        const float sum = F.sum;
+        if ((sum <= 0.0f) || !(fabsf(sum) <= 3.402823466e38f)) {
+            if (tid == 0) {
+                F.token = id_at(0);
+                F.flags = LLM_CUDA_ROW_DEGENERATE;
+            }
+            done = true;
+        }
+        if (!done) {
+            for (uint32_t i = tid; i < n; i += THREADS) __stcg(&vals[i], __fdiv_rn(__ldcg(&vals[i]), sum));
+            cta_sync();
+            if (rc.min_p > 0.0f) {
+                const float thr = __fmul_rn(rc.min_p, __ldcg(&vals[0]));
+                uint32_t first_fail = n;
+                for (uint32_t i = tid; i < n; i += THREADS) {
+                    if (!(__ldcg(&vals[i]) >= thr)) {
+                        first_fail = i;
+                        break;
+                    }
+                }
+                if (first_fail < n) atomicMin(&F.keep, first_fail);
+                cta_sync();
+                if (tid == 0) {
+                    F.thr = thr;
+                    if (F.keep < 1u) F.keep = 1u;
+                }
+                cta_sync();
+            }
+            if (tid == 0) {
+                const uint32_t keep_minp = F.keep;
+                uint32_t keep = keep_minp;
+                float total = 0.0f;
+                const float p0 = __ldcg(&vals[0]);
+                const float tiny = __fmul_rn(p0, 1.4901161193847656e-08f);  // 2^-26 of the leader: below half an ulp of any running sum
+                if (rc.top_p < 1.0f) {
+                    float cum = 0.0f;
+                    for (uint32_t i = 0; i < keep_minp; ++i) {
+                        const float p = __ldcg(&vals[i]);
+                        if (p < tiny) break;  // this and all later terms leave cum unchanged: top_p is never reached
+                        cum = __fadd_rn(cum, p);
+                        if (cum >= rc.top_p) {
+                            keep = i + 1u;
+                            break;
+                        }
+                    }
+                    total = cum;
+                } else {
+                    for (uint32_t i = 0; i < keep_minp; ++i) {
+                        const float p = __ldcg(&vals[i]);
+                        if (p < tiny) break;
+                        total = __fadd_rn(total, p);
+                    }
+                }
+                float u;
+                if (P.uniforms) {
+                    u = P.uniforms[b];
+                } else {
+                    const uint64_t seed = P.seeds ? P.seeds[b] : P.seed_base + (uint64_t)b;
+                    const uint64_t dn = P.draw_index ? P.draw_index[b] : 0ull;
+                    u = u24_to_f32(splitmix_output(seed, dn + 1ull));
+                }
+                float rr = __fmul_rn(u, total);
+                F.total = total;
+                F.u = u;
+                F.r = rr;
+                uint32_t flags = LLM_CUDA_ROW_DRAW_CONSUMED;
+                uint32_t token = 0u;
+                bool found = false;
+                for (uint32_t i = 0; i < keep; ++i) {
+                    const float p = __ldcg(&vals[i]);
+                    if (rr < p) {
+                        token = id_at(i);
+                        found = true;
+                        break;
+                    }
+                    rr = __fsub_rn(rr, p);
+                }
+                if (!found) {
+                    token = id_at(keep - 1u);
+                    flags |= LLM_CUDA_ROW_FALLBACK_LAST;
+                }
+                F.token = token;
+                F.flags = flags;
+                F.keep = keep;
+                F.kept_n = keep;
+            }
+        }
+    }
+    cta_sync();
+    const uint32_t flags = F.flags | LLM_CUDA_ROW_FULL_SORT;
+    if (tid == 0) {
+        P.tokens[b] = F.token;
+        if (P.row_flags) P.row_flags[b] = flags;
+        if (P.kept_count) P.kept_count[b] = F.kept_n;
+        if (P.row_stats) {
+            float* st = P.row_stats + (size_t)b * LLM_CUDA_ROW_STATS;
+            st[0] = mx;
+            st[1] = F.sum;
+            st[2] = F.total;
+            st[3] = F.u;
+            st[4] = F.thr;
+            st[5] = F.r;
+        }
+    }
+    if (P.kept_cap && (flags & LLM_CUDA_ROW_DRAW_CONSUMED)) {
+        const uint32_t lim = min(F.keep, P.kept_cap);
+        for (uint32_t i = tid; i < lim; i += THREADS) {
+            if (P.kept_ids) P.kept_ids[(size_t)b * P.kept_cap + i] = id_at(i);
+            if (P.kept_probs) P.kept_probs[(size_t)b * P.kept_cap + i] = __ldcg(&vals[i]);
+        }
+    }
+    cta_sync();
+    if (tid == 0) {
+        __threadfence();
+        atomicExch(&P.full_slots[F.slot], 0u);
+    }
+}
+
 template <typename ElemT, bool BITS, int MODE>
 __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const __grid_constant__ KParams P) {
     constexpr int VEC = Traits<ElemT>::VEC;
@@ -313,6 +597,10 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
     const uint32_t b = blockIdx.y, shard = blockIdx.x, tid = threadIdx.x;
     const unsigned lane = tid & 31u, warp = tid >> 5;
     const uint32_t LOWEST = 0x007fffffu;  // okey(-inf)
+    // A launch that asked to overlap its predecessor may start now. Until grid_dependency_wait()
+    // below, this kernel reads its inputs and writes shared memory only; everything it writes to
+    // global memory (outputs, the scratch rows and tickets the launches of a handle share) comes after.
+    grid_launch_dependents();
     if (tid == 0) {
         resolve_row(P, b, S.rc);
         S.count = 0u;
@@ -333,6 +621,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
     if (MODE == 2) rc.windowed = 0u;  // ... or the window code
     PHASE(0);
     if (rc.invalid) {
+        grid_dependency_wait();
         if (shard == 0 && tid == 0) {
             if (P.out_q) {
                 P.out_cnt[b] = 0u;
@@ -345,7 +634,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
         return;
     }
     if (P.force_full) {
-        if (shard == 0 && tid == 0) push_full(P, b);
+        grid_dependency_wait();
+        if (warp < (unsigned)WARPS && shard == 0) full_sort_row(P, b, *reinterpret_cast<FullShared*>(ring), hkeys, hcnt);
         return;
     }
 
@@ -491,13 +781,22 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
     //      (packed bf16 arithmetic for bf16 rows) and notes the vectors that reach the threshold in
     //      its warp's list, (B) the warp examines its listed vectors 32/VEC at a time.
     bool wait_failed = false;
+#ifdef LLMC_PROFILE_STAGES
+    long long acc[6] = {0, 0, 0, 0, 0, 0};
+    long long c_a = clock64(), c_b;
+#define TICK(k) do { c_b = clock64(); acc[k] += c_b - c_a; c_a = c_b; } while (0)
+#else
+#define TICK(k) do { } while (0)
+#endif
     for (uint32_t tt = 0; tt <= vtiles; ++tt) {
         // iteration tt == vtiles only settles the buffer
         const bool max_sweep = rc.windowed != 0u;  // window-mode rows only take maxima here
         const uint32_t t = tt;
         if (tt < vtiles) {
             const uint32_t stage = tt % RING_STAGES;
+            TICK(5);
             if (!mbar_wait_bounded(&full_bar[stage], (tt / RING_STAGES) & 1u)) wait_failed = true;
+            TICK(0);
             const uint4* sv = reinterpret_cast<const uint4*>(ring + (size_t)stage * STAGE_BYTES);
             float vm[U];
 #pragma unroll
@@ -509,7 +808,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
                 vm[u] = m;  // of the raw values; NaN elements are ignored by the maxima
                 if (!BITS) tmax = fmaxf(tmax, m);
             }
-            if (BITS && (max_sweep || (tt == 0 && !rc.windowed))) {
+            if (BITS) {
                 // a maximum of the edited row is wanted: flagged ids (penalised, blocked) must not count
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
@@ -564,23 +863,16 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
                 if (lane == 0) mbar_arrive(&empty_bar[stage]);
                 continue;
             } else {
-                if (tt == 0) {
-                    // (top-k rows) bootstrap the threshold from the first stage, before anything of it is appended
-                    if (rc.k_eff <= (uint32_t)THREADS) {
-                        // each lane's maximum is an element of the edited row, so the r-th largest lane maximum
-                        // of a warp has >= r elements at or above it; the minimum over the warps of those
-                        // bounds has >= WARPS*r >= k elements at or above it: a valid lower bound for the
-                        // k-th largest value of the whole row
-                        const uint32_t r = (rc.k_eff + WARPS - 1u) / WARPS;
-                        const uint32_t mykey = okey(tmax);
-                        uint32_t rank = 0u;
-#pragma unroll 4
-                        for (int o = 1; o < 32; ++o) {
-                            const unsigned src = (lane + o) & 31u;
-                            const uint32_t other = __shfl_sync(FULL_MASK, mykey, src);
-                            rank += (other > mykey || (other == mykey && src < lane)) ? 1u : 0u;
-                        }
-                        if (rank == r - 1u) S.wkth[warp] = mykey;
+                if (rc.k_eff <= (uint32_t)THREADS) {
+                    // A lower bound for the k-th largest value of the row, refreshed every stage from the
+                    // lanes' running maxima: each lane's maximum is an element of the edited row, so the
+                    // r-th largest lane maximum of a warp has >= r elements at or above it, and the
+                    // minimum over the warps of those bounds has >= WARPS*r >= k. The bound rises as the
+                    // lanes see more of the row, which keeps the candidate list short without compaction.
+                    const uint32_t r = (rc.k_eff + WARPS - 1u) / WARPS;
+                    const uint32_t kth = warp_rth_largest(okey(tmax), r, lane);
+                    if (lane == 0) S.wkth[warp] = kth;
+                    if (tt == 0) {  // before anything of the first stage is appended
                         cta_sync();
                         if (tid == 0) {
                             uint32_t lo = S.wkth[0];
@@ -591,6 +883,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
                         cta_sync();
                     }
                 }
+                TICK(1);
                 const float tau = okey_to_float(vol_load(&S.tau_key));
                 // this warp's list of vectors that hold a passing value ...
                 uint32_t wcnt = 0u;
@@ -635,7 +928,15 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
             if (lane == 0) atomicMax(&S.max_key, wk);
         }
         end = __reduce_max_sync(FULL_MASK, end);
+        TICK(2);
         const int over = cta_sync_or(end > P.limit ? 1 : 0);
+        TICK(3);
+        if (!rc.windowed && rc.k_eff <= (uint32_t)THREADS && tid == 0) {
+            uint32_t lo = S.wkth[0];  // written before the barrier; a later, larger value is just as valid
+#pragma unroll
+            for (int w = 1; w < WARPS; ++w) lo = min(lo, S.wkth[w]);
+            if (lo > S.tau_key) S.tau_key = lo;
+        }
         if (over) {
             uint32_t n = min(S.count, P.ccap);
             cta_sync();
@@ -669,6 +970,14 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
     cta_sync();
     bool window_filtered = false;  // the candidates already are exactly the window
     PHASE(7);
+#ifdef LLMC_PROFILE_STAGES
+    TICK(4);
+    if (P.phase_ns && (tid == 0 || tid == 255)) {
+        unsigned long long* o = P.phase_ns + ((size_t)gridDim.x * gridDim.y + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 2u + (tid ? 1u : 0u)) * 8u;
+        for (int k = 0; k < 6; ++k) o[k] = acc[k];
+        o[6] = vtiles; o[7] = S.count;
+    }
+#endif
     if (rc.windowed) {
         // the row's maximum fixes the threshold; the vectors noted during the sweep are read again
         // (from L2) and their elements tested against the exact window
@@ -776,6 +1085,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
     }
     PHASE(2);
     if (wait_failed) atomicOr(&S.error, 4u);
+    grid_dependency_wait();  // the previous kernel of the stream is complete from here on
     cta_sync();
 
     uint32_t n = min(S.count, P.ccap);
@@ -787,7 +1097,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
     }
 
     if (P.split == 1u) {
-        finish_row(P, b, rc, n, overflow, qmax, S, cand_q, cand_i, ring, window_filtered);
+        if (finish_row(P, b, rc, n, overflow, qmax, S, cand_q, cand_i, ring, window_filtered))
+            full_sort_row(P, b, *reinterpret_cast<FullShared*>(ring), hkeys, hcnt);
         return;
     }
 
@@ -826,7 +1137,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
     if (tid == 0) P.sc_ticket[b] = 0u;  // re-armed for the next launch on this stream
     __threadfence();
     n = merge_lists(P, b, rc, P.split, S, cand_q, cand_i, overflow, qmax);
-    finish_row(P, b, rc, n, overflow, qmax, S, cand_q, cand_i, ring);
+    if (finish_row(P, b, rc, n, overflow, qmax, S, cand_q, cand_i, ring))
+        full_sort_row(P, b, *reinterpret_cast<FullShared*>(ring), hkeys, hcnt);
 }
 
 // Ordered tail over gathered candidate lists: one CTA per row.
@@ -854,248 +1166,8 @@ __global__ void __launch_bounds__(THREADS) merge_draw_kernel(const __grid_consta
     bool overflow;
     float qmax;
     const uint32_t n = merge_lists(P, b, rc, P.split, S, cand_q, cand_i, overflow, qmax);
-    finish_row(P, b, rc, n, overflow, qmax, S, cand_q, cand_i, scratch);
-}
-
-// ---------------------------------------------------------------------------
-// Full ordering of a row in global scratch (bitonic sort of 64-bit keys), then
-// the ordered tail exactly as the reference walks it. Slow and rarely needed:
-// rows whose window overflowed or whose kept set / walk left the window.
-struct FullShared {
-    RowCfg rc;
-    uint32_t nvalid, keep, token, flags, kept_n;
-    float sum, total, u, r, thr;
-};
-
-__global__ void __launch_bounds__(FULL_THREADS) full_sort_kernel(const __grid_constant__ KParams P, uint64_t* keys_all,
-                                                                 float* vals_all, uint32_t vpad, uint32_t* ticket) {
-    extern __shared__ __align__(16) unsigned char dynf[];
-    __shared__ FullShared F;
-    uint32_t* hkeys = reinterpret_cast<uint32_t*>(dynf);
-    uint32_t* hcnt = hkeys + P.hash_slots;
-    const uint32_t tid = threadIdx.x;
-    const uint32_t count = *(volatile uint32_t*)P.full_count;
-    uint64_t* keys = keys_all + (size_t)blockIdx.x * vpad;
-    float* vals = vals_all + (size_t)blockIdx.x * vpad;
-    const uint32_t V = P.vocab;
-    uint32_t m = 1u;
-    while (m < V) m <<= 1;
-
-    for (uint32_t r = blockIdx.x; r < count; r += gridDim.x) {
-        const uint32_t b = __ldcg(&P.full_list[r]);
-        if (tid == 0) {
-            resolve_row(P, b, F.rc);
-            F.nvalid = 0u;
-            F.keep = 0u;
-            F.flags = 0u;
-            F.kept_n = 0u;
-            F.token = 0u;
-            F.sum = F.total = F.u = F.r = F.thr = 0.f;
-        }
-        for (uint32_t i = tid; i < P.hash_slots; i += FULL_THREADS) {
-            hkeys[i] = EMPTY_KEY;
-            hcnt[i] = 0u;
-        }
-        __syncthreads();
-        const RowCfg rc = F.rc;
-        if (rc.has_pen) {
-            const uint32_t* hist = P.history + (size_t)b * P.hist_stride;
-            for (uint32_t j = tid; j < rc.hlen; j += FULL_THREADS) {
-                const uint32_t id = __ldg(&hist[j]);
-                if (id >= P.col_offset && id - P.col_offset < V) hash_insert(hkeys, hcnt, P.hash_slots, id);
-            }
-        }
-        __syncthreads();
-        // ---- keys: ascending u64 order == value descending, index ascending
-        uint32_t myvalid = 0u;
-        for (uint32_t c = tid; c < m; c += FULL_THREADS) {
-            uint64_t key = ~0ull;
-            if (c < V) {
-                float x;
-                if (P.dtype == LLM_CUDA_DTYPE_BF16)
-                    x = load_logit(reinterpret_cast<const uint16_t*>(P.logits) + (size_t)b * P.row_stride + c);
-                else
-                    x = load_logit(reinterpret_cast<const float*>(P.logits) + (size_t)b * P.row_stride + c);
-                const uint32_t gid = P.col_offset + c;
-                if (id_blocked(P, gid)) x = neg_inf();
-                if (rc.has_pen) x = penalize(x, rc.pen, hash_count(hkeys, hcnt, P.hash_slots, gid));
-                const float q = temper(x, rc.T);
-                if (q == q) {
-                    key = ((uint64_t)(~okey(q)) << 32) | (uint64_t)c;
-                    ++myvalid;
-                }
-            }
-            __stcg(&keys[c], key);
-        }
-        if (myvalid) atomicAdd(&F.nvalid, myvalid);
-        __syncthreads();
-        for (uint32_t size = 2u; size <= m; size <<= 1) {
-            for (uint32_t stride = size >> 1; stride > 0u; stride >>= 1) {
-                for (uint32_t t = tid; t < (m >> 1); t += FULL_THREADS) {
-                    const uint32_t lo = ((t & ~(stride - 1u)) << 1) | (t & (stride - 1u));
-                    const uint32_t hi = lo + stride;
-                    const uint64_t a = __ldcg(&keys[lo]), c = __ldcg(&keys[hi]);
-                    const bool ascending = ((lo & size) == 0u);
-                    if ((a > c) == ascending) {
-                        __stcg(&keys[lo], c);
-                        __stcg(&keys[hi], a);
-                    }
-                }
-                __syncthreads();
-            }
-        }
-        const uint32_t n = min(F.nvalid, rc.k_eff);
-        auto q_at = [&](uint32_t i) { return okey_to_float(~(uint32_t)(__ldcg(&keys[i]) >> 32)); };
-        auto id_at = [&](uint32_t i) { return P.col_offset + (uint32_t)(__ldcg(&keys[i]) & 0xffffffffull); };
-        float mx = 0.f;
-        bool done = false;
-        if (rc.greedy || n == 0u) {
-            if (tid == 0) {
-                F.token = n ? id_at(0) : 0u;
-                if (n && q_at(0) == neg_inf()) F.token = 0u;
-                F.flags = rc.greedy ? LLM_CUDA_ROW_GREEDY : LLM_CUDA_ROW_DEGENERATE;
-            }
-            done = true;
-        }
-        if (!done) {
-            mx = q_at(0);
-            for (uint32_t i = tid; i < n; i += FULL_THREADS) __stcg(&vals[i], exp_f32(__fsub_rn(q_at(i), mx)));
-            __syncthreads();
-            if (tid == 0) {
-                float s = 0.0f;
-                for (uint32_t i = 0; i < n; ++i) {
-                    const float e = __ldcg(&vals[i]);
-                    if (e < 5.9604644775390625e-08f && s >= 1.0f) break;
-                    s = __fadd_rn(s, e);
-                }
-                F.sum = s;
-                F.keep = n;
-            }
-            __syncthreads();
-            const float sum = F.sum;
-            if ((sum <= 0.0f) || !(fabsf(sum) <= 3.402823466e38f)) {
-                if (tid == 0) {
-                    F.token = id_at(0);
-                    F.flags = LLM_CUDA_ROW_DEGENERATE;
-                }
-                done = true;
-            }
-            if (!done) {
-                for (uint32_t i = tid; i < n; i += FULL_THREADS) __stcg(&vals[i], __fdiv_rn(__ldcg(&vals[i]), sum));
-                __syncthreads();
-                if (rc.min_p > 0.0f) {
-                    const float thr = __fmul_rn(rc.min_p, __ldcg(&vals[0]));
-                    uint32_t first_fail = n;
-                    for (uint32_t i = tid; i < n; i += FULL_THREADS) {
-                        if (!(__ldcg(&vals[i]) >= thr)) {
-                            first_fail = i;
-                            break;
-                        }
-                    }
-                    if (first_fail < n) atomicMin(&F.keep, first_fail);
-                    __syncthreads();
-                    if (tid == 0) {
-                        F.thr = thr;
-                        if (F.keep < 1u) F.keep = 1u;
-                    }
-                    __syncthreads();
-                }
-                if (tid == 0) {
-                    const uint32_t keep_minp = F.keep;
-                    uint32_t keep = keep_minp;
-                    float total = 0.0f;
-                    const float p0 = __ldcg(&vals[0]);
-                    const float tiny = __fmul_rn(p0, 1.4901161193847656e-08f);  // 2^-26 of the leader: below half an ulp of any running sum
-                    if (rc.top_p < 1.0f) {
-                        float cum = 0.0f;
-                        for (uint32_t i = 0; i < keep_minp; ++i) {
-                            const float p = __ldcg(&vals[i]);
-                            if (p < tiny) break;  // this and all later terms leave cum unchanged: top_p is never reached
-                            cum = __fadd_rn(cum, p);
-                            if (cum >= rc.top_p) {
-                                keep = i + 1u;
-                                break;
-                            }
-                        }
-                        total = cum;
-                    } else {
-                        for (uint32_t i = 0; i < keep_minp; ++i) {
-                            const float p = __ldcg(&vals[i]);
-                            if (p < tiny) break;
-                            total = __fadd_rn(total, p);
-                        }
-                    }
-                    float u;
-                    if (P.uniforms) {
-                        u = P.uniforms[b];
-                    } else {
-                        const uint64_t seed = P.seeds ? P.seeds[b] : P.seed_base + (uint64_t)b;
-                        const uint64_t dn = P.draw_index ? P.draw_index[b] : 0ull;
-                        u = u24_to_f32(splitmix_output(seed, dn + 1ull));
-                    }
-                    float rr = __fmul_rn(u, total);
-                    F.total = total;
-                    F.u = u;
-                    F.r = rr;
-                    uint32_t flags = LLM_CUDA_ROW_DRAW_CONSUMED;
-                    uint32_t token = 0u;
-                    bool found = false;
-                    for (uint32_t i = 0; i < keep; ++i) {
-                        const float p = __ldcg(&vals[i]);
-                        if (rr < p) {
-                            token = id_at(i);
-                            found = true;
-                            break;
-                        }
-                        rr = __fsub_rn(rr, p);
-                    }
-                    if (!found) {
-                        token = id_at(keep - 1u);
-                        flags |= LLM_CUDA_ROW_FALLBACK_LAST;
-                    }
-                    F.token = token;
-                    F.flags = flags;
-                    F.keep = keep;
-                    F.kept_n = keep;
-                }
-            }
-        }
-        __syncthreads();
-        const uint32_t flags = F.flags | LLM_CUDA_ROW_FULL_SORT;
-        if (tid == 0) {
-            P.tokens[b] = F.token;
-            if (P.row_flags) P.row_flags[b] = flags;
-            if (P.kept_count) P.kept_count[b] = F.kept_n;
-            if (P.row_stats) {
-                float* st = P.row_stats + (size_t)b * LLM_CUDA_ROW_STATS;
-                st[0] = mx;
-                st[1] = F.sum;
-                st[2] = F.total;
-                st[3] = F.u;
-                st[4] = F.thr;
-                st[5] = F.r;
-            }
-        }
-        if (P.kept_cap && (flags & LLM_CUDA_ROW_DRAW_CONSUMED)) {
-            const uint32_t lim = min(F.keep, P.kept_cap);
-            for (uint32_t i = tid; i < lim; i += FULL_THREADS) {
-                if (P.kept_ids) P.kept_ids[(size_t)b * P.kept_cap + i] = id_at(i);
-                if (P.kept_probs) P.kept_probs[(size_t)b * P.kept_cap + i] = __ldcg(&vals[i]);
-            }
-        }
-        __syncthreads();
-    }
-    // the last CTA to leave re-arms the row list for the next launch
-    __syncthreads();
-    if (tid == 0) {
-        __threadfence();
-        const uint32_t t = atomicAdd(ticket, 1u);
-        if (t == gridDim.x - 1u) {
-            *P.full_count = 0u;
-            *ticket = 0u;
-            __threadfence();
-        }
-    }
+    // the logits of a gathered row live on other GPUs: a row its lists cannot decide is reported
+    if (finish_row(P, b, rc, n, overflow, qmax, S, cand_q, cand_i, scratch) && threadIdx.x == 0) report_unresolved(P, b);
 }
 
 // ---------------------------------------------------------------------------
@@ -1178,8 +1250,8 @@ int plan_launch(const DeviceInfo& dev, const KParams& base, bool top_k_known, ui
         // ... on top of the compaction trigger and of the penalised ids, which are appended before the stream
         uint32_t hist = 0u;
         if (base.history != nullptr) hist = base.hist_len_rows ? base.hist_stride : base.hist_len;
-        plan->limit = 2u * kcap;
-        plan->ccap = (2u * kcap > hist ? 2u * kcap : hist) + 32u + tile;
+        plan->limit = 2u * kcap > 1024u ? 2u * kcap : 1024u;  // the refreshed bound keeps lists short; compaction is the exception
+        plan->ccap = (plan->limit > hist ? plan->limit : hist) + 32u + tile;
         if (plan->ccap < WINDOW_CAP) plan->ccap = WINDOW_CAP;  // rows with top_k 0 may be mixed in
     }
     plan->bits = (base.allowed_bits != nullptr) || (base.history != nullptr && (base.r_rows != nullptr || base.penalty != 1.0f) &&
@@ -1241,44 +1313,51 @@ cudaError_t configure_kernels(size_t max_dyn_smem) {
     if ((e = configure_stream<uint16_t, false>(v)) != cudaSuccess) return e;
     if ((e = configure_stream<uint16_t, true>(v)) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(merge_draw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, v)) != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute(full_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, v)) != cudaSuccess) return e;
     return cudaSuccess;
 }
 
 template <typename ElemT, bool BITS, int MODE>
-static cudaError_t launch_stream_t(const KParams& P, const LaunchPlan& plan, cudaStream_t stream) {
+static cudaError_t launch_stream_t(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap) {
     auto kern = stream_select_kernel<ElemT, BITS, MODE>;
     dim3 grid(plan.split, P.batch, 1);
-    kern<<<grid, STREAM_THREADS, plan.smem, stream>>>(P);
-    return cudaGetLastError();
+    if (!overlap) {
+        kern<<<grid, STREAM_THREADS, plan.smem, stream>>>(P);
+        return cudaGetLastError();
+    }
+    // programmatic dependent launch: the grid may start while the previous kernel of the stream is
+    // still running, if that kernel allows it (this kernel does, at its first instruction); it reads
+    // only its inputs until its dependency wait, which returns once the previous grid has finished
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(STREAM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = plan.smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, P);
 }
 
 template <typename ElemT, bool BITS>
-static cudaError_t launch_stream_m(const KParams& P, const LaunchPlan& plan, cudaStream_t stream) {
-    if (plan.mode == 1) return launch_stream_t<ElemT, BITS, 1>(P, plan, stream);
-    if (plan.mode == 2) return launch_stream_t<ElemT, BITS, 2>(P, plan, stream);
-    return launch_stream_t<ElemT, BITS, 0>(P, plan, stream);
+static cudaError_t launch_stream_m(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap) {
+    if (plan.mode == 1) return launch_stream_t<ElemT, BITS, 1>(P, plan, stream, overlap);
+    if (plan.mode == 2) return launch_stream_t<ElemT, BITS, 2>(P, plan, stream, overlap);
+    return launch_stream_t<ElemT, BITS, 0>(P, plan, stream, overlap);
 }
 
-cudaError_t launch_stream_select(const KParams& P, const LaunchPlan& plan, cudaStream_t stream) {
+cudaError_t launch_stream_select(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap) {
     if (P.dtype == LLM_CUDA_DTYPE_BF16) {
-        return plan.bits ? launch_stream_m<uint16_t, true>(P, plan, stream) : launch_stream_m<uint16_t, false>(P, plan, stream);
+        return plan.bits ? launch_stream_m<uint16_t, true>(P, plan, stream, overlap)
+                         : launch_stream_m<uint16_t, false>(P, plan, stream, overlap);
     }
-    return plan.bits ? launch_stream_m<float, true>(P, plan, stream) : launch_stream_m<float, false>(P, plan, stream);
+    return plan.bits ? launch_stream_m<float, true>(P, plan, stream, overlap) : launch_stream_m<float, false>(P, plan, stream, overlap);
 }
 
 cudaError_t launch_merge_draw(const KParams& P, const LaunchPlan& plan, cudaStream_t stream) {
     const size_t smem = (size_t)RING_STAGES * STAGE_BYTES + (size_t)plan.ccap * 8u;
     merge_draw_kernel<<<P.batch, THREADS, smem, stream>>>(P);
-    return cudaGetLastError();
-}
-
-cudaError_t launch_full_sort(const KParams& P, uint32_t hash_slots, uint32_t nslots, uint64_t* keys, float* vals, uint32_t vpad,
-                             uint32_t* ticket, cudaStream_t stream) {
-    KParams Q = P;
-    Q.hash_slots = hash_slots;
-    const size_t smem = (size_t)hash_slots * 8u;
-    full_sort_kernel<<<nslots, FULL_THREADS, smem, stream>>>(Q, keys, vals, vpad, ticket);
     return cudaGetLastError();
 }
 

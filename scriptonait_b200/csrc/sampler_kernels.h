@@ -52,17 +52,13 @@ struct KParams {
     uint32_t* out_i;
     uint32_t* out_cnt;
     uint32_t out_stride;
-    // rows handed to the full-sort kernel
-    uint32_t* full_list;
-    uint32_t* full_count;
     uint32_t force_full;
-    // full-sort stage, launched from the device (tail launch) by the first CTA that hands a row over
-    unsigned long long* full_keys;
-    float* full_vals;
-    uint32_t* full_ticket;
-    uint32_t full_vpad, full_nslots, full_hash_slots;
-    uint32_t tail_launch;           // 1: the streaming kernel launches the full-sort kernel itself when a row needs it
-    uint32_t* device_errors;        // bit 0: a bulk copy did not complete within the wait limit
+    // full ordering of the rare rows the stream cannot decide: scratch slots claimed by the row's own CTA
+    unsigned long long* full_keys;  // [full_nslots][full_vpad] 64-bit sort keys, or NULL = no such stage
+    float* full_vals;               // [full_nslots][full_vpad]
+    uint32_t* full_slots;           // [full_nslots] 0 = free, 1 = taken; all zero between launches
+    uint32_t full_vpad, full_nslots;
+    uint32_t* device_errors;        // bit 0: a bulk copy did not complete within the wait limit; bit 1: no full-sort slot came free
     unsigned long long* phase_ns;   // optional [CTAs][8] phase timestamps (development aid), or NULL
 };
 
@@ -86,10 +82,10 @@ cudaError_t configure_kernels(size_t max_dyn_smem);
 int plan_launch(const DeviceInfo& dev, const KParams& base, bool top_k_known, uint32_t top_k_hint, uint32_t max_top_k,
                 uint32_t max_history, uint32_t requested_split, uint32_t max_lists, LaunchPlan* plan);
 
-cudaError_t launch_stream_select(const KParams& P, const LaunchPlan& plan, cudaStream_t stream);
+// `overlap`: launch with programmatic stream serialization, so the grid may begin reading its inputs
+// while the previous kernel of the stream (if it is this kernel too) is still finishing.
+cudaError_t launch_stream_select(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap = false);
 cudaError_t launch_merge_draw(const KParams& P, const LaunchPlan& plan, cudaStream_t stream);
-cudaError_t launch_full_sort(const KParams& P, uint32_t hash_slots, uint32_t nslots, uint64_t* keys, float* vals, uint32_t vpad,
-                             uint32_t* ticket, cudaStream_t stream);
 cudaError_t launch_advance_rows(uint32_t batch, const uint32_t* tokens, const uint32_t* row_flags, uint32_t* history,
                                 uint32_t history_stride, uint32_t window, uint32_t* history_len, uint32_t* history_pos,
                                 uint64_t* draw_index, uint8_t* finished, uint32_t eos_id, cudaStream_t stream);

@@ -216,13 +216,16 @@ class Sampler:
                      allowed_bits=None, allowed_len: Optional[int] = None, eos_id: int = EOS, seeds=None,
                      draw_index=None, seed_base: int = 0, uniforms=None, batch: Optional[int] = None,
                      row_stride: Optional[int] = None, trace: bool = False, kept_capacity: int = 64, split: int = 0,
-                     force_full_sort: bool = False, out_tokens=None, stream=None, prepare_only: bool = False):
+                     force_full_sort: bool = False, out_tokens=None, stream=None, prepare_only: bool = False,
+                     overlap_previous: bool = False):
         """Row r of `logits` ([B, V] CUDA tensor, float32 / bfloat16 / uint16 bf16 bits) is one
         `sample_with` call with Rng::seed_from_u64(seeds[r]) advanced by draw_index[r] outputs.
         Parameters are scalars or per-row arrays. Asynchronous on the current (or given) stream.
         With `prepare_only` nothing is launched: the returned PreparedCall re-issues the same call
         (same buffers, same stream) with one C-ABI call per `launch()`, which is what a decode
-        loop over fixed buffers wants."""
+        loop over fixed buffers wants. `overlap_previous` lets the launch begin reading its inputs
+        while the previous sample_batch launch on the stream is finishing (outputs keep stream
+        order); only for calls whose inputs that previous call does not write."""
         torch = _torch()
         assert logits.is_cuda and logits.dim() == 2 and logits.stride(1) == 1, "logits: [B, V] CUDA tensor, unit column stride"
         if logits.dtype == torch.float32:
@@ -242,6 +245,7 @@ class Sampler:
                             allowed_bits=allowed_bits, allowed_len=allowed_len, eos_id=eos_id, seeds=seeds,
                             draw_index=draw_index, seed_base=seed_base, uniforms=uniforms, split=split,
                             force_full_sort=force_full_sort, stream=st, keep=keep)
+        a.overlap_previous = 1 if overlap_previous else 0
         res = self._outputs(a, B, trace, kept_capacity, out_tokens, logits.device)
         res._keepalive = keep  # inputs must outlive the asynchronous launch
         call = PreparedCall(self, a, res)
