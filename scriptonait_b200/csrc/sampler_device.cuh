@@ -569,10 +569,17 @@ __device__ __forceinline__ void ordered_tail(const KParams& P, uint32_t b, const
     cta_sync();
 }
 
+// Programmatic dependent launch. Both are no-ops for a grid launched the ordinary way. A grid that
+// was allowed to start before its predecessor on the stream finished must pass the wait before it
+// writes global memory or touches scratch the two grids share.
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // Writes the row's results. `listed` = how many kept entries cand/probs hold.
 __device__ __forceinline__ void write_row_outputs(const KParams& P, uint32_t b, uint32_t extra_flags, const Shared& S,
                                                   float mx, const uint32_t* cand_i, const float* probs, uint32_t listed) {
     const uint32_t flags = S.out_flags | extra_flags;
+    grid_dependency_wait();
     if (threadIdx.x == 0) {
         P.tokens[b] = S.token;
         if (P.row_flags) P.row_flags[b] = flags;

@@ -126,10 +126,6 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     return false;
 }
 
-// Programmatic dependent launch. Both are no-ops for a grid launched the ordinary way.
-__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-
 __device__ __forceinline__ unsigned long long global_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -218,6 +214,7 @@ __device__ bool finish_row(const KParams& P, uint32_t b, const RowCfg& rc, uint3
     const uint32_t n_use = min(n, rc.k_eff);
     const bool truncated = rc.windowed && (n_use < rc.k_eff);
     if (P.out_q) {  // vocabulary sharding, step 1: the ordered list is the result
+        grid_dependency_wait();
         for (uint32_t i = threadIdx.x; i < min(n_use, P.out_stride); i += THREADS) {
             P.out_q[(size_t)b * P.out_stride + i] = cand_q[i];
             P.out_i[(size_t)b * P.out_stride + i] = cand_i[i];
@@ -337,6 +334,7 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
     const uint32_t V = P.vocab;
     uint32_t m = 1u;
     while (m < V) m <<= 1;
+    grid_dependency_wait();  // the scratch slots are shared with the previous launch
     if (!P.full_keys) {
         if (tid == 0) report_unresolved(P, b);
         return;
@@ -597,9 +595,9 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
     const uint32_t b = blockIdx.y, shard = blockIdx.x, tid = threadIdx.x;
     const unsigned lane = tid & 31u, warp = tid >> 5;
     const uint32_t LOWEST = 0x007fffffu;  // okey(-inf)
-    // A launch that asked to overlap its predecessor may start now. Until grid_dependency_wait()
-    // below, this kernel reads its inputs and writes shared memory only; everything it writes to
-    // global memory (outputs, the scratch rows and tickets the launches of a handle share) comes after.
+    // A launch that asked to overlap its predecessor may start now. This kernel reads its inputs and
+    // writes shared memory only until it has passed grid_dependency_wait(): that comes right before a
+    // row's outputs are written, before the split-row scratch and before the full-ordering scratch.
     grid_launch_dependents();
     if (tid == 0) {
         resolve_row(P, b, S.rc);
@@ -1085,7 +1083,6 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
     }
     PHASE(2);
     if (wait_failed) atomicOr(&S.error, 4u);
-    grid_dependency_wait();  // the previous kernel of the stream is complete from here on
     cta_sync();
 
     uint32_t n = min(S.count, P.ccap);
@@ -1104,6 +1101,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
 
     // ---- several CTAs share the row: leave this shard's survivors in scratch;
     //      the CTA that arrives last merges them (no CTA ever waits for another)
+    grid_dependency_wait();  // the scratch lists and tickets are shared with the previous launch
     if (!rc.windowed) {
         n = keep_top_k(n, rc.k_eff, S, cand_q, cand_i);
     } else if (!overflow) {
