@@ -44,6 +44,11 @@ BATCH, VOCAB = 256, 128256
 N_BUFFERS = 5  # 5 x 65.7 MB of distinct logits > 126 MB of L2
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one c3 launch (65.75 MB + 0.49 MB), from the ncu capture
+# summarised under profiles/; the timed run itself is never profiled
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 66_240_000
+
+
 def measured_hbm_peak():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
@@ -311,9 +316,11 @@ def run_ours(args, rank, world, local_rank):
                        "region_ms_min_median_max": [min(regions), ms_region, max(regions)]},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS, "peak_source": peak_src,
-                         "traffic": None, "algorithmic_bytes_per_launch": alg_bytes,
-                         "note": "duration = whole step (every kernel the call launches), so the fraction is a lower "
-                                 "bound for the streaming kernel alone"},
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "algorithmic_bytes_per_launch": alg_bytes,
+                         "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture "
+                                           "summarised in profiles/stream_select_bf16_c3.md (not measured in this run)",
+                         "note": "duration = timed region / launches (one kernel per step; consecutive launches overlap "
+                                 "unless --strict-order)"},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": "rows/s", "h2d_bytes_per_step": int(batches[0].logits.nbytes + BATCH * 8),
                     "d2h_bytes_per_step": BATCH * 4, "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
