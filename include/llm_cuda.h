@@ -46,7 +46,7 @@ extern "C" {
 #define LLM_CUDA_ROW_DEGENERATE 2u     /* softmax sum <= 0 or not finite: first id of the ordering returned, no draw consumed (generate.rs:375-377) */
 #define LLM_CUDA_ROW_FALLBACK_LAST 4u  /* the walk ran past the kept set: last kept id returned (generate.rs:419) */
 #define LLM_CUDA_ROW_DRAW_CONSUMED 8u  /* exactly one RNG output was used: the caller advances draw_index by one */
-#define LLM_CUDA_ROW_FULL_SORT 16u     /* the row was resolved by the full-sort kernel (candidate window too small) */
+#define LLM_CUDA_ROW_FULL_SORT 16u     /* the row was resolved by ordering the whole row (candidate window too small) */
 #define LLM_CUDA_ROW_INVALID 64u       /* a per-row parameter was NaN; token 0 returned */
 #define LLM_CUDA_ROW_WINDOWED 128u     /* ordering ran on the significant-value window, not on a top-k list */
 
@@ -128,7 +128,7 @@ typedef struct llm_cuda_sample_args {
     uint32_t vocab_global;       /* 0 = vocab */
 
     uint32_t split;              /* CTAs per row; 0 = choose */
-    uint32_t force_full_sort;    /* testing aid: resolve every row with the full-sort kernel */
+    uint32_t force_full_sort;    /* testing aid: resolve every row by ordering the whole row */
     void* stream;                /* cudaStream_t */
 } llm_cuda_sample_args;
 
