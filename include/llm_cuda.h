@@ -137,7 +137,8 @@ void llm_cuda_sampling_config_default(llm_cuda_sampling_config* out);
 
 /* Creates a sampler bound to `device` with scratch sized for the given maxima.
  * Replaces nothing in the reference (it allocates two Vecs per call,
- * generate.rs:331,364); this is where the device scratch those become lives. */
+ * generate.rs:331,364); this is where the device scratch those become lives.
+ * max_batch <= 65535 (LLM_CUDA_ERR_CAPACITY beyond). */
 int32_t llm_cuda_sampler_create(int32_t device, uint32_t max_batch, uint32_t max_vocab, uint32_t max_history,
                                 uint32_t max_top_k, llm_cuda_sampler** out);
 int32_t llm_cuda_sampler_destroy(llm_cuda_sampler* s);

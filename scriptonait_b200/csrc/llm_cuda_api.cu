@@ -246,6 +246,8 @@ int32_t llm_cuda_sampler_create(int32_t device, uint32_t max_batch, uint32_t max
     if (!out) return fail(nullptr, LLM_CUDA_ERR_BAD_ARGUMENT, "out is NULL");
     *out = nullptr;
     if (max_batch == 0 || max_vocab == 0) return fail(nullptr, LLM_CUDA_ERR_BAD_ARGUMENT, "max_batch and max_vocab must be > 0");
+    if (max_batch > 65535u)  // rows are the grid's y dimension
+        return fail(nullptr, LLM_CUDA_ERR_CAPACITY, "max_batch %u exceeds the 65535 rows one launch can take", max_batch);
     int ndev = 0;
     cudaError_t e = cudaGetDeviceCount(&ndev);
     if (e != cudaSuccess || ndev == 0)
