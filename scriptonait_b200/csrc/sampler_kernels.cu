@@ -779,6 +779,9 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
     //      (packed bf16 arithmetic for bf16 rows) and notes the vectors that reach the threshold in
     //      its warp's list, (B) the warp examines its listed vectors 32/VEC at a time.
     bool wait_failed = false;
+    // exact-selection rows with a small rank cut stream like window rows: maxima and flags only
+    const bool sweep_k = !rc.windowed && rc.k_eff <= (uint32_t)THREADS;
+    uint32_t tau_k = LOWEST;  // this warp's view of the running lower bound (ordered key, pre-temperature domain)
 #ifdef LLMC_PROFILE_STAGES
     long long acc[6] = {0, 0, 0, 0, 0, 0};
     long long c_a = clock64(), c_b;
@@ -807,12 +810,15 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
                 if (!BITS) tmax = fmaxf(tmax, m);
             }
             if (BITS) {
-                // a maximum of the edited row is wanted: flagged ids (penalised, blocked) must not count
+                // a maximum of the edited row is wanted: flagged ids (penalised, blocked) must not count.
+                // Only a vector that would raise the lane's maximum is looked up in the bitmap (a lane's
+                // maximum rises O(log n) times over a row); vm[u] stays the raw maximum, which keeps
+                // every test against a threshold below a superset test.
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
-                    const uint32_t j = u * THREADS + tid;
-                    const uint32_t v = t * VPS + j;
-                    if (v < nvi && !wait_failed) {
+                    if (vm[u] > tmax) {
+                        const uint32_t j = u * THREADS + tid;
+                        const uint32_t v = t * VPS + j;
                         const uint32_t j2 = head + v * VEC + lead;
                         const uint32_t nib = (bitmap[j2 >> 5] >> (j2 & 31u)) & ((1u << VEC) - 1u);
                         float m = vm[u];
@@ -825,11 +831,12 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
                                 if (!((nib >> e) & 1u)) m = fmaxf(m, x[e]);
                         }
                         tmax = fmaxf(tmax, m);
-                        vm[u] = m;
                     }
                 }
             }
-            if (max_sweep) {
+            if (max_sweep || sweep_k) {
+              float tau_run;
+              if (max_sweep) {
                 // the running maximum gives a running threshold; each group of 32 vectors (one warp
                 // step) records which of its vectors reach it - a superset of those that will reach
                 // the final threshold, since the maximum only rises
@@ -849,38 +856,39 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
                     const float qmax1 = temper(okey_to_float(max(prev, wk)), T);
                     atomicMax(&S.tau_key, raw_threshold_key(window_stream_bound(qmax1), T));
                 }
-                const float tau_run = okey_to_float(vol_load(&S.tau_key));
+                tau_run = okey_to_float(vol_load(&S.tau_key));
+              } else {
+                // Exact-selection rows with k <= 256: a lower bound of the k-th largest value of the row
+                // from the lanes' running maxima. Each lane's maximum is an element of the edited row
+                // and the lanes' elements are disjoint, so the r-th largest lane maximum of a warp has
+                // >= r elements at or above it, and the minimum over the warps of those (r = ceil(k/8))
+                // has >= k. Maxima only rise, so a warp may combine its fresh value with whatever the
+                // other warps published last: no barrier after the first stage. The bound is refreshed
+                // at stages 0-4, 6, 8, 12, 16, ... (the gain of a refresh falls off as 1/stage).
+                const uint32_t h3 = tt / 3u;
+                const bool refresh = tt < 4u || (tt & (tt - 1u)) == 0u || (tt == 3u * h3 && (h3 & (h3 - 1u)) == 0u);
+                if (refresh) {
+                    const uint32_t r = (rc.k_eff + WARPS - 1u) / WARPS;
+                    const uint32_t kth = warp_rth_largest(okey(tmax), r, lane);
+                    if (lane == 0) *(volatile uint32_t*)&S.wkth[warp] = kth;
+                    if (tt == 0) cta_sync();  // every warp has published once
+                    else __syncwarp();
+                    const uint32_t lo = __reduce_min_sync(FULL_MASK, vol_load(&S.wkth[lane & (WARPS - 1u)]));
+                    tau_k = max(tau_k, max(lo, LOWEST));
+                }
+                tau_run = okey_to_float(tau_k);
+              }
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
-                    // vm[u] is the lane's maximum over unflagged elements when BITS (recomputed above)
+                    // the raw maximum of the vector: a superset test
                     const unsigned gm = __ballot_sync(FULL_MASK, vm[u] >= tau_run);
                     if (lane == 0) grp_max[(t * U + u) * WARPS + warp] = gm;
                 }
-                // window rows run the sweep without CTA barriers: the warp releases the stage and goes on
+                // these rows run the sweep without CTA barriers: the warp releases the stage and goes on
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty_bar[stage]);
                 continue;
             } else {
-                if (rc.k_eff <= (uint32_t)THREADS) {
-                    // A lower bound for the k-th largest value of the row, refreshed every stage from the
-                    // lanes' running maxima: each lane's maximum is an element of the edited row, so the
-                    // r-th largest lane maximum of a warp has >= r elements at or above it, and the
-                    // minimum over the warps of those bounds has >= WARPS*r >= k. The bound rises as the
-                    // lanes see more of the row, which keeps the candidate list short without compaction.
-                    const uint32_t r = (rc.k_eff + WARPS - 1u) / WARPS;
-                    const uint32_t kth = warp_rth_largest(okey(tmax), r, lane);
-                    if (lane == 0) S.wkth[warp] = kth;
-                    if (tt == 0) {  // before anything of the first stage is appended
-                        cta_sync();
-                        if (tid == 0) {
-                            uint32_t lo = S.wkth[0];
-#pragma unroll
-                            for (int w = 1; w < WARPS; ++w) lo = min(lo, S.wkth[w]);
-                            S.tau_key = max(lo, LOWEST);
-                        }
-                        cta_sync();
-                    }
-                }
                 TICK(1);
                 const float tau = okey_to_float(vol_load(&S.tau_key));
                 // this warp's list of vectors that hold a passing value ...
@@ -929,12 +937,6 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
         TICK(2);
         const int over = cta_sync_or(end > P.limit ? 1 : 0);
         TICK(3);
-        if (!rc.windowed && rc.k_eff <= (uint32_t)THREADS && tid == 0) {
-            uint32_t lo = S.wkth[0];  // written before the barrier; a later, larger value is just as valid
-#pragma unroll
-            for (int w = 1; w < WARPS; ++w) lo = min(lo, S.wkth[w]);
-            if (lo > S.tau_key) S.tau_key = lo;
-        }
         if (over) {
             uint32_t n = min(S.count, P.ccap);
             cta_sync();
@@ -976,18 +978,33 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
         o[6] = vtiles; o[7] = S.count;
     }
 #endif
-    if (rc.windowed) {
-        // the row's maximum fixes the threshold; the vectors noted during the sweep are read again
-        // (from L2) and their elements tested against the exact window
+    if (rc.windowed || sweep_k) {
+        // the sweep fixed the threshold; the vectors noted during the sweep are read again (from L2)
+        // and their elements tested exactly
         const uint32_t unfiltered = S.count;  // leading / trailing elements and penalised ids, appended before the sweep
+        if (sweep_k) {
+            // every lane's final maximum goes into its warp's bound
+            const uint32_t r = (rc.k_eff + WARPS - 1u) / WARPS;
+            const uint32_t kth = warp_rth_largest(okey(tmax), r, lane);
+            if (lane == 0) S.wkth[warp] = kth;
+        }
         if (tid == 0) {
             S.keep = 0u;
             S.last = 0u;
         }
         cta_sync();
-        // every thread derives the final threshold from the row's maximum itself
+        // every thread derives the final threshold itself: from the row's maximum (window rows), or
+        // as the minimum of the warps' bounds (a lower bound of the k-th largest value)
         const float qmaxf = temper(okey_to_float(S.max_key), T);
-        const float tau = okey_to_float(raw_threshold_key(window_stream_bound(qmaxf), T));
+        float tau;
+        if (sweep_k) {
+            uint32_t lo = S.wkth[0];
+#pragma unroll
+            for (int w = 1; w < WARPS; ++w) lo = min(lo, S.wkth[w]);
+            tau = okey_to_float(max(lo, LOWEST));
+        } else {
+            tau = okey_to_float(raw_threshold_key(window_stream_bound(qmaxf), T));
+        }
         const uint32_t ngroups = (nvi + 31u) / 32u;
         const uint4* gv = reinterpret_cast<const uint4*>(vbase);
         uint32_t* vlist = reinterpret_cast<uint32_t*>(ring);  // the ring is idle now
@@ -1035,7 +1052,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
                 for (int e = 0; e < VEC; ++e) {
                     if (x[e] >= tau && !((nib >> e) & 1u)) {
                         x[e] = temper(x[e], T);
-                        if ((__fsub_rn(x[e], qmaxf) >= WINDOW_EXACT) || (x[e] == qmaxf)) em |= 1u << e;  // exactly the terms the reference's sums can see
+                        // window rows: exactly the terms the reference's sums can see
+                        if (sweep_k || (__fsub_rn(x[e], qmaxf) >= WINDOW_EXACT) || (x[e] == qmaxf)) em |= 1u << e;
                     }
                 }
             }
@@ -1065,21 +1083,42 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
                 }
             }
         };
+        // Exact-selection rows check the buffer after every round of 256 vectors (at most 256*VEC new
+        // entries, which the buffer has room for beyond `limit`) and keep the best k when it fills;
+        // `tau` then rises to the k-th value, in every thread alike. Window rows that overflow are
+        // ordered in full instead.
+        auto settle = [&]() {
+            if (!sweep_k) return;
+            const int over = cta_sync_or(vol_load(&S.count) > P.limit ? 1 : 0);
+            if (!over) return;
+            uint32_t n2 = min(S.count, P.ccap);
+            cta_sync();
+            if (n2 > rc.k_eff) {
+                n2 = keep_top_k(n2, rc.k_eff, S, cand_q, cand_i);
+                if (tid == 0) S.count = n2;
+                cta_sync();
+                tau = fmaxf(tau, okey_to_float(raw_threshold_key(okey_to_float(S.minkey), T)));
+            }
+            cta_sync();
+        };
         if (nq <= VLIST_CAP) {
             for (uint32_t i0 = 0; i0 < nq; i0 += THREADS) {
                 const uint32_t i = i0 + tid;
                 const uint32_t v = i < nq ? vlist[i] : 0xffffffffu;
                 examine(v < nvi, v);
+                settle();
             }
         } else {
-            for (uint32_t g = warp; g < ngroups; g += WARPS) {
-                const unsigned m = grp_max[g];  // same word for the whole warp
+            for (uint32_t g0 = 0; g0 < ngroups; g0 += WARPS) {
+                const uint32_t g = g0 + warp;
+                const unsigned m = g < ngroups ? grp_max[g] : 0u;  // same word for the whole warp
                 const uint32_t v = g * 32u + lane;
                 examine(((m >> lane) & 1u) && v < nvi, v);
+                settle();
             }
         }
         cta_sync();
-        window_filtered = (unfiltered == 0u) && P.split == 1u;
+        window_filtered = rc.windowed && (unfiltered == 0u) && P.split == 1u;
     }
     PHASE(2);
     if (wait_failed) atomicOr(&S.error, 4u);
@@ -1244,13 +1283,18 @@ int plan_launch(const DeviceInfo& dev, const KParams& base, bool top_k_known, ui
         plan->ccap = WINDOW_CAP;
         plan->limit = WINDOW_CAP / 2u;
     } else {
-        // a tile can append at most `tile` entries, so the buffer never overflows between two checks
-        // ... on top of the compaction trigger and of the penalised ids, which are appended before the stream
+        // between two checks of the buffer at most `room` entries are appended: a whole stage for rows
+        // that append while they stream (rank cut above 256), one round of 256 vectors for rows that
+        // only flag vectors while they stream - on top of the compaction trigger and of the penalised
+        // ids, which are appended before the stream
         uint32_t hist = 0u;
         if (base.history != nullptr) hist = base.hist_len_rows ? base.hist_stride : base.hist_len;
-        plan->limit = 2u * kcap > 1024u ? 2u * kcap : 1024u;  // the refreshed bound keeps lists short; compaction is the exception
-        plan->ccap = (plan->limit > hist ? plan->limit : hist) + 32u + tile;
-        if (plan->ccap < WINDOW_CAP) plan->ccap = WINDOW_CAP;  // rows with top_k 0 may be mixed in
+        const uint32_t vec_elems0 = 16u / (base.dtype == LLM_CUDA_DTYPE_BF16 ? 2u : 4u);
+        const bool small_k = top_k_known && kcap <= (uint32_t)THREADS;
+        const uint32_t room = small_k ? (uint32_t)THREADS * vec_elems0 : tile;
+        plan->limit = 2u * kcap > 1024u ? 2u * kcap : 1024u;
+        plan->ccap = (plan->limit > hist ? plan->limit : hist) + 32u + room;
+        if (plan->ccap < WINDOW_CAP && !top_k_known) plan->ccap = WINDOW_CAP;  // rows with top_k 0 may be mixed in
     }
     plan->bits = (base.allowed_bits != nullptr) || (base.history != nullptr && (base.r_rows != nullptr || base.penalty != 1.0f) &&
                                                     (base.hist_len_rows != nullptr || base.hist_len > 0u));
@@ -1280,15 +1324,21 @@ int plan_launch(const DeviceInfo& dev, const KParams& base, bool top_k_known, ui
     plan->shard_cols = shard_cols;
     if (plan->bits) {
         plan->bitmap_words = (shard_cols + 8u + 31u) / 32u + 1u;
-        plan->hash_slots = pow2_ceil(2u * (max_history ? max_history : 1u));
+        // sized for this launch's longest history (the handle's maximum when rows bring their own lengths)
+        uint32_t hmax = max_history ? max_history : 1u;
+        if (base.history != nullptr) {
+            const uint32_t hl = base.hist_len_rows ? base.hist_stride : base.hist_len;
+            if (hl > 0u && hl < hmax) hmax = hl;
+        }
+        plan->hash_slots = pow2_ceil(2u * hmax);
         if (plan->hash_slots < 64u) plan->hash_slots = 64u;
     } else {
         plan->bitmap_words = 0u;
         plan->hash_slots = 0u;
     }
-    // window-mode rows keep one word per group of 32 vectors of the shard
+    // one flag word per group of 32 vectors of the shard
     const uint32_t vec_elems = 16u / (base.dtype == LLM_CUDA_DTYPE_BF16 ? 2u : 4u);
-    plan->groups = (window_only || !top_k_known) ? (shard_cols / vec_elems + 31u) / 32u + WARPS * (STAGE_BYTES / 16u / THREADS) : 0u;
+    plan->groups = (shard_cols / vec_elems + 31u) / 32u + WARPS * (STAGE_BYTES / 16u / THREADS);
     plan->smem = (size_t)RING_STAGES * STAGE_BYTES + (size_t)plan->ccap * 8u + (size_t)plan->bitmap_words * 4u +
                  (size_t)plan->hash_slots * 8u + (size_t)plan->groups * 4u;
     if (plan->smem > dev.max_dyn_smem) return -1;
