@@ -583,14 +583,14 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
     __shared__ Shared S;
     __shared__ __align__(8) uint64_t full_bar[RING_STAGES];   // a stage's bytes have landed
     __shared__ __align__(8) uint64_t empty_bar[RING_STAGES];  // all consumer warps are done with a stage
-    __shared__ uint16_t hit_list[WARPS][U * 32];  // per warp: stage-relative vector numbers that hold a passing value
     unsigned char* ring = dyn;
     float* cand_q = reinterpret_cast<float*>(dyn + RING_STAGES * STAGE_BYTES);
     uint32_t* cand_i = reinterpret_cast<uint32_t*>(cand_q + P.ccap);
     uint32_t* bitmap = cand_i + P.ccap;
     uint32_t* hkeys = bitmap + P.bitmap_words;
     uint32_t* hcnt = hkeys + P.hash_slots;
-    uint32_t* grp_max = hcnt + P.hash_slots;  // window-mode rows: ordered key of each 32-vector group's maximum
+    float* lane_top = reinterpret_cast<float*>(hcnt + P.hash_slots);  // rank cuts above 256: every lane's best values
+    uint32_t* grp_max = reinterpret_cast<uint32_t*>(lane_top + P.lane_top_words);  // one flag word per 32 vectors
 
     const uint32_t b = blockIdx.y, shard = blockIdx.x, tid = threadIdx.x;
     const unsigned lane = tid & 31u, warp = tid >> 5;
@@ -770,58 +770,74 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
         warp_append(valid && x >= neg_inf(), temper(x, T), gid0 + rel, S, cand_q, cand_i, P.ccap, end);
     }
 
-    // ---- the stream.
-    //      Window-mode rows: one sweep that only takes maxima - per thread for the row's maximum,
-    //      per group of 32 vectors (one warp step, 512 bytes) into `grp_max`. When the sweep ends
-    //      the threshold max - 17.5 is exact wherever in the row the maximum sat, and only the
-    //      groups whose maximum reaches it (a few per cent of the row) are read again, from L2.
-    //      Other rows: per stage, (A) every lane takes the maximum of each of its 16-byte vectors
-    //      (packed bf16 arithmetic for bf16 rows) and notes the vectors that reach the threshold in
-    //      its warp's list, (B) the warp examines its listed vectors 32/VEC at a time.
+    // ---- the stream: one sweep without CTA barriers (after the first stage) that only takes maxima
+    //      and flags. Every lane takes the maximum of each of its 16-byte vectors (packed bf16
+    //      arithmetic for bf16 rows); one ballot word per warp step (32 vectors, 512 bytes) records
+    //      which vectors reach the running threshold - a superset of those that reach the final one,
+    //      because the threshold only rises. Afterwards only the flagged vectors (a few per cent of
+    //      the row) are read again, from L2, against the final threshold.
+    //      Window rows: threshold = running maximum - 17.5 (exact once the sweep has seen the row).
+    //      Exact-selection rows: a running lower bound of the k-th largest value. The lanes' elements
+    //      are disjoint, so each lane's m best vector maxima are m distinct elements of the edited row:
+    //        k <= 256 (m = 1): the r-th largest lane maximum of a warp has >= r elements at or above
+    //          it, and the minimum over the warps of those (r = ceil(k/8)) has >= k;
+    //        k  > 256 (m = ceil(k/256) <= 8, kept sorted in shared memory): the minimum over all
+    //          lanes of the lane's m-th best has >= 256*m >= k elements at or above it.
+    //      Lane values only rise, so a warp combines its fresh value with whatever the other warps
+    //      published last: no barrier. The bound is refreshed at stages 0-4, 6, 8, 12, 16, ... (the
+    //      gain of a refresh falls off as 1/stage).
     bool wait_failed = false;
-    // exact-selection rows with a small rank cut stream like window rows: maxima and flags only
-    const bool sweep_k = !rc.windowed && rc.k_eff <= (uint32_t)THREADS;
+    const bool sweep_k = !rc.windowed;
+    const uint32_t m_lane = sweep_k ? (rc.k_eff + (uint32_t)THREADS - 1u) / (uint32_t)THREADS : 1u;  // 1..8
     uint32_t tau_k = LOWEST;  // this warp's view of the running lower bound (ordered key, pre-temperature domain)
-#ifdef LLMC_PROFILE_STAGES
-    long long acc[6] = {0, 0, 0, 0, 0, 0};
-    long long c_a = clock64(), c_b;
-#define TICK(k) do { c_b = clock64(); acc[k] += c_b - c_a; c_a = c_b; } while (0)
-#else
-#define TICK(k) do { } while (0)
-#endif
-    for (uint32_t tt = 0; tt <= vtiles; ++tt) {
-        // iteration tt == vtiles only settles the buffer
-        const bool max_sweep = rc.windowed != 0u;  // window-mode rows only take maxima here
+    float lmin = neg_inf();   // m_lane > 1: the lane's m-th best so far
+    if (m_lane > 1u)
+        for (uint32_t i = 0; i < m_lane; ++i) lane_top[i * THREADS + tid] = neg_inf();
+    // the lane's m best, descending, in lane_top[i*THREADS + tid]; returns the new m-th best
+    auto lane_insert = [&](float v) {
+        for (uint32_t i = 0; i < m_lane; ++i) {
+            const float cur = lane_top[i * THREADS + tid];
+            if (v > cur) {
+                lane_top[i * THREADS + tid] = v;
+                v = cur;
+            }
+        }
+        return lane_top[(m_lane - 1u) * THREADS + tid];
+    };
+    // this warp's share of the bound, from the lanes' current values
+    auto warp_bound = [&]() -> uint32_t {
+        if (m_lane > 1u) return __reduce_min_sync(FULL_MASK, okey(lmin));
+        return warp_rth_largest(okey(tmax), (rc.k_eff + WARPS - 1u) / WARPS, lane);
+    };
+    for (uint32_t tt = 0; tt < vtiles; ++tt) {
         const uint32_t t = tt;
-        if (tt < vtiles) {
-            const uint32_t stage = tt % RING_STAGES;
-            TICK(5);
-            if (!mbar_wait_bounded(&full_bar[stage], (tt / RING_STAGES) & 1u)) wait_failed = true;
-            TICK(0);
-            const uint4* sv = reinterpret_cast<const uint4*>(ring + (size_t)stage * STAGE_BYTES);
-            float vm[U];
+        const uint32_t stage = tt % RING_STAGES;
+        if (!mbar_wait_bounded(&full_bar[stage], (tt / RING_STAGES) & 1u)) wait_failed = true;
+        const uint4* sv = reinterpret_cast<const uint4*>(ring + (size_t)stage * STAGE_BYTES);
+        float vm[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint32_t j = u * THREADS + tid;
+            const uint32_t v = t * VPS + j;
+            float m = __uint_as_float(0x7fc00000u);  // NaN: an absent vector never passes and never raises a maximum
+            if (v < nvi && !wait_failed) m = vector_max<ElemT>(sv[j]);
+            vm[u] = m;  // of the raw values; NaN elements are ignored by the maxima
+            if (!BITS && m_lane == 1u) tmax = fmaxf(tmax, m);
+        }
+        if (BITS || m_lane > 1u) {
+            // A value of the edited row is wanted: flagged ids (penalised, blocked) must not count.
+            // Only a vector that would change the lane's state is looked up in the bitmap (a lane's
+            // best values change O(m log n) times over a row); vm[u] stays the raw maximum, which
+            // keeps every test against a threshold below a superset test.
 #pragma unroll
             for (int u = 0; u < U; ++u) {
-                const uint32_t j = u * THREADS + tid;
-                const uint32_t v = t * VPS + j;
-                float m = __uint_as_float(0x7fc00000u);  // NaN: an absent vector never passes and never raises a maximum
-                if (v < nvi && !wait_failed) m = vector_max<ElemT>(sv[j]);
-                vm[u] = m;  // of the raw values; NaN elements are ignored by the maxima
-                if (!BITS) tmax = fmaxf(tmax, m);
-            }
-            if (BITS) {
-                // a maximum of the edited row is wanted: flagged ids (penalised, blocked) must not count.
-                // Only a vector that would raise the lane's maximum is looked up in the bitmap (a lane's
-                // maximum rises O(log n) times over a row); vm[u] stays the raw maximum, which keeps
-                // every test against a threshold below a superset test.
-#pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    if (vm[u] > tmax) {
+                if (vm[u] > ((m_lane > 1u) ? lmin : tmax)) {
+                    float m = vm[u];
+                    if (BITS) {
                         const uint32_t j = u * THREADS + tid;
                         const uint32_t v = t * VPS + j;
                         const uint32_t j2 = head + v * VEC + lead;
                         const uint32_t nib = (bitmap[j2 >> 5] >> (j2 & 31u)) & ((1u << VEC) - 1u);
-                        float m = vm[u];
                         if (nib) {
                             float x[VEC];
                             unpack<ElemT>(sv[j], x);
@@ -830,162 +846,98 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
                             for (int e = 0; e < VEC; ++e)
                                 if (!((nib >> e) & 1u)) m = fmaxf(m, x[e]);
                         }
+                    }
+                    if (m_lane > 1u) {
+                        if (m > lmin) lmin = lane_insert(m);
+                    } else {
                         tmax = fmaxf(tmax, m);
                     }
                 }
             }
-            if (max_sweep || sweep_k) {
-              float tau_run;
-              if (max_sweep) {
-                // the running maximum gives a running threshold; each group of 32 vectors (one warp
-                // step) records which of its vectors reach it - a superset of those that will reach
-                // the final threshold, since the maximum only rises
-                const uint32_t wk = __reduce_max_sync(FULL_MASK, okey(tmax));
-                if (tt == 0) {
-                    if (lane == 0) atomicMax(&S.max_key, wk);
-                    cta_sync();
-                    if (tid == 0) {
-                        const float qmax0 = temper(okey_to_float(S.max_key), T);
-                        S.tau_key = raw_threshold_key(window_stream_bound(qmax0), T);
-                    }
-                    cta_sync();
-                } else if (lane == 0 && wk > vol_load(&S.max_key)) {
-                    // the maximum rose: this warp tightens the shared threshold itself (monotone, so
-                    // warps that still read the old value only keep a superset)
-                    const uint32_t prev = atomicMax(&S.max_key, wk);
-                    const float qmax1 = temper(okey_to_float(max(prev, wk)), T);
-                    atomicMax(&S.tau_key, raw_threshold_key(window_stream_bound(qmax1), T));
-                }
-                tau_run = okey_to_float(vol_load(&S.tau_key));
-              } else {
-                // Exact-selection rows with k <= 256: a lower bound of the k-th largest value of the row
-                // from the lanes' running maxima. Each lane's maximum is an element of the edited row
-                // and the lanes' elements are disjoint, so the r-th largest lane maximum of a warp has
-                // >= r elements at or above it, and the minimum over the warps of those (r = ceil(k/8))
-                // has >= k. Maxima only rise, so a warp may combine its fresh value with whatever the
-                // other warps published last: no barrier after the first stage. The bound is refreshed
-                // at stages 0-4, 6, 8, 12, 16, ... (the gain of a refresh falls off as 1/stage).
-                const uint32_t h3 = tt / 3u;
-                const bool refresh = tt < 4u || (tt & (tt - 1u)) == 0u || (tt == 3u * h3 && (h3 & (h3 - 1u)) == 0u);
-                if (refresh) {
-                    const uint32_t r = (rc.k_eff + WARPS - 1u) / WARPS;
-                    const uint32_t kth = warp_rth_largest(okey(tmax), r, lane);
-                    if (lane == 0) *(volatile uint32_t*)&S.wkth[warp] = kth;
-                    if (tt == 0) cta_sync();  // every warp has published once
-                    else __syncwarp();
-                    const uint32_t lo = __reduce_min_sync(FULL_MASK, vol_load(&S.wkth[lane & (WARPS - 1u)]));
-                    tau_k = max(tau_k, max(lo, LOWEST));
-                }
-                tau_run = okey_to_float(tau_k);
-              }
-#pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    // the raw maximum of the vector: a superset test
-                    const unsigned gm = __ballot_sync(FULL_MASK, vm[u] >= tau_run);
-                    if (lane == 0) grp_max[(t * U + u) * WARPS + warp] = gm;
-                }
-                // these rows run the sweep without CTA barriers: the warp releases the stage and goes on
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&empty_bar[stage]);
-                continue;
-            } else {
-                TICK(1);
-                const float tau = okey_to_float(vol_load(&S.tau_key));
-                // this warp's list of vectors that hold a passing value ...
-                uint32_t wcnt = 0u;
-#pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    const bool hit = vm[u] >= tau;
-                    const unsigned pm = __ballot_sync(FULL_MASK, hit);
-                    if (hit) hit_list[warp][wcnt + (uint32_t)__popc(pm & ((1u << lane) - 1u))] = (uint16_t)(u * THREADS + tid);
-                    wcnt += (uint32_t)__popc(pm);
-                }
-                if (wcnt) {
-                    // ... examined by the warp itself, 32/VEC vectors at a time: lane l looks at element
-                    // l % VEC of list entry l / VEC, so no lane runs a long divergent path and warps
-                    // without a passing value skip all of this
-                    __syncwarp();
-                    constexpr uint32_t G = 32u / VEC;
-                    for (uint32_t g0 = 0; g0 < wcnt; g0 += G) {
-                        const uint32_t g = g0 + lane / VEC, e = lane % VEC;
-                        float x = __uint_as_float(0x7fc00000u);
-                        uint32_t rel = 0u;
-                        if (g < wcnt) {
-                            const uint32_t j = hit_list[warp][g];
-                            rel = head + (t * VPS + j) * VEC + e;
-                            x = load_logit(reinterpret_cast<const ElemT*>(sv) + (size_t)j * VEC + e);
-                            if (BITS) {
-                                const uint32_t j2 = rel + lead;
-                                if ((bitmap[j2 >> 5] >> (j2 & 31u)) & 1u) x = __uint_as_float(0x7fc00000u);  // flagged: not part of the stream
-                            }
-                        }
-                        const bool pass = x >= tau;
-                        warp_append(pass, pass ? temper(x, T) : 0.0f, gid0 + rel, S, cand_q, cand_i, P.ccap, end);
-                    }
-                    __syncwarp();
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&empty_bar[stage]);  // this warp is done with the stage
-            }
         }
-        if (rc.windowed && tt == vtiles) {
-            // covers rows too short for a whole vector: only the leading / trailing elements exist
+        float tau_run;
+        if (!sweep_k) {
+            // window rows: the running maximum gives the running threshold
             const uint32_t wk = __reduce_max_sync(FULL_MASK, okey(tmax));
-            if (lane == 0) atomicMax(&S.max_key, wk);
-        }
-        end = __reduce_max_sync(FULL_MASK, end);
-        TICK(2);
-        const int over = cta_sync_or(end > P.limit ? 1 : 0);
-        TICK(3);
-        if (over) {
-            uint32_t n = min(S.count, P.ccap);
-            cta_sync();
-            if (!rc.windowed) {
-                if (n > rc.k_eff) {
-                    n = keep_top_k(n, rc.k_eff, S, cand_q, cand_i);
-                    if (tid == 0) {
-                        S.count = n;
-                        S.tau_key = max(S.tau_key, raw_threshold_key(okey_to_float(S.minkey), T));
-                    }
-                }
-            } else {
-                const float qmax = temper(okey_to_float(S.max_key), T);
-                const float tq = window_stream_bound(qmax);
-                n = compact_inplace(
-                    n, [=](float q, uint32_t) { return q >= tq; }, S, cand_q, cand_i);
+            if (tt == 0) {
+                if (lane == 0) atomicMax(&S.max_key, wk);
+                cta_sync();
                 if (tid == 0) {
-                    if (n > P.limit) {  // the window does not fit: the full-sort kernel takes the row
-                        S.count = 0u;
-                        S.tau_key = 0xff800000u;  // okey(+inf): nothing finite passes any more
-                        S.error |= 2u;
-                    } else {
-                        S.count = n;
-                    }
+                    const float qmax0 = temper(okey_to_float(S.max_key), T);
+                    S.tau_key = raw_threshold_key(window_stream_bound(qmax0), T);
+                }
+                cta_sync();
+            } else if (lane == 0 && wk > vol_load(&S.max_key)) {
+                // the maximum rose: this warp tightens the shared threshold itself (monotone, so
+                // warps that still read the old value only keep a superset)
+                const uint32_t prev = atomicMax(&S.max_key, wk);
+                const float qmax1 = temper(okey_to_float(max(prev, wk)), T);
+                atomicMax(&S.tau_key, raw_threshold_key(window_stream_bound(qmax1), T));
+            }
+            tau_run = okey_to_float(vol_load(&S.tau_key));
+        } else {
+            const uint32_t h3 = tt / 3u;
+            const bool refresh = tt < 4u || (tt & (tt - 1u)) == 0u || (tt == 3u * h3 && (h3 & (h3 - 1u)) == 0u);
+            if (refresh) {
+                const uint32_t kth = warp_bound();
+                if (lane == 0) *(volatile uint32_t*)&S.wkth[warp] = kth;
+                if (tt == 0) cta_sync();  // every warp has published once
+                else __syncwarp();
+                const uint32_t lo = __reduce_min_sync(FULL_MASK, vol_load(&S.wkth[lane & (WARPS - 1u)]));
+                tau_k = max(tau_k, max(lo, LOWEST));
+            }
+            tau_run = okey_to_float(tau_k);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const unsigned gm = __ballot_sync(FULL_MASK, vm[u] >= tau_run);
+            if (lane == 0) grp_max[(t * U + u) * WARPS + warp] = gm;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[stage]);  // this warp is done with the stage
+    }
+    if (rc.windowed) {
+        // covers rows too short for a whole vector: only the leading / trailing elements exist
+        const uint32_t wk = __reduce_max_sync(FULL_MASK, okey(tmax));
+        if (lane == 0) atomicMax(&S.max_key, wk);
+    }
+    // ---- what was appended before the sweep (penalised ids, leading / trailing elements) may already
+    //      pass the compaction trigger
+    end = __reduce_max_sync(FULL_MASK, end);
+    if (cta_sync_or(end > P.limit ? 1 : 0)) {
+        uint32_t n = min(S.count, P.ccap);
+        cta_sync();
+        if (!rc.windowed) {
+            if (n > rc.k_eff) {
+                n = keep_top_k(n, rc.k_eff, S, cand_q, cand_i);
+                if (tid == 0) S.count = n;
+            }
+        } else {
+            const float qmax = temper(okey_to_float(S.max_key), T);
+            const float tq = window_stream_bound(qmax);
+            n = compact_inplace(
+                n, [=](float q, uint32_t) { return q >= tq; }, S, cand_q, cand_i);
+            if (tid == 0) {
+                if (n > P.limit) {  // the window does not fit: the row is ordered in full
+                    S.count = 0u;
+                    S.error |= 2u;
+                } else {
+                    S.count = n;
                 }
             }
-            cta_sync();
-            end = S.count;
         }
+        cta_sync();
     }
     cta_sync();
     bool window_filtered = false;  // the candidates already are exactly the window
     PHASE(7);
-#ifdef LLMC_PROFILE_STAGES
-    TICK(4);
-    if (P.phase_ns && (tid == 0 || tid == 255)) {
-        unsigned long long* o = P.phase_ns + ((size_t)gridDim.x * gridDim.y + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 2u + (tid ? 1u : 0u)) * 8u;
-        for (int k = 0; k < 6; ++k) o[k] = acc[k];
-        o[6] = vtiles; o[7] = S.count;
-    }
-#endif
-    if (rc.windowed || sweep_k) {
+    {
         // the sweep fixed the threshold; the vectors noted during the sweep are read again (from L2)
         // and their elements tested exactly
         const uint32_t unfiltered = S.count;  // leading / trailing elements and penalised ids, appended before the sweep
         if (sweep_k) {
-            // every lane's final maximum goes into its warp's bound
-            const uint32_t r = (rc.k_eff + WARPS - 1u) / WARPS;
-            const uint32_t kth = warp_rth_largest(okey(tmax), r, lane);
+            // every lane's final values go into its warp's bound
+            const uint32_t kth = warp_bound();
             if (lane == 0) S.wkth[warp] = kth;
         }
         if (tid == 0) {
@@ -1283,15 +1235,13 @@ int plan_launch(const DeviceInfo& dev, const KParams& base, bool top_k_known, ui
         plan->ccap = WINDOW_CAP;
         plan->limit = WINDOW_CAP / 2u;
     } else {
-        // between two checks of the buffer at most `room` entries are appended: a whole stage for rows
-        // that append while they stream (rank cut above 256), one round of 256 vectors for rows that
-        // only flag vectors while they stream - on top of the compaction trigger and of the penalised
-        // ids, which are appended before the stream
+        // between two checks of the buffer at most `room` entries are appended (one round of 256
+        // flagged vectors) - on top of the compaction trigger and of the penalised ids, which are
+        // appended before the stream
         uint32_t hist = 0u;
         if (base.history != nullptr) hist = base.hist_len_rows ? base.hist_stride : base.hist_len;
         const uint32_t vec_elems0 = 16u / (base.dtype == LLM_CUDA_DTYPE_BF16 ? 2u : 4u);
-        const bool small_k = top_k_known && kcap <= (uint32_t)THREADS;
-        const uint32_t room = small_k ? (uint32_t)THREADS * vec_elems0 : tile;
+        const uint32_t room = (uint32_t)THREADS * vec_elems0;
         plan->limit = 2u * kcap > 1024u ? 2u * kcap : 1024u;
         plan->ccap = (plan->limit > hist ? plan->limit : hist) + 32u + room;
         if (plan->ccap < WINDOW_CAP && !top_k_known) plan->ccap = WINDOW_CAP;  // rows with top_k 0 may be mixed in
@@ -1339,8 +1289,10 @@ int plan_launch(const DeviceInfo& dev, const KParams& base, bool top_k_known, ui
     // one flag word per group of 32 vectors of the shard
     const uint32_t vec_elems = 16u / (base.dtype == LLM_CUDA_DTYPE_BF16 ? 2u : 4u);
     plan->groups = (shard_cols / vec_elems + 31u) / 32u + WARPS * (STAGE_BYTES / 16u / THREADS);
+    // rank cuts above 256 keep ceil(k/256) best values per lane
+    plan->lane_top_words = (!window_only && kcap > (uint32_t)THREADS) ? kcap : 0u;
     plan->smem = (size_t)RING_STAGES * STAGE_BYTES + (size_t)plan->ccap * 8u + (size_t)plan->bitmap_words * 4u +
-                 (size_t)plan->hash_slots * 8u + (size_t)plan->groups * 4u;
+                 (size_t)plan->hash_slots * 8u + (size_t)plan->lane_top_words * 4u + (size_t)plan->groups * 4u;
     if (plan->smem > dev.max_dyn_smem) return -1;
     return 0;
 }

@@ -40,6 +40,7 @@ struct KParams {
     uint32_t split, shard_cols;
     uint32_t kcap, ccap, limit;     // kcap: exact-selection capacity; ccap: buffer entries; limit: compaction trigger
     uint32_t hash_slots, bitmap_words;
+    uint32_t lane_top_words;        // floats of shared memory for the lanes' best values (rank cuts above 256), else 0
     // scratch shared by the CTAs of one row when split > 1 (also the input of merge_draw)
     float* sc_q;                    // [shard][row][sc_stride]   (element (s, b, i) at (s*sc_rows + b)*sc_stride + i)
     uint32_t* sc_i;
@@ -68,7 +69,7 @@ struct DeviceInfo {
 };
 
 struct LaunchPlan {
-    uint32_t split, shard_cols, kcap, ccap, limit, hash_slots, bitmap_words, groups;
+    uint32_t split, shard_cols, kcap, ccap, limit, hash_slots, bitmap_words, groups, lane_top_words;
     size_t smem;
     bool bits;  // mask or penalty tables needed
     int mode;   // kernel variant: 0 rows of either kind, 1 window-mode rows only, 2 exact-selection rows only
