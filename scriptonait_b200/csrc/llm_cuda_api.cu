@@ -187,6 +187,10 @@ int32_t run_select(llm_cuda_sampler* s, const llm_cuda_sample_args* a, KParams& 
     P.hash_slots = plan.hash_slots;
     P.bitmap_words = plan.bitmap_words;
     P.lane_top_words = plan.lane_top_words;
+    P.cand_off = plan.cand_off;
+    P.scratch_off = plan.scratch_off;
+    P.tables_off = plan.tables_off;
+    P.vlist_cap = plan.vlist_cap;
     P.sc_q = s->sc_q;
     P.sc_i = s->sc_i;
     P.sc_cnt = s->sc_cnt;

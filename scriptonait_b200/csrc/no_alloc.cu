@@ -179,6 +179,10 @@ int32_t llm_cuda_sample_batch_static(int32_t device, const llm_cuda_sample_args*
     P.hash_slots = plan.hash_slots;
     P.bitmap_words = plan.bitmap_words;
     P.lane_top_words = plan.lane_top_words;
+    P.cand_off = plan.cand_off;
+    P.scratch_off = plan.scratch_off;
+    P.tables_off = plan.tables_off;
+    P.vlist_cap = plan.vlist_cap;
     P.sc_q = reinterpret_cast<float*>(d->scratch + kOffValues);
     P.sc_i = reinterpret_cast<uint32_t*>(d->scratch + kOffIds);
     P.sc_cnt = reinterpret_cast<uint32_t*>(d->scratch + kOffCounts);

@@ -21,6 +21,7 @@ constexpr uint32_t STAGE_BYTES = 12288;  // one ring stage = one tile: the logit
 constexpr int RING_STAGES = 3;           // bulk copies in flight per CTA: up to RING_STAGES stages
 constexpr uint32_t WINDOW_CAP = 2048;    // candidate buffer of launches whose rows all run in window mode
 constexpr uint32_t MAX_SORT = 4096;      // most candidates the ordered tail takes (its scratch is the 32 KB ring)
+constexpr uint32_t EPILOGUE_SCRATCH = (uint32_t)THREADS * 8u + MAX_SORT * 4u;  // sort keys of a rank sort + probabilities
 static_assert((size_t)THREADS * 8u + (size_t)MAX_SORT * 4u <= (size_t)RING_STAGES * STAGE_BYTES, "epilogue scratch");
 constexpr unsigned FULL_MASK = 0xffffffffu;
 constexpr uint32_t EMPTY_KEY = 0xffffffffu;

@@ -190,7 +190,8 @@ __device__ bool finish_row(const KParams& P, uint32_t b, const RowCfg& rc, uint3
     uint64_t* keys64 = reinterpret_cast<uint64_t*>(scratch);                     // THREADS 64-bit words
     float* probs = reinterpret_cast<float*>(scratch + (size_t)THREADS * 8u);     // up to MAX_SORT floats
     if (!rc.windowed) {
-        n = keep_top_k(n, rc.k_eff, S, cand_q, cand_i);
+        // a set the rank sort below takes in one go needs no selection first: it is cut after sorting
+        if (n > (uint32_t)THREADS) n = keep_top_k(n, rc.k_eff, S, cand_q, cand_i);
     } else if (!overflow) {
         // exact window: exactly the terms the reference's f32 sums can see
         if (!window_filtered)
@@ -574,7 +575,7 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
 }
 
 template <typename ElemT, bool BITS, int MODE>
-__global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const __grid_constant__ KParams P) {
+__global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const __grid_constant__ KParams P) {
     constexpr int VEC = Traits<ElemT>::VEC;
     constexpr uint32_t VPS = STAGE_BYTES / 16u;      // 16-byte vectors per stage
     constexpr int U = VPS / THREADS;                 // vectors per thread per stage
@@ -584,9 +585,12 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
     __shared__ __align__(8) uint64_t full_bar[RING_STAGES];   // a stage's bytes have landed
     __shared__ __align__(8) uint64_t empty_bar[RING_STAGES];  // all consumer warps are done with a stage
     unsigned char* ring = dyn;
-    float* cand_q = reinterpret_cast<float*>(dyn + RING_STAGES * STAGE_BYTES);
+    // The candidate buffer and the epilogue scratch are only used after the sweep; when they fit they
+    // share the ring's memory (the launch plan decides and passes the offsets).
+    float* cand_q = reinterpret_cast<float*>(dyn + P.cand_off);
     uint32_t* cand_i = reinterpret_cast<uint32_t*>(cand_q + P.ccap);
-    uint32_t* bitmap = cand_i + P.ccap;
+    unsigned char* scratch = dyn + P.scratch_off;  // list of flagged vectors during the revisit, then finish_row's sort keys / probabilities
+    uint32_t* bitmap = reinterpret_cast<uint32_t*>(dyn + P.tables_off);
     uint32_t* hkeys = bitmap + P.bitmap_words;
     uint32_t* hcnt = hkeys + P.hash_slots;
     float* lane_top = reinterpret_cast<float*>(hcnt + P.hash_slots);  // rank cuts above 256: every lane's best values
@@ -729,45 +733,57 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
     PHASE(1);
 
     // ---- ids with a penalty: the stream never edits values. Every distinct history id of this
-    //      CTA's columns is read once here, masked, penalised and appended as a candidate; the
-    //      stream then skips all flagged ids (penalised or blocked by the mask).
+    //      CTA's columns is read once here, masked and penalised; the value replaces the id's count
+    //      in the table and becomes a candidate after the sweep, if it can still matter then. The
+    //      stream skips all flagged ids (penalised or blocked by the mask).
     if (BITS) {
-        for (uint32_t base = 0; base < P.hash_slots; base += THREADS) {
-            const uint32_t slot = base + tid;
-            const uint32_t id = slot < P.hash_slots ? hkeys[slot] : EMPTY_KEY;
-            const bool have = id != EMPTY_KEY;
-            float x = __uint_as_float(0x7fc00000u);
-            if (have) {
-                x = load_logit(row + (id - P.col_offset));
-                if (id_blocked(P, id)) x = neg_inf();
-                x = penalize(x, rc.pen, hcnt[slot]);
-                tmax = fmaxf(tmax, x);
+        // four table slots per thread and round, so that the scattered loads of a round are in flight together
+        for (uint32_t base = 0; base < P.hash_slots; base += 4u * THREADS) {
+            uint32_t id[4], cnt[4];
+            float x[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const uint32_t slot = base + (uint32_t)k * THREADS + tid;
+                id[k] = slot < P.hash_slots ? hkeys[slot] : EMPTY_KEY;
+                cnt[k] = slot < P.hash_slots ? hcnt[slot] : 0u;
             }
-            warp_append(have && x >= neg_inf(), temper(x, T), id, S, cand_q, cand_i, P.ccap, end);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                x[k] = __uint_as_float(0x7fc00000u);
+                if (id[k] != EMPTY_KEY) x[k] = load_logit(row + (id[k] - P.col_offset));
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                if (id[k] != EMPTY_KEY) {
+                    if (id_blocked(P, id[k])) x[k] = neg_inf();
+                    x[k] = penalize(x[k], rc.pen, cnt[k]);
+                    tmax = fmaxf(tmax, x[k]);
+                    hcnt[base + (uint32_t)k * THREADS + tid] = __float_as_uint(x[k]);  // only this thread touches the slot
+                }
+            }
         }
     }
 
-    // ---- leading / trailing elements that are not part of a whole aligned vector (warp 0)
+    // ---- leading / trailing elements that are not part of a whole aligned vector (warp 0, one per lane)
+    float ht_x = __uint_as_float(0x7fc00000u);
+    uint32_t ht_rel = 0u;
     if (warp == 0) {
         bool valid = false;
-        uint32_t rel = 0u;
         if (lane < head) {
-            rel = lane;
+            ht_rel = lane;
             valid = true;
         } else if (lane >= 16u && lane - 16u < ntail) {
-            rel = tail0 + (lane - 16u);
+            ht_rel = tail0 + (lane - 16u);
             valid = true;
         }
-        float x = __uint_as_float(0x7fc00000u);
         if (valid) {
-            x = load_logit(row + c0 + rel);
+            ht_x = load_logit(row + c0 + ht_rel);
             if (BITS) {
-                const uint32_t j2 = rel + lead;
-                if ((bitmap[j2 >> 5] >> (j2 & 31u)) & 1u) x = __uint_as_float(0x7fc00000u);  // handled above / blocked
+                const uint32_t j2 = ht_rel + lead;
+                if ((bitmap[j2 >> 5] >> (j2 & 31u)) & 1u) ht_x = __uint_as_float(0x7fc00000u);  // handled above / blocked
             }
-            tmax = fmaxf(tmax, x);
+            tmax = fmaxf(tmax, ht_x);
         }
-        warp_append(valid && x >= neg_inf(), temper(x, T), gid0 + rel, S, cand_q, cand_i, P.ccap, end);
     }
 
     // ---- the stream: one sweep without CTA barriers (after the first stage) that only takes maxima
@@ -901,40 +917,12 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
         const uint32_t wk = __reduce_max_sync(FULL_MASK, okey(tmax));
         if (lane == 0) atomicMax(&S.max_key, wk);
     }
-    // ---- what was appended before the sweep (penalised ids, leading / trailing elements) may already
-    //      pass the compaction trigger
-    end = __reduce_max_sync(FULL_MASK, end);
-    if (cta_sync_or(end > P.limit ? 1 : 0)) {
-        uint32_t n = min(S.count, P.ccap);
-        cta_sync();
-        if (!rc.windowed) {
-            if (n > rc.k_eff) {
-                n = keep_top_k(n, rc.k_eff, S, cand_q, cand_i);
-                if (tid == 0) S.count = n;
-            }
-        } else {
-            const float qmax = temper(okey_to_float(S.max_key), T);
-            const float tq = window_stream_bound(qmax);
-            n = compact_inplace(
-                n, [=](float q, uint32_t) { return q >= tq; }, S, cand_q, cand_i);
-            if (tid == 0) {
-                if (n > P.limit) {  // the window does not fit: the row is ordered in full
-                    S.count = 0u;
-                    S.error |= 2u;
-                } else {
-                    S.count = n;
-                }
-            }
-        }
-        cta_sync();
-    }
     cta_sync();
     bool window_filtered = false;  // the candidates already are exactly the window
     PHASE(7);
     {
-        // the sweep fixed the threshold; the vectors noted during the sweep are read again (from L2)
-        // and their elements tested exactly
-        const uint32_t unfiltered = S.count;  // leading / trailing elements and penalised ids, appended before the sweep
+        // the sweep fixed the threshold: the penalised ids, the leading / trailing elements and the
+        // vectors flagged during the sweep (read again, from L2) are tested exactly and appended
         if (sweep_k) {
             // every lane's final values go into its warp's bound
             const uint32_t kth = warp_bound();
@@ -957,11 +945,52 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
         } else {
             tau = okey_to_float(raw_threshold_key(window_stream_bound(qmaxf), T));
         }
+        // Exact-selection rows check the buffer after every round (at most ROUND*VEC = 1024 new
+        // entries, which the buffer has room for beyond `limit`) and keep the best k when it fills;
+        // `tau` then rises to the k-th value, in every thread alike. Window rows that overflow are
+        // ordered in full instead.
+        auto settle = [&]() {
+            if (!sweep_k) return;
+            const int over = cta_sync_or(vol_load(&S.count) > P.limit ? 1 : 0);
+            if (!over) return;
+            uint32_t n2 = min(S.count, P.ccap);
+            cta_sync();
+            if (n2 > rc.k_eff) {
+                n2 = keep_top_k(n2, rc.k_eff, S, cand_q, cand_i);
+                if (tid == 0) S.count = n2;
+                cta_sync();
+                tau = fmaxf(tau, okey_to_float(raw_threshold_key(okey_to_float(S.minkey), T)));
+            }
+            cta_sync();
+        };
+        // does a value of the edited row (pre-temperature x, post-temperature q) still matter?
+        auto matters = [&](float x, float q) {
+            if (sweep_k) return x >= tau;
+            return (__fsub_rn(q, qmaxf) >= WINDOW_EXACT) || (q == qmaxf);  // exactly the terms the reference's sums can see
+        };
+        // (1) penalised ids: their edited values wait in the table
+        if (BITS) {
+            for (uint32_t base = 0; base < P.hash_slots; base += THREADS) {
+                const uint32_t slot = base + tid;
+                const uint32_t id = slot < P.hash_slots ? hkeys[slot] : EMPTY_KEY;
+                const bool have = id != EMPTY_KEY;
+                const float x = have ? __uint_as_float(hcnt[slot]) : __uint_as_float(0x7fc00000u);
+                const float q = temper(x, T);
+                warp_append(have && x >= neg_inf() && matters(x, q), q, id, S, cand_q, cand_i, P.ccap, end);
+                settle();
+            }
+        }
+        // (2) leading / trailing elements
+        if (warp == 0) {
+            const float q = temper(ht_x, T);
+            warp_append(ht_x >= neg_inf() && matters(ht_x, q), q, gid0 + ht_rel, S, cand_q, cand_i, P.ccap, end);
+        }
+        // (3) the flagged vectors
         const uint32_t ngroups = (nvi + 31u) / 32u;
         const uint4* gv = reinterpret_cast<const uint4*>(vbase);
-        uint32_t* vlist = reinterpret_cast<uint32_t*>(ring);  // the ring is idle now
-        constexpr uint32_t VLIST_CAP = RING_STAGES * STAGE_BYTES / 4u;
-        // list the noted vectors: one shared-memory atomic per warp step (prefix sums inside the warp)
+        uint32_t* vlist = reinterpret_cast<uint32_t*>(scratch);
+        const uint32_t VLIST_CAP = P.vlist_cap;
+        // list them: one shared-memory atomic per warp step (prefix sums inside the warp)
         for (uint32_t g0 = 0; g0 < ngroups; g0 += THREADS) {
             const uint32_t g = g0 + tid;
             unsigned m = g < ngroups ? grp_max[g] : 0u;
@@ -987,8 +1016,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
         }
         cta_sync();
         const uint32_t nq = S.keep;
-        // read a noted vector again (L2) and append the elements inside the exact window; the
-        // appends of a warp step share one atomic
+        // read a flagged vector again (L2) and append the elements that matter; the appends of a
+        // warp step share one atomic
         auto examine = [&](bool have, uint32_t v) {
             float x[VEC];
             uint32_t em = 0u;
@@ -1003,9 +1032,9 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
 #pragma unroll
                 for (int e = 0; e < VEC; ++e) {
                     if (x[e] >= tau && !((nib >> e) & 1u)) {
-                        x[e] = temper(x[e], T);
-                        // window rows: exactly the terms the reference's sums can see
-                        if (sweep_k || (__fsub_rn(x[e], qmaxf) >= WINDOW_EXACT) || (x[e] == qmaxf)) em |= 1u << e;
+                        const float q = temper(x[e], T);
+                        if (matters(x[e], q)) em |= 1u << e;
+                        x[e] = q;
                     }
                 }
             }
@@ -1035,42 +1064,27 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
                 }
             }
         };
-        // Exact-selection rows check the buffer after every round of 256 vectors (at most 256*VEC new
-        // entries, which the buffer has room for beyond `limit`) and keep the best k when it fills;
-        // `tau` then rises to the k-th value, in every thread alike. Window rows that overflow are
-        // ordered in full instead.
-        auto settle = [&]() {
-            if (!sweep_k) return;
-            const int over = cta_sync_or(vol_load(&S.count) > P.limit ? 1 : 0);
-            if (!over) return;
-            uint32_t n2 = min(S.count, P.ccap);
-            cta_sync();
-            if (n2 > rc.k_eff) {
-                n2 = keep_top_k(n2, rc.k_eff, S, cand_q, cand_i);
-                if (tid == 0) S.count = n2;
-                cta_sync();
-                tau = fmaxf(tau, okey_to_float(raw_threshold_key(okey_to_float(S.minkey), T)));
-            }
-            cta_sync();
-        };
+        // a round of an exact-selection row appends at most 1024 entries: 1024/VEC vectors
+        const uint32_t ROUND = sweep_k ? 1024u / (uint32_t)VEC : (uint32_t)THREADS;
         if (nq <= VLIST_CAP) {
-            for (uint32_t i0 = 0; i0 < nq; i0 += THREADS) {
+            for (uint32_t i0 = 0; i0 < nq; i0 += ROUND) {
                 const uint32_t i = i0 + tid;
-                const uint32_t v = i < nq ? vlist[i] : 0xffffffffu;
+                const uint32_t v = (tid < ROUND && i < nq) ? vlist[i] : 0xffffffffu;
                 examine(v < nvi, v);
                 settle();
             }
         } else {
-            for (uint32_t g0 = 0; g0 < ngroups; g0 += WARPS) {
+            const uint32_t wr = ROUND / 32u;  // warps taking part in a round
+            for (uint32_t g0 = 0; g0 < ngroups; g0 += wr) {
                 const uint32_t g = g0 + warp;
-                const unsigned m = g < ngroups ? grp_max[g] : 0u;  // same word for the whole warp
+                const unsigned m = (warp < wr && g < ngroups) ? grp_max[g] : 0u;  // same word for the whole warp
                 const uint32_t v = g * 32u + lane;
                 examine(((m >> lane) & 1u) && v < nvi, v);
                 settle();
             }
         }
         cta_sync();
-        window_filtered = rc.windowed && (unfiltered == 0u) && P.split == 1u;
+        window_filtered = rc.windowed && P.split == 1u;
     }
     PHASE(2);
     if (wait_failed) atomicOr(&S.error, 4u);
@@ -1085,7 +1099,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
     }
 
     if (P.split == 1u) {
-        if (finish_row(P, b, rc, n, overflow, qmax, S, cand_q, cand_i, ring, window_filtered))
+        if (finish_row(P, b, rc, n, overflow, qmax, S, cand_q, cand_i, scratch, window_filtered))
             full_sort_row(P, b, *reinterpret_cast<FullShared*>(ring), hkeys, hcnt);
         return;
     }
@@ -1126,7 +1140,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 3) stream_select_kernel(const 
     if (tid == 0) P.sc_ticket[b] = 0u;  // re-armed for the next launch on this stream
     __threadfence();
     n = merge_lists(P, b, rc, P.split, S, cand_q, cand_i, overflow, qmax);
-    if (finish_row(P, b, rc, n, overflow, qmax, S, cand_q, cand_i, ring))
+    if (finish_row(P, b, rc, n, overflow, qmax, S, cand_q, cand_i, scratch))
         full_sort_row(P, b, *reinterpret_cast<FullShared*>(ring), hkeys, hcnt);
 }
 
@@ -1231,19 +1245,14 @@ int plan_launch(const DeviceInfo& dev, const KParams& base, bool top_k_known, ui
     const bool may_be_greedy = base.t_rows != nullptr || base.temperature <= 0.0f;
     plan->mode = (window_only && !may_be_greedy) ? 1 : ((top_k_known && !window_only) ? 2 : 0);
     if (window_only) {
-        // no per-tile headroom: an append that falls off the buffer sends the row to the full-sort kernel
+        // an append that falls off the buffer sends the row to the full ordering
         plan->ccap = WINDOW_CAP;
         plan->limit = WINDOW_CAP / 2u;
     } else {
-        // between two checks of the buffer at most `room` entries are appended (one round of 256
-        // flagged vectors) - on top of the compaction trigger and of the penalised ids, which are
-        // appended before the stream
-        uint32_t hist = 0u;
-        if (base.history != nullptr) hist = base.hist_len_rows ? base.hist_stride : base.hist_len;
-        const uint32_t vec_elems0 = 16u / (base.dtype == LLM_CUDA_DTYPE_BF16 ? 2u : 4u);
-        const uint32_t room = (uint32_t)THREADS * vec_elems0;
+        // candidates are appended after the sweep in rounds of at most 1024 entries, each followed by a
+        // check of the buffer against the compaction trigger
         plan->limit = 2u * kcap > 1024u ? 2u * kcap : 1024u;
-        plan->ccap = (plan->limit > hist ? plan->limit : hist) + 32u + room;
+        plan->ccap = plan->limit + 32u + 1024u;
         if (plan->ccap < WINDOW_CAP && !top_k_known) plan->ccap = WINDOW_CAP;  // rows with top_k 0 may be mixed in
     }
     plan->bits = (base.allowed_bits != nullptr) || (base.history != nullptr && (base.r_rows != nullptr || base.penalty != 1.0f) &&
@@ -1291,18 +1300,44 @@ int plan_launch(const DeviceInfo& dev, const KParams& base, bool top_k_known, ui
     plan->groups = (shard_cols / vec_elems + 31u) / 32u + WARPS * (STAGE_BYTES / 16u / THREADS);
     // rank cuts above 256 keep ceil(k/256) best values per lane
     plan->lane_top_words = (!window_only && kcap > (uint32_t)THREADS) ? kcap : 0u;
-    plan->smem = (size_t)RING_STAGES * STAGE_BYTES + (size_t)plan->ccap * 8u + (size_t)plan->bitmap_words * 4u +
-                 (size_t)plan->hash_slots * 8u + (size_t)plan->lane_top_words * 4u + (size_t)plan->groups * 4u;
+    // The candidate buffer and the epilogue scratch (sort keys + probabilities) are used only after the
+    // sweep: when both fit into the ring they live there, which is what lets four CTAs share an SM.
+    const size_t ring_bytes = (size_t)RING_STAGES * STAGE_BYTES;
+    const size_t cand_bytes = (size_t)plan->ccap * 8u;
+    const size_t tables_bytes = (size_t)plan->bitmap_words * 4u + (size_t)plan->hash_slots * 8u +
+                                (size_t)plan->lane_top_words * 4u + (size_t)plan->groups * 4u;
+    if (cand_bytes + EPILOGUE_SCRATCH <= ring_bytes) {
+        plan->cand_off = 0u;
+        plan->scratch_off = (uint32_t)cand_bytes;
+        plan->tables_off = (uint32_t)ring_bytes;
+        plan->vlist_cap = (uint32_t)((ring_bytes - cand_bytes) / 4u);
+        plan->smem = ring_bytes + tables_bytes;
+    } else {
+        plan->cand_off = (uint32_t)ring_bytes;
+        plan->scratch_off = 0u;
+        plan->tables_off = (uint32_t)(ring_bytes + cand_bytes);
+        plan->vlist_cap = (uint32_t)(ring_bytes / 4u);
+        plan->smem = ring_bytes + cand_bytes + tables_bytes;
+    }
     if (plan->smem > dev.max_dyn_smem) return -1;
     return 0;
+}
+
+template <typename ElemT, bool BITS, int MODE>
+static cudaError_t configure_one(int v) {
+    cudaError_t e = cudaFuncSetAttribute(stream_select_kernel<ElemT, BITS, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, v);
+    if (e != cudaSuccess) return e;
+    // four CTAs of ~55 KB each only fit when the SM's L1/shared split favours shared memory
+    return cudaFuncSetAttribute(stream_select_kernel<ElemT, BITS, MODE>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                (int)cudaSharedmemCarveoutMaxShared);
 }
 
 template <typename ElemT, bool BITS>
 static cudaError_t configure_stream(int v) {
     cudaError_t e;
-    if ((e = cudaFuncSetAttribute(stream_select_kernel<ElemT, BITS, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, v)) != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute(stream_select_kernel<ElemT, BITS, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, v)) != cudaSuccess) return e;
-    return cudaFuncSetAttribute(stream_select_kernel<ElemT, BITS, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, v);
+    if ((e = configure_one<ElemT, BITS, 0>(v)) != cudaSuccess) return e;
+    if ((e = configure_one<ElemT, BITS, 1>(v)) != cudaSuccess) return e;
+    return configure_one<ElemT, BITS, 2>(v);
 }
 
 cudaError_t configure_kernels(size_t max_dyn_smem) {

@@ -40,6 +40,8 @@ struct KParams {
     uint32_t split, shard_cols;
     uint32_t kcap, ccap, limit;     // kcap: exact-selection capacity; ccap: buffer entries; limit: compaction trigger
     uint32_t hash_slots, bitmap_words;
+    uint32_t cand_off, scratch_off, tables_off;  // byte offsets into the kernel's dynamic shared memory
+    uint32_t vlist_cap;             // flagged vectors the revisit list can hold
     uint32_t lane_top_words;        // floats of shared memory for the lanes' best values (rank cuts above 256), else 0
     // scratch shared by the CTAs of one row when split > 1 (also the input of merge_draw)
     float* sc_q;                    // [shard][row][sc_stride]   (element (s, b, i) at (s*sc_rows + b)*sc_stride + i)
@@ -69,7 +71,8 @@ struct DeviceInfo {
 };
 
 struct LaunchPlan {
-    uint32_t split, shard_cols, kcap, ccap, limit, hash_slots, bitmap_words, groups, lane_top_words;
+    uint32_t split, shard_cols, kcap, ccap, limit, hash_slots, bitmap_words, groups, lane_top_words,
+        cand_off, scratch_off, tables_off, vlist_cap;
     size_t smem;
     bool bits;  // mask or penalty tables needed
     int mode;   // kernel variant: 0 rows of either kind, 1 window-mode rows only, 2 exact-selection rows only
