@@ -685,6 +685,16 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
 
     // ---- mask / penalty side tables
     if (BITS) {
+        // the first 512 history ids are fetched while the tables are cleared
+        const uint32_t* hist = P.history + (size_t)b * P.hist_stride;
+        uint32_t pre_id[2] = {0u, 0u};
+        if (rc.has_pen) {
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                const uint32_t j = (uint32_t)k * THREADS + tid;
+                if (j < rc.hlen) pre_id[k] = __ldg(&hist[j]);
+            }
+        }
         for (uint32_t w = tid; w < P.bitmap_words; w += THREADS) bitmap[w] = 0u;
         for (uint32_t i = tid; i < P.hash_slots; i += THREADS) {
             hkeys[i] = EMPTY_KEY;
@@ -692,15 +702,17 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
         }
         cta_sync();
         if (rc.has_pen) {
-            const uint32_t* hist = P.history + (size_t)b * P.hist_stride;
-            for (uint32_t j = tid; j < rc.hlen; j += THREADS) {
-                const uint32_t id = __ldg(&hist[j]);
+            auto note = [&](uint32_t id) {
                 if (id >= gid0 && id - gid0 < ncols) {  // ids outside the vocabulary are skipped (generate.rs:345)
                     hash_insert(hkeys, hcnt, P.hash_slots, id);
                     const uint32_t j2 = id - gid0 + lead;
                     atomicOr(&bitmap[j2 >> 5], 1u << (j2 & 31u));
                 }
-            }
+            };
+#pragma unroll
+            for (int k = 0; k < 2; ++k)
+                if ((uint32_t)k * THREADS + tid < rc.hlen) note(pre_id[k]);
+            for (uint32_t j = 2u * THREADS + tid; j < rc.hlen; j += THREADS) note(__ldg(&hist[j]));
         }
         if (P.allowed_bits) {
             // bit jb of bitmap word w stands for global id gid0 - lead + 32*w + jb
@@ -1018,12 +1030,12 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
         const uint32_t nq = S.keep;
         // read a flagged vector again (L2) and append the elements that matter; the appends of a
         // warp step share one atomic
-        auto examine = [&](bool have, uint32_t v) {
+        auto examine = [&](bool have, uint32_t v, const uint4& data) {
             float x[VEC];
             uint32_t em = 0u;
             const uint32_t rel0 = head + v * VEC;
             if (have) {
-                unpack<ElemT>(__ldg(gv + v), x);
+                unpack<ElemT>(data, x);
                 uint32_t nib = 0u;
                 if (BITS) {
                     const uint32_t j2 = rel0 + lead;
@@ -1066,12 +1078,26 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
         };
         // a round of an exact-selection row appends at most 1024 entries: 1024/VEC vectors
         const uint32_t ROUND = sweep_k ? 1024u / (uint32_t)VEC : (uint32_t)THREADS;
+        const uint4 nothing = make_uint4(0u, 0u, 0u, 0u);
         if (nq <= VLIST_CAP) {
-            for (uint32_t i0 = 0; i0 < nq; i0 += ROUND) {
-                const uint32_t i = i0 + tid;
-                const uint32_t v = (tid < ROUND && i < nq) ? vlist[i] : 0xffffffffu;
-                examine(v < nvi, v);
-                settle();
+            // four rounds' loads are issued together: they may miss L2 by now, and one trip to memory
+            // is better than four
+            for (uint32_t i0 = 0; i0 < nq; i0 += 4u * ROUND) {
+                uint32_t v[4];
+                uint4 d[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const uint32_t i = i0 + (uint32_t)k * ROUND + tid;
+                    v[k] = (tid < ROUND && i < nq) ? vlist[i] : 0xffffffffu;
+                    d[k] = v[k] < nvi ? __ldg(gv + v[k]) : nothing;
+                }
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    if (i0 + (uint32_t)k * ROUND < nq) {  // the same for every thread
+                        examine(v[k] < nvi, v[k], d[k]);
+                        settle();
+                    }
+                }
             }
         } else {
             const uint32_t wr = ROUND / 32u;  // warps taking part in a round
@@ -1079,7 +1105,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
                 const uint32_t g = g0 + warp;
                 const unsigned m = (warp < wr && g < ngroups) ? grp_max[g] : 0u;  // same word for the whole warp
                 const uint32_t v = g * 32u + lane;
-                examine(((m >> lane) & 1u) && v < nvi, v);
+                const bool have = ((m >> lane) & 1u) && v < nvi;
+                examine(have, v, have ? __ldg(gv + v) : nothing);
                 settle();
             }
         }
