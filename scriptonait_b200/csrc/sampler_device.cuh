@@ -191,7 +191,8 @@ struct Shared {
     uint32_t error;        // internal consistency failures (buffer overrun guard)
     uint32_t last;         // this CTA merges the row
     uint32_t wkth[WARPS];   // per-warp lower bounds for the first tile's threshold
-    uint32_t hit_cnt[WARPS];  // per-warp number of listed vectors of the current stage
+    float u_pre;              // the row's uniform, fetched early by kernels that can (u_pre_valid != 0)
+    uint32_t u_pre_valid;
     uint32_t hist[2][256];  // radix-select histograms, alternated between passes
     float f_sum, f_total, f_u, f_r, f_thr;
     uint32_t token, out_flags, kept_n, walk_end;
@@ -415,6 +416,15 @@ __device__ __forceinline__ void sort_candidates(uint32_t n, float* cand_q, uint3
 // the significance window (window mode only). Thread 0 owns the sequential
 // chains; everything else is data parallel. Returns through S: token, flags,
 // kept_n and the stage statistics.
+// The uniform the row's draw consumes: output `draw_index + 1` of its SplitMix64 stream
+// (rng.rs:31-34), or the caller's pinned value.
+__device__ __forceinline__ float row_uniform(const KParams& P, uint32_t b) {
+    if (P.uniforms) return P.uniforms[b];
+    const uint64_t seed = P.seeds ? P.seeds[b] : P.seed_base + (uint64_t)b;
+    const uint64_t done = P.draw_index ? P.draw_index[b] : 0ull;
+    return u24_to_f32(splitmix_output(seed, done + 1ull));
+}
+
 __device__ __forceinline__ void ordered_tail(const KParams& P, uint32_t b, const RowCfg& rc, uint32_t n, bool truncated,
                                              uint32_t k_total, Shared& S, const float* cand_q, const uint32_t* cand_i,
                                              float* probs) {
@@ -520,14 +530,7 @@ __device__ __forceinline__ void ordered_tail(const KParams& P, uint32_t b, const
         }
         // entries past the window add less than half an ulp to `cum`/`total`, so both are final
         const bool tail_kept = open_tail && !reached;
-        float u;
-        if (P.uniforms) {
-            u = P.uniforms[b];
-        } else {
-            const uint64_t seed = P.seeds ? P.seeds[b] : P.seed_base + (uint64_t)b;
-            const uint64_t done = P.draw_index ? P.draw_index[b] : 0ull;
-            u = u24_to_f32(splitmix_output(seed, done + 1ull));  // rng.rs:31-34
-        }
+        const float u = S.u_pre_valid ? S.u_pre : row_uniform(P, b);
         float r = __fmul_rn(u, total);  // :412
         S.f_total = total;
         S.f_u = u;

@@ -134,7 +134,7 @@ __device__ __forceinline__ unsigned long long global_ns() {
 #define PHASE(slot)                                                                                              \
     do {                                                                                                         \
         if (P.phase_ns && threadIdx.x == 0)                                                                      \
-            P.phase_ns[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 8u + (slot)] = global_ns();              \
+            P.phase_ns[((size_t)(blockIdx.y + P.row_base) * gridDim.x + blockIdx.x) * 8u + (slot)] = global_ns();              \
     } while (0)
 
 // A row that needs the full ordering where no full-sort scratch exists (the allocation-free
@@ -251,18 +251,40 @@ __device__ uint32_t merge_lists(const KParams& P, uint32_t b, const RowCfg& rc, 
     if (threadIdx.x == 0) {
         S.count = 0u;
         S.max_key = 0x007fffffu;
-        S.keep = 0u;  // overflow marker seen
+        S.keep = 0u;      // overflow marker seen
+        S.newcount = 0u;  // entries of all lists together
     }
     cta_sync();
     for (uint32_t s = threadIdx.x; s < nsh; s += THREADS) {
         const size_t at = (size_t)s * P.sc_rows + b;
         if (P.sc_maxkey) atomicMax(&S.max_key, __ldcg(&P.sc_maxkey[at]));
-        if (__ldcg(&P.sc_cnt[at]) == 0xffffffffu) S.keep = 1u;
+        const uint32_t cnt = __ldcg(&P.sc_cnt[at]);
+        if (cnt == 0xffffffffu) S.keep = 1u;
+        else atomicAdd(&S.newcount, min(cnt, P.sc_stride));
     }
     cta_sync();
     overflow = S.keep != 0u;
     qmax = okey_to_float(S.max_key);
     const float tq = window_stream_bound(qmax);
+    if (!overflow && S.newcount <= P.ccap) {
+        // everything fits at once: each warp copies whole lists, all lists in flight together
+        const uint32_t lane = threadIdx.x & 31u;
+        for (uint32_t s = threadIdx.x >> 5; s < nsh; s += WARPS) {
+            const size_t at = (size_t)s * P.sc_rows + b;
+            const uint32_t cnt = min(__ldcg(&P.sc_cnt[at]), P.sc_stride);
+            uint32_t base = 0u;
+            if (lane == 0) base = atomicAdd(&S.count, cnt);
+            base = __shfl_sync(FULL_MASK, base, 0);
+            const float* sq = P.sc_q + at * P.sc_stride;
+            const uint32_t* si = P.sc_i + at * P.sc_stride;
+            for (uint32_t i = lane; i < cnt; i += 32u) {
+                cand_q[base + i] = __ldcg(&sq[i]);
+                cand_i[base + i] = __ldcg(&si[i]);
+            }
+        }
+        cta_sync();
+        return S.count;
+    }
     for (uint32_t s = 0; s < nsh && !overflow; ++s) {
         const size_t at = (size_t)s * P.sc_rows + b;
         const uint32_t cnt = min(__ldcg(&P.sc_cnt[at]), P.sc_stride);
@@ -596,7 +618,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
     float* lane_top = reinterpret_cast<float*>(hcnt + P.hash_slots);  // rank cuts above 256: every lane's best values
     uint32_t* grp_max = reinterpret_cast<uint32_t*>(lane_top + P.lane_top_words);  // one flag word per 32 vectors
 
-    const uint32_t b = blockIdx.y, shard = blockIdx.x, tid = threadIdx.x;
+    const uint32_t b = blockIdx.y + P.row_base, shard = blockIdx.x, tid = threadIdx.x;
     const unsigned lane = tid & 31u, warp = tid >> 5;
     const uint32_t LOWEST = 0x007fffffu;  // okey(-inf)
     // A launch that asked to overlap its predecessor may start now. This kernel reads its inputs and
@@ -605,6 +627,9 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
     grid_launch_dependents();
     if (tid == 0) {
         resolve_row(P, b, S.rc);
+        // the draw's uniform is an input: fetched now, its latency is hidden behind the sweep
+        S.u_pre_valid = P.out_q ? 0u : 1u;
+        S.u_pre = P.out_q ? 0.0f : row_uniform(P, b);
         S.count = 0u;
         S.tau_key = LOWEST;
         S.max_key = LOWEST;
@@ -1135,7 +1160,13 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
     //      the CTA that arrives last merges them (no CTA ever waits for another)
     grid_dependency_wait();  // the scratch lists and tickets are shared with the previous launch
     if (!rc.windowed) {
-        n = keep_top_k(n, rc.k_eff, S, cand_q, cand_i);
+        if (n <= (uint32_t)THREADS) {
+            // small enough for the rank sort: ordered and cut at k in two barriers
+            sort_candidates(n, cand_q, cand_i, reinterpret_cast<uint64_t*>(scratch));
+            n = min(n, rc.k_eff);
+        } else {
+            n = keep_top_k(n, rc.k_eff, S, cand_q, cand_i);
+        }
     } else if (!overflow) {
         n = compact_inplace(
             n, [=](float q, uint32_t) { return (__fsub_rn(q, qmax) >= WINDOW_EXACT) || (q == qmax); }, S, cand_q, cand_i);
@@ -1182,6 +1213,7 @@ __global__ void __launch_bounds__(THREADS) merge_draw_kernel(const __grid_consta
     if (threadIdx.x == 0) {
         resolve_row(P, b, S.rc);
         S.error = 0u;
+        S.u_pre_valid = 0u;
     }
     cta_sync();
     const RowCfg rc = S.rc;
@@ -1379,9 +1411,9 @@ cudaError_t configure_kernels(size_t max_dyn_smem) {
 }
 
 template <typename ElemT, bool BITS, int MODE>
-static cudaError_t launch_stream_t(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap) {
+static cudaError_t launch_stream_t(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap, uint32_t rows) {
     auto kern = stream_select_kernel<ElemT, BITS, MODE>;
-    dim3 grid(plan.split, P.batch, 1);
+    dim3 grid(plan.split, rows, 1);
     if (!overlap) {
         kern<<<grid, STREAM_THREADS, plan.smem, stream>>>(P);
         return cudaGetLastError();
@@ -1403,18 +1435,20 @@ static cudaError_t launch_stream_t(const KParams& P, const LaunchPlan& plan, cud
 }
 
 template <typename ElemT, bool BITS>
-static cudaError_t launch_stream_m(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap) {
-    if (plan.mode == 1) return launch_stream_t<ElemT, BITS, 1>(P, plan, stream, overlap);
-    if (plan.mode == 2) return launch_stream_t<ElemT, BITS, 2>(P, plan, stream, overlap);
-    return launch_stream_t<ElemT, BITS, 0>(P, plan, stream, overlap);
+static cudaError_t launch_stream_m(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap, uint32_t rows) {
+    if (plan.mode == 1) return launch_stream_t<ElemT, BITS, 1>(P, plan, stream, overlap, rows);
+    if (plan.mode == 2) return launch_stream_t<ElemT, BITS, 2>(P, plan, stream, overlap, rows);
+    return launch_stream_t<ElemT, BITS, 0>(P, plan, stream, overlap, rows);
 }
 
-cudaError_t launch_stream_select(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap) {
+cudaError_t launch_stream_select(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap, uint32_t rows) {
+    if (rows == 0u) rows = P.batch;
     if (P.dtype == LLM_CUDA_DTYPE_BF16) {
-        return plan.bits ? launch_stream_m<uint16_t, true>(P, plan, stream, overlap)
-                         : launch_stream_m<uint16_t, false>(P, plan, stream, overlap);
+        return plan.bits ? launch_stream_m<uint16_t, true>(P, plan, stream, overlap, rows)
+                         : launch_stream_m<uint16_t, false>(P, plan, stream, overlap, rows);
     }
-    return plan.bits ? launch_stream_m<float, true>(P, plan, stream, overlap) : launch_stream_m<float, false>(P, plan, stream, overlap);
+    return plan.bits ? launch_stream_m<float, true>(P, plan, stream, overlap, rows)
+                     : launch_stream_m<float, false>(P, plan, stream, overlap, rows);
 }
 
 cudaError_t launch_merge_draw(const KParams& P, const LaunchPlan& plan, cudaStream_t stream) {

@@ -56,6 +56,7 @@ struct KParams {
     uint32_t* out_cnt;
     uint32_t out_stride;
     uint32_t force_full;
+    uint32_t row_base;              // this launch handles rows row_base .. row_base + gridDim.y - 1
     // full ordering of the rare rows the stream cannot decide: scratch slots claimed by the row's own CTA
     unsigned long long* full_keys;  // [full_nslots][full_vpad] 64-bit sort keys, or NULL = no such stage
     float* full_vals;               // [full_nslots][full_vpad]
@@ -88,7 +89,9 @@ int plan_launch(const DeviceInfo& dev, const KParams& base, bool top_k_known, ui
 
 // `overlap`: launch with programmatic stream serialization, so the grid may begin reading its inputs
 // while the previous kernel of the stream (if it is this kernel too) is still finishing.
-cudaError_t launch_stream_select(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap = false);
+// `rows`: rows of this launch, starting at P.row_base (0 = all of P.batch).
+cudaError_t launch_stream_select(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap = false,
+                                 uint32_t rows = 0u);
 cudaError_t launch_merge_draw(const KParams& P, const LaunchPlan& plan, cudaStream_t stream);
 cudaError_t launch_advance_rows(uint32_t batch, const uint32_t* tokens, const uint32_t* row_flags, uint32_t* history,
                                 uint32_t history_stride, uint32_t window, uint32_t* history_len, uint32_t* history_pos,
