@@ -324,6 +324,8 @@ def run_ours(args, rank, world, local_rank):
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": "rows/s", "h2d_bytes_per_step": int(batches[0].logits.nbytes + BATCH * 8),
                     "d2h_bytes_per_step": BATCH * 4, "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
+                    "bound": "host-to-device copy of the logits (PCIe)",
+                    "h2d_gbs_achieved": (batches[0].logits.nbytes + BATCH * 8) / (e2e_ms / e2e_steps * 1e-3) / 1e9,
                     "tokens_match_device_path": same},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clock_info,
