@@ -54,7 +54,7 @@ struct llm_cuda_sampler {
     unsigned char* arena = nullptr;
     size_t arena_bytes = 0;
     uint32_t last_kernels = 0, last_split = 0;
-    bool stagger = true;  // development aid: llm_cuda_debug_stagger(s, 0) starts every CTA at once
+    bool stagger = false;  // development aid: llm_cuda_debug_stagger(s, 1) staggers the first wave of a grid larger than the GPU
     char err[512] = "";
 };
 
