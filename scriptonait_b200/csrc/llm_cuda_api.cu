@@ -54,7 +54,6 @@ struct llm_cuda_sampler {
     unsigned char* arena = nullptr;
     size_t arena_bytes = 0;
     uint32_t last_kernels = 0, last_split = 0;
-    bool stagger = false;  // development aid: llm_cuda_debug_stagger(s, 1) staggers the first wave of a grid larger than the GPU
     char err[512] = "";
 };
 
@@ -210,20 +209,6 @@ int32_t run_select(llm_cuda_sampler* s, const llm_cuda_sample_args* a, KParams& 
     P.full_vpad = s->vpad;
     P.full_nslots = s->nslots;
     (void)lists_out;
-    {
-        // more CTAs than the GPU holds at once (four per SM): the second half of the first wave starts late
-        // by the time the first half needs to stream its rows at the HBM rate
-        const uint64_t slots = 4ull * s->dev.sm_count;
-        const uint64_t ctas = (uint64_t)plan.split * P.batch;
-        P.stagger_ns = 0u;
-        if (s->stagger && ctas > slots + slots / 4u) {
-            const double shard_bytes = (double)plan.shard_cols * (P.dtype == LLM_CUDA_DTYPE_BF16 ? 2.0 : 4.0);
-            const double ns = (double)(slots / 2u) * shard_bytes / 6500.0;  // bytes / (6.5e12 B/s) in ns
-            P.stagger_ns = ns > 200000.0 ? 200000u : (uint32_t)ns;
-            P.stagger_lo = (uint32_t)(slots / 2u);
-            P.stagger_hi = (uint32_t)slots;
-        }
-    }
     CUDA_TRY(s, launch_stream_select(P, plan, stream, a->overlap_previous != 0u));
     s->last_kernels++;
     return LLM_CUDA_OK;
@@ -338,13 +323,6 @@ int32_t llm_cuda_last_launch_info(const llm_cuda_sampler* s, uint32_t* kernels_l
 int32_t llm_cuda_debug_phase_buffer(llm_cuda_sampler* s, unsigned long long* device_buffer) {
     if (!s) return LLM_CUDA_ERR_BAD_ARGUMENT;
     s->phase_ns = device_buffer;
-    return LLM_CUDA_OK;
-}
-
-// Development aid (not part of the public header): 0 starts every CTA of a large grid at once.
-int32_t llm_cuda_debug_stagger(llm_cuda_sampler* s, uint32_t on) {
-    if (!s) return LLM_CUDA_ERR_BAD_ARGUMENT;
-    s->stagger = on != 0u;
     return LLM_CUDA_OK;
 }
 

@@ -625,18 +625,6 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
     // writes shared memory only until it has passed grid_dependency_wait(): that comes right before a
     // row's outputs are written, before the split-row scratch and before the full-ordering scratch.
     grid_launch_dependents();
-    if (P.stagger_ns) {
-        // A grid of more CTAs than the GPU holds at once would stream all resident rows together and
-        // then order them all together, with HBM idle. The CTAs that take the second half of each SM's
-        // slots in the first wave start late by the time the first half needs to stream, so the two
-        // halves (and every CTA that later inherits their slots) take turns on HBM. A plain delay:
-        // nobody waits for anybody.
-        const uint32_t lin = blockIdx.y * gridDim.x + blockIdx.x;
-        if (lin >= P.stagger_lo && lin < P.stagger_hi) {
-            const unsigned long long until = global_ns() + P.stagger_ns;
-            for (int i = 0; i < 4096 && global_ns() < until; ++i) __nanosleep(200);
-        }
-    }
     if (tid == 0) {
         resolve_row(P, b, S.rc);
         // the draw's uniform is an input: fetched now, its latency is hidden behind the sweep

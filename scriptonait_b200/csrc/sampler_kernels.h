@@ -56,7 +56,6 @@ struct KParams {
     uint32_t* out_cnt;
     uint32_t out_stride;
     uint32_t force_full;
-    uint32_t stagger_ns, stagger_lo, stagger_hi;  // CTAs stagger_lo <= linear id < stagger_hi start stagger_ns late (0 = off)
     uint32_t row_base;              // this launch handles rows row_base .. row_base + gridDim.y - 1
     // full ordering of the rare rows the stream cannot decide: scratch slots claimed by the row's own CTA
     unsigned long long* full_keys;  // [full_nslots][full_vpad] 64-bit sort keys, or NULL = no such stage
