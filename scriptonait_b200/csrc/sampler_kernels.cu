@@ -625,48 +625,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
     // writes shared memory only until it has passed grid_dependency_wait(): that comes right before a
     // row's outputs are written, before the split-row scratch and before the full-ordering scratch.
     grid_launch_dependents();
-    if (tid == 0) {
-        resolve_row(P, b, S.rc);
-        // the draw's uniform is an input: fetched now, its latency is hidden behind the sweep
-        S.u_pre_valid = P.out_q ? 0u : 1u;
-        S.u_pre = P.out_q ? 0.0f : row_uniform(P, b);
-        S.count = 0u;
-        S.tau_key = LOWEST;
-        S.max_key = LOWEST;
-        S.error = 0u;
-        S.last = 0u;
-#pragma unroll
-        for (int i = 0; i < RING_STAGES; ++i) {
-            mbar_init(&full_bar[i], 1u);
-            mbar_init(&empty_bar[i], (uint32_t)WARPS);
-        }
-        mbar_fence_init();
-    }
-    __syncthreads();  // the one barrier all STREAM_THREADS threads share
-    RowCfg rc = S.rc;
-    if (MODE == 1) rc.windowed = 1u;  // lets the compiler drop the exact-selection code
-    if (MODE == 2) rc.windowed = 0u;  // ... or the window code
-    PHASE(0);
-    if (rc.invalid) {
-        grid_dependency_wait();
-        if (shard == 0 && tid == 0) {
-            if (P.out_q) {
-                P.out_cnt[b] = 0u;
-            } else {
-                P.tokens[b] = 0u;
-                if (P.row_flags) P.row_flags[b] = LLM_CUDA_ROW_INVALID;
-                if (P.kept_count) P.kept_count[b] = 0u;
-            }
-        }
-        return;
-    }
-    if (P.force_full) {
-        grid_dependency_wait();
-        if (warp < (unsigned)WARPS && shard == 0) full_sort_row(P, b, *reinterpret_cast<FullShared*>(ring), hkeys, hcnt);
-        return;
-    }
 
-    // ---- this CTA's columns and their 16-byte alignment
+    // ---- this CTA's columns and their 16-byte alignment (independent of the row's parameters)
     const uint32_t c0 = shard * P.shard_cols;
     const uint32_t c1 = min(c0 + P.shard_cols, P.vocab);
     const uint32_t ncols = c1 - c0;
@@ -679,26 +639,82 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
     const uint32_t ntail = ncols - tail0;
     const uint32_t gid0 = P.col_offset + c0;                          // global id of column c0
     const unsigned char* vbase = reinterpret_cast<const unsigned char*>(row + c0 + head);  // 16-byte aligned
-    const float T = rc.T;
-    const uint32_t ntiles = (nvi + VPS - 1u) / VPS;
+    const uint32_t vtiles = (nvi + VPS - 1u) / VPS;
+    const uint32_t first_stages = min((uint32_t)RING_STAGES, vtiles);
 
-    // ---- start the ring before anything else: the copies run while the side tables are built
-    const uint32_t vtiles = ntiles;
-    auto issue = [&](uint32_t tt) {  // thread 0 only
-        const uint32_t t = tt;
-        const uint32_t first = t * VPS;
+    auto issue = [&](uint32_t tt) {  // the producer lane only
+        const uint32_t first = tt * VPS;
         const uint32_t nv = min(VPS, nvi - first);
         uint64_t* bar = &full_bar[tt % RING_STAGES];
         mbar_expect_tx(bar, nv * 16u);
         bulk_load(ring + (size_t)(tt % RING_STAGES) * STAGE_BYTES, vbase + (size_t)first * 16u, nv * 16u, bar);
     };
+    // ---- the ring starts before anything else: the producer lane sets up the barriers and requests the
+    //      first stages while thread 0 still reads the row's parameters
+    if (tid == (uint32_t)THREADS) {
+#pragma unroll
+        for (int i = 0; i < RING_STAGES; ++i) {
+            mbar_init(&full_bar[i], 1u);
+            mbar_init(&empty_bar[i], (uint32_t)WARPS);
+        }
+        mbar_fence_init();
+        for (uint32_t tt = 0; tt < first_stages; ++tt) issue(tt);
+    }
+    // the draw's uniform is an input: one thread requests its ingredients now and finishes it after the
+    // tables are built, so that the latency hides behind the sweep
+    const bool fetch_u = (tid == 32u) && !P.out_q;
+    uint64_t u_seed = 0ull, u_done = 0ull;
+    float u_given = 0.0f;
+    if (fetch_u) {
+        if (P.uniforms) {
+            u_given = P.uniforms[b];
+        } else {
+            u_seed = P.seeds ? P.seeds[b] : P.seed_base + (uint64_t)b;
+            u_done = P.draw_index ? P.draw_index[b] : 0ull;
+        }
+    }
+    if (tid == 0) {
+        resolve_row(P, b, S.rc);
+        S.u_pre_valid = 0u;
+        S.count = 0u;
+        S.tau_key = LOWEST;
+        S.max_key = LOWEST;
+        S.error = 0u;
+        S.last = 0u;
+    }
+    __syncthreads();  // the one barrier all STREAM_THREADS threads share
+    RowCfg rc = S.rc;
+    if (MODE == 1) rc.windowed = 1u;  // lets the compiler drop the exact-selection code
+    if (MODE == 2) rc.windowed = 0u;  // ... or the window code
+    PHASE(0);
+    if (rc.invalid || P.force_full) {
+        // the stages already requested must have landed before this CTA's shared memory is given up
+        for (uint32_t tt = 0; tt < first_stages; ++tt) (void)mbar_wait_bounded(&full_bar[tt], 0u);
+        grid_dependency_wait();
+        if (rc.invalid) {
+            if (shard == 0 && tid == 0) {
+                if (P.out_q) {
+                    P.out_cnt[b] = 0u;
+                } else {
+                    P.tokens[b] = 0u;
+                    if (P.row_flags) P.row_flags[b] = LLM_CUDA_ROW_INVALID;
+                    if (P.kept_count) P.kept_count[b] = 0u;
+                }
+            }
+            return;
+        }
+        __syncthreads();  // every thread has seen its stages land: the ring may be reused
+        if (warp < (unsigned)WARPS && shard == 0) full_sort_row(P, b, *reinterpret_cast<FullShared*>(ring), hkeys, hcnt);
+        return;
+    }
+    const float T = rc.T;
+
     if (warp == (unsigned)WARPS) {
         // the producer warp: keeps the ring full, refilling a stage as soon as every consumer warp
         // has released it; it takes no part in the consumers' barriers and leaves when all is issued
         if (lane == 0) {
-            for (uint32_t tt = 0; tt < vtiles; ++tt) {
-                if (tt >= (uint32_t)RING_STAGES &&
-                    !mbar_wait_bounded(&empty_bar[tt % RING_STAGES], ((tt / RING_STAGES) - 1u) & 1u)) {
+            for (uint32_t tt = first_stages; tt < vtiles; ++tt) {
+                if (!mbar_wait_bounded(&empty_bar[tt % RING_STAGES], ((tt / RING_STAGES) - 1u) & 1u)) {
                     atomicOr(&S.error, 4u);  // consumers will time out on the stage as well and report it
                     break;
                 }
@@ -768,6 +784,10 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
     uint32_t end = 0u;  // highest candidate slot handed out, as seen by this warp
     float tmax = neg_inf();  // largest value of the edited row this thread has seen
     PHASE(1);
+    if (fetch_u) {  // read by thread 0 after several more barriers
+        S.u_pre = P.uniforms ? u_given : u24_to_f32(splitmix_output(u_seed, u_done + 1ull));  // rng.rs:31-34
+        S.u_pre_valid = 1u;
+    }
 
     // ---- ids with a penalty: the stream never edits values. Every distinct history id of this
     //      CTA's columns is read once here, masked and penalised; the value replaces the id's count
