@@ -189,9 +189,11 @@ int32_t llm_cuda_shard_select(llm_cuda_sampler* s, const llm_cuda_sample_args* a
 /* Vocabulary sharding, step 2 of 2: after the candidate lists of all `n_shards`
  * have been gathered as [n_shards, batch, cand_stride] (+ counts
  * [n_shards, batch]), merges them per row with the same comparator and runs
- * softmax, min-p, top-p and the draw (generate.rs:368-419). `args` supplies the
- * parameters, RNG and outputs; its logits/history fields are ignored. Every
- * rank that calls this with the same inputs gets the same tokens. */
+ * softmax, min-p, top-p and the draw (generate.rs:368-419). The lists must be
+ * as llm_cuda_shard_select wrote them (each in the reference order, best first):
+ * the merge relies on that order to skip entries that cannot reach the kept set.
+ * `args` supplies the parameters, RNG and outputs; its logits/history fields are
+ * ignored. Every rank that calls this with the same inputs gets the same tokens. */
 int32_t llm_cuda_merge_draw(llm_cuda_sampler* s, const llm_cuda_sample_args* args, const float* cand_values,
                             const uint32_t* cand_ids, const uint32_t* cand_count, uint32_t n_shards,
                             uint32_t cand_stride);

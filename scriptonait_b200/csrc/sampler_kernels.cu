@@ -246,21 +246,43 @@ __device__ bool finish_row(const KParams& P, uint32_t b, const RowCfg& rc, uint3
 // Pulls the candidate lists of `nsh` shards of row b into cand[] (compacting
 // whenever the next list would not fit) and returns the count; `overflow` and
 // `qmax` as finish_row expects them.
+constexpr uint32_t LIST_SORTED = 0x40000000u;  // flag in a list's count: entries are in the reference order
+constexpr uint32_t LIST_COUNT = 0x3fffffffu;
+
 __device__ uint32_t merge_lists(const KParams& P, uint32_t b, const RowCfg& rc, uint32_t nsh, Shared& S, float* cand_q,
-                                uint32_t* cand_i, bool& overflow, float& qmax) {
+                                uint32_t* cand_i, bool& overflow, float& qmax, bool all_sorted = false) {
+    const uint32_t LOWEST = 0x007fffffu;  // okey(-inf)
     if (threadIdx.x == 0) {
         S.count = 0u;
-        S.max_key = 0x007fffffu;
+        S.max_key = LOWEST;
         S.keep = 0u;      // overflow marker seen
         S.newcount = 0u;  // entries of all lists together
+        S.tau_key = LOWEST;      // largest k-th entry of a sorted list
+        S.minkey = 0xffffffffu;  // smallest r-th entry over the lists, r = ceil(k / lists)
     }
     cta_sync();
+    // Rank-cut rows: two lower bounds of the k-th largest value come for free from sorted lists. A
+    // list's k-th entry has k entries at or above it; and with r = ceil(k / lists), every list has r
+    // entries at or above its own r-th entry, so the smallest of those has lists * r >= k. Entries
+    // below the better of the two cannot be among the best k and are not copied at all.
+    const uint32_t k = rc.k_eff;
+    const uint32_t r = (k + nsh - 1u) / nsh;
     for (uint32_t s = threadIdx.x; s < nsh; s += THREADS) {
         const size_t at = (size_t)s * P.sc_rows + b;
         if (P.sc_maxkey) atomicMax(&S.max_key, __ldcg(&P.sc_maxkey[at]));
-        const uint32_t cnt = __ldcg(&P.sc_cnt[at]);
-        if (cnt == 0xffffffffu) S.keep = 1u;
-        else atomicAdd(&S.newcount, min(cnt, P.sc_stride));
+        const uint32_t raw = __ldcg(&P.sc_cnt[at]);
+        if (raw == 0xffffffffu) {
+            S.keep = 1u;
+        } else {
+            const uint32_t cnt = min(raw & LIST_COUNT, P.sc_stride);
+            atomicAdd(&S.newcount, cnt);
+            if (!rc.windowed) {
+                const bool sorted = all_sorted || (raw & LIST_SORTED);
+                const float* sq = P.sc_q + at * P.sc_stride;
+                if (sorted && cnt >= k) atomicMax(&S.tau_key, okey(__ldcg(&sq[k - 1u])));
+                atomicMin(&S.minkey, (sorted && cnt >= r) ? okey(__ldcg(&sq[r - 1u])) : LOWEST);
+            }
+        }
     }
     cta_sync();
     overflow = S.keep != 0u;
@@ -268,18 +290,32 @@ __device__ uint32_t merge_lists(const KParams& P, uint32_t b, const RowCfg& rc, 
     const float tq = window_stream_bound(qmax);
     if (!overflow && S.newcount <= P.ccap) {
         // everything fits at once: each warp copies whole lists, all lists in flight together
+        const uint32_t thr = rc.windowed ? LOWEST : max(S.tau_key, S.minkey == 0xffffffffu ? LOWEST : S.minkey);
         const uint32_t lane = threadIdx.x & 31u;
         for (uint32_t s = threadIdx.x >> 5; s < nsh; s += WARPS) {
             const size_t at = (size_t)s * P.sc_rows + b;
-            const uint32_t cnt = min(__ldcg(&P.sc_cnt[at]), P.sc_stride);
-            uint32_t base = 0u;
-            if (lane == 0) base = atomicAdd(&S.count, cnt);
-            base = __shfl_sync(FULL_MASK, base, 0);
+            const uint32_t raw = __ldcg(&P.sc_cnt[at]);
+            const uint32_t cnt = min(raw & LIST_COUNT, P.sc_stride);
+            const bool sorted = all_sorted || (raw & LIST_SORTED);
             const float* sq = P.sc_q + at * P.sc_stride;
             const uint32_t* si = P.sc_i + at * P.sc_stride;
-            for (uint32_t i = lane; i < cnt; i += 32u) {
-                cand_q[base + i] = __ldcg(&sq[i]);
-                cand_i[base + i] = __ldcg(&si[i]);
+            for (uint32_t i0 = 0; i0 < cnt; i0 += 32u) {
+                const uint32_t i = i0 + lane;
+                const float q = i < cnt ? __ldcg(&sq[i]) : 0.0f;
+                const bool pass = i < cnt && okey(q) >= thr;
+                const unsigned m = __ballot_sync(FULL_MASK, pass);
+                if (m == 0u) {
+                    if (sorted && !rc.windowed) break;  // everything further down the list is smaller still
+                    continue;
+                }
+                uint32_t base = 0u;
+                if (lane == 0) base = atomicAdd(&S.count, (uint32_t)__popc(m));
+                base = __shfl_sync(FULL_MASK, base, 0);
+                if (pass) {
+                    const uint32_t slot = base + (uint32_t)__popc(m & ((1u << lane) - 1u));
+                    cand_q[slot] = q;
+                    cand_i[slot] = __ldcg(&si[i]);
+                }
             }
         }
         cta_sync();
@@ -287,7 +323,7 @@ __device__ uint32_t merge_lists(const KParams& P, uint32_t b, const RowCfg& rc, 
     }
     for (uint32_t s = 0; s < nsh && !overflow; ++s) {
         const size_t at = (size_t)s * P.sc_rows + b;
-        const uint32_t cnt = min(__ldcg(&P.sc_cnt[at]), P.sc_stride);
+        const uint32_t cnt = min(__ldcg(&P.sc_cnt[at]) & LIST_COUNT, P.sc_stride);
         uint32_t n = S.count;
         if (n + cnt > P.ccap) {
             if (!rc.windowed) {
@@ -1179,13 +1215,15 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
     // ---- several CTAs share the row: leave this shard's survivors in scratch;
     //      the CTA that arrives last merges them (no CTA ever waits for another)
     grid_dependency_wait();  // the scratch lists and tickets are shared with the previous launch
+    bool list_sorted = false;
     if (!rc.windowed) {
+        if (n > (uint32_t)THREADS) n = keep_top_k(n, rc.k_eff, S, cand_q, cand_i);
         if (n <= (uint32_t)THREADS) {
-            // small enough for the rank sort: ordered and cut at k in two barriers
+            // small enough for the rank sort: ordered (and cut at k) in two barriers; the merging CTA
+            // uses the order to leave most of the list behind
             sort_candidates(n, cand_q, cand_i, reinterpret_cast<uint64_t*>(scratch));
             n = min(n, rc.k_eff);
-        } else {
-            n = keep_top_k(n, rc.k_eff, S, cand_q, cand_i);
+            list_sorted = true;
         }
     } else if (!overflow) {
         n = compact_inplace(
@@ -1203,7 +1241,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
             }
         }
         if (tid == 0) {
-            __stcg(&P.sc_cnt[at], overflow ? 0xffffffffu : n);
+            __stcg(&P.sc_cnt[at], overflow ? 0xffffffffu : (n | (list_sorted ? LIST_SORTED : 0u)));
             __stcg(&P.sc_maxkey[at], okey(qmax));
         }
     }
@@ -1247,7 +1285,8 @@ __global__ void __launch_bounds__(THREADS) merge_draw_kernel(const __grid_consta
     }
     bool overflow;
     float qmax;
-    const uint32_t n = merge_lists(P, b, rc, P.split, S, cand_q, cand_i, overflow, qmax);
+    // the gathered lists were written in order by finish_row on their GPUs
+    const uint32_t n = merge_lists(P, b, rc, P.split, S, cand_q, cand_i, overflow, qmax, /*all_sorted=*/true);
     // the logits of a gathered row live on other GPUs: a row its lists cannot decide is reported
     if (finish_row(P, b, rc, n, overflow, qmax, S, cand_q, cand_i, scratch) && threadIdx.x == 0) report_unresolved(P, b);
 }
