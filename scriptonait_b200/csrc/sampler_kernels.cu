@@ -1042,8 +1042,9 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
         // entries, which the buffer has room for beyond `limit`) and keep the best k when it fills;
         // `tau` then rises to the k-th value, in every thread alike. Window rows that overflow are
         // ordered in full instead.
+        bool can_overflow = true;  // set below from what is still to come: most rows can skip every check
         auto settle = [&]() {
-            if (!sweep_k) return;
+            if (!sweep_k || !can_overflow) return;
             const int over = cta_sync_or(vol_load(&S.count) > P.limit ? 1 : 0);
             if (!over) return;
             uint32_t n2 = min(S.count, P.ccap);
@@ -1061,7 +1062,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
             if (sweep_k) return x >= tau;
             return (__fsub_rn(q, qmaxf) >= WINDOW_EXACT) || (q == qmaxf);  // exactly the terms the reference's sums can see
         };
-        // (1) penalised ids: their edited values wait in the table
+        // (1) penalised ids: their edited values wait in the table (at most half the table is in use)
+        can_overflow = P.hash_slots / 2u + 64u > P.ccap;
         if (BITS) {
             for (uint32_t base = 0; base < P.hash_slots; base += THREADS) {
                 const uint32_t slot = base + tid;
@@ -1109,6 +1111,9 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
         }
         cta_sync();
         const uint32_t nq = S.keep;
+        // everything appended so far plus every element of every flagged vector: if even that fits,
+        // the buffer cannot fill up and the final selection sees it all at once
+        can_overflow = (uint64_t)S.count + (uint64_t)nq * (uint32_t)VEC > (uint64_t)P.ccap;
         // read a flagged vector again (L2) and append the elements that matter; the appends of a
         // warp step share one atomic
         auto examine = [&](bool have, uint32_t v, const uint4& data) {
