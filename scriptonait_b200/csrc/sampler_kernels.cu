@@ -632,12 +632,11 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
     }
 }
 
-template <typename ElemT, bool BITS, int MODE>
+template <typename ElemT, bool BITS, int MODE, int U>
 __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const __grid_constant__ KParams P) {
     constexpr int VEC = Traits<ElemT>::VEC;
-    constexpr uint32_t VPS = STAGE_BYTES / 16u;      // 16-byte vectors per stage
-    constexpr int U = VPS / THREADS;                 // vectors per thread per stage
-    static_assert(VPS % THREADS == 0, "stage geometry");
+    constexpr uint32_t VPS = (uint32_t)U * THREADS;  // 16-byte vectors per stage: U per consumer thread
+    constexpr uint32_t STAGE = VPS * 16u;            // bytes per ring stage (12 KB or 16 KB, the launch plan's choice)
     extern __shared__ __align__(128) unsigned char dyn[];
     __shared__ Shared S;
     __shared__ __align__(8) uint64_t full_bar[RING_STAGES];   // a stage's bytes have landed
@@ -683,7 +682,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
         const uint32_t nv = min(VPS, nvi - first);
         uint64_t* bar = &full_bar[tt % RING_STAGES];
         mbar_expect_tx(bar, nv * 16u);
-        bulk_load(ring + (size_t)(tt % RING_STAGES) * STAGE_BYTES, vbase + (size_t)first * 16u, nv * 16u, bar);
+        bulk_load(ring + (size_t)(tt % RING_STAGES) * STAGE, vbase + (size_t)first * 16u, nv * 16u, bar);
     };
     // ---- the ring starts before anything else: the producer lane sets up the barriers and requests the
     //      first stages while thread 0 still reads the row's parameters
@@ -922,7 +921,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
         const uint32_t t = tt;
         const uint32_t stage = tt % RING_STAGES;
         if (!mbar_wait_bounded(&full_bar[stage], (tt / RING_STAGES) & 1u)) wait_failed = true;
-        const uint4* sv = reinterpret_cast<const uint4*>(ring + (size_t)stage * STAGE_BYTES);
+        const uint4* sv = reinterpret_cast<const uint4*>(ring + (size_t)stage * STAGE);
         float vm[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
@@ -1420,16 +1419,35 @@ int plan_launch(const DeviceInfo& dev, const KParams& base, bool top_k_known, ui
     }
     // one flag word per group of 32 vectors of the shard
     const uint32_t vec_elems = 16u / (base.dtype == LLM_CUDA_DTYPE_BF16 ? 2u : 4u);
-    plan->groups = (shard_cols / vec_elems + 31u) / 32u + WARPS * (STAGE_BYTES / 16u / THREADS);
+    plan->groups = (shard_cols / vec_elems + 31u) / 32u + WARPS * 4u;  // + one stage of slack at the larger stage size
     // rank cuts above 256 keep ceil(k/256) best values per lane
     plan->lane_top_words = (!window_only && kcap > (uint32_t)THREADS) ? kcap : 0u;
     // The candidate buffer and the epilogue scratch (sort keys + probabilities) are used only after the
     // sweep: when both fit into the ring they live there, which is what lets four CTAs share an SM.
-    const size_t ring_bytes = (size_t)RING_STAGES * STAGE_BYTES;
     const size_t cand_bytes = (size_t)plan->ccap * 8u;
     const size_t tables_bytes = (size_t)plan->bitmap_words * 4u + (size_t)plan->hash_slots * 8u +
                                 (size_t)plan->lane_top_words * 4u + (size_t)plan->groups * 4u;
-    if (cand_bytes + EPILOGUE_SCRATCH <= ring_bytes) {
+    // Stage size: 16 KB stages (48 KB in flight per CTA) unless that costs a resident CTA; an SM has
+    // 228 KB of shared memory, and each CTA takes 1 KB of it plus the kernel's static share.
+    auto layout = [&](uint32_t u, size_t* smem, bool* aliased) {
+        const size_t ring_bytes = (size_t)RING_STAGES * u * THREADS * 16u;
+        *aliased = cand_bytes + EPILOGUE_SCRATCH <= ring_bytes;
+        *smem = ring_bytes + tables_bytes + (*aliased ? 0u : cand_bytes);
+    };
+    auto resident = [&](size_t smem) {
+        const size_t per_cta = smem + 1024u + 2304u;
+        const size_t n = 233472u / per_cta;
+        return n > 4u ? (size_t)4u : n;
+    };
+    size_t smem3, smem4;
+    bool alias3, alias4;
+    layout(3u, &smem3, &alias3);
+    layout(4u, &smem4, &alias4);
+    const bool big = smem4 <= dev.max_dyn_smem && resident(smem4) >= resident(smem3);
+    plan->stage_u = big ? 4u : 3u;
+    const bool aliased = big ? alias4 : alias3;
+    const size_t ring_bytes = (size_t)RING_STAGES * plan->stage_u * THREADS * 16u;
+    if (aliased) {
         plan->cand_off = 0u;
         plan->scratch_off = (uint32_t)cand_bytes;
         plan->tables_off = (uint32_t)ring_bytes;
@@ -1446,21 +1464,24 @@ int plan_launch(const DeviceInfo& dev, const KParams& base, bool top_k_known, ui
     return 0;
 }
 
-template <typename ElemT, bool BITS, int MODE>
+template <typename ElemT, bool BITS, int MODE, int U>
 static cudaError_t configure_one(int v) {
-    cudaError_t e = cudaFuncSetAttribute(stream_select_kernel<ElemT, BITS, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, v);
+    cudaError_t e = cudaFuncSetAttribute(stream_select_kernel<ElemT, BITS, MODE, U>, cudaFuncAttributeMaxDynamicSharedMemorySize, v);
     if (e != cudaSuccess) return e;
     // four CTAs of ~55 KB each only fit when the SM's L1/shared split favours shared memory
-    return cudaFuncSetAttribute(stream_select_kernel<ElemT, BITS, MODE>, cudaFuncAttributePreferredSharedMemoryCarveout,
+    return cudaFuncSetAttribute(stream_select_kernel<ElemT, BITS, MODE, U>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                 (int)cudaSharedmemCarveoutMaxShared);
 }
 
 template <typename ElemT, bool BITS>
 static cudaError_t configure_stream(int v) {
     cudaError_t e;
-    if ((e = configure_one<ElemT, BITS, 0>(v)) != cudaSuccess) return e;
-    if ((e = configure_one<ElemT, BITS, 1>(v)) != cudaSuccess) return e;
-    return configure_one<ElemT, BITS, 2>(v);
+    if ((e = configure_one<ElemT, BITS, 0, 3>(v)) != cudaSuccess) return e;
+    if ((e = configure_one<ElemT, BITS, 1, 3>(v)) != cudaSuccess) return e;
+    if ((e = configure_one<ElemT, BITS, 2, 3>(v)) != cudaSuccess) return e;
+    if ((e = configure_one<ElemT, BITS, 0, 4>(v)) != cudaSuccess) return e;
+    if ((e = configure_one<ElemT, BITS, 1, 4>(v)) != cudaSuccess) return e;
+    return configure_one<ElemT, BITS, 2, 4>(v);
 }
 
 cudaError_t configure_kernels(size_t max_dyn_smem) {
@@ -1474,9 +1495,9 @@ cudaError_t configure_kernels(size_t max_dyn_smem) {
     return cudaSuccess;
 }
 
-template <typename ElemT, bool BITS, int MODE>
+template <typename ElemT, bool BITS, int MODE, int U>
 static cudaError_t launch_stream_t(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap, uint32_t rows) {
-    auto kern = stream_select_kernel<ElemT, BITS, MODE>;
+    auto kern = stream_select_kernel<ElemT, BITS, MODE, U>;
     dim3 grid(plan.split, rows, 1);
     if (!overlap) {
         kern<<<grid, STREAM_THREADS, plan.smem, stream>>>(P);
@@ -1498,11 +1519,17 @@ static cudaError_t launch_stream_t(const KParams& P, const LaunchPlan& plan, cud
     return cudaLaunchKernelEx(&cfg, kern, P);
 }
 
+template <typename ElemT, bool BITS, int MODE>
+static cudaError_t launch_stream_u(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap, uint32_t rows) {
+    if (plan.stage_u == 4u) return launch_stream_t<ElemT, BITS, MODE, 4>(P, plan, stream, overlap, rows);
+    return launch_stream_t<ElemT, BITS, MODE, 3>(P, plan, stream, overlap, rows);
+}
+
 template <typename ElemT, bool BITS>
 static cudaError_t launch_stream_m(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap, uint32_t rows) {
-    if (plan.mode == 1) return launch_stream_t<ElemT, BITS, 1>(P, plan, stream, overlap, rows);
-    if (plan.mode == 2) return launch_stream_t<ElemT, BITS, 2>(P, plan, stream, overlap, rows);
-    return launch_stream_t<ElemT, BITS, 0>(P, plan, stream, overlap, rows);
+    if (plan.mode == 1) return launch_stream_u<ElemT, BITS, 1>(P, plan, stream, overlap, rows);
+    if (plan.mode == 2) return launch_stream_u<ElemT, BITS, 2>(P, plan, stream, overlap, rows);
+    return launch_stream_u<ElemT, BITS, 0>(P, plan, stream, overlap, rows);
 }
 
 cudaError_t launch_stream_select(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap, uint32_t rows) {

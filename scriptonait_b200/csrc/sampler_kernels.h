@@ -73,7 +73,7 @@ struct DeviceInfo {
 
 struct LaunchPlan {
     uint32_t split, shard_cols, kcap, ccap, limit, hash_slots, bitmap_words, groups, lane_top_words,
-        cand_off, scratch_off, tables_off, vlist_cap;
+        cand_off, scratch_off, tables_off, vlist_cap, stage_u;  // stage_u: 16-byte vectors per consumer thread and ring stage (3 or 4)
     size_t smem;
     bool bits;  // mask or penalty tables needed
     int mode;   // kernel variant: 0 rows of either kind, 1 window-mode rows only, 2 exact-selection rows only
