@@ -656,11 +656,11 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
     const uint32_t b = blockIdx.y + P.row_base, shard = blockIdx.x, tid = threadIdx.x;
     const unsigned lane = tid & 31u, warp = tid >> 5;
     const uint32_t LOWEST = 0x007fffffu;  // okey(-inf)
-    // A launch that asked to overlap its predecessor may start now. This kernel reads its inputs and
+    // A launch that asked to overlap its predecessor is released by the producer lane of every CTA
+    // once three eighths of the CTA's row have been requested (measured best: released at the very
+    // start, three launches stream at once and then order at once). That launch reads its inputs and
     // writes shared memory only until it has passed grid_dependency_wait(): that comes right before a
     // row's outputs are written, before the split-row scratch and before the full-ordering scratch.
-    grid_launch_dependents();
-
     // ---- this CTA's columns and their 16-byte alignment (independent of the row's parameters)
     const uint32_t c0 = shard * P.shard_cols;
     const uint32_t c1 = min(c0 + P.shard_cols, P.vocab);
@@ -676,6 +676,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
     const unsigned char* vbase = reinterpret_cast<const unsigned char*>(row + c0 + head);  // 16-byte aligned
     const uint32_t vtiles = (nvi + VPS - 1u) / VPS;
     const uint32_t first_stages = min((uint32_t)RING_STAGES, vtiles);
+    // the stage whose request releases a launch that asked to overlap this one (see below)
+    const uint32_t release_at = (vtiles * 3u) / 8u;
 
     auto issue = [&](uint32_t tt) {  // the producer lane only
         const uint32_t first = tt * VPS;
@@ -694,6 +696,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
         }
         mbar_fence_init();
         for (uint32_t tt = 0; tt < first_stages; ++tt) issue(tt);
+        if (release_at < first_stages) grid_launch_dependents();  // a short row: released at once
     }
     // the draw's uniform is an input: one thread requests its ingredients now and finishes it after the
     // tables are built, so that the latency hides behind the sweep
@@ -754,6 +757,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
                     break;
                 }
                 issue(tt);
+                if (tt == release_at) grid_launch_dependents();
             }
         }
         return;
