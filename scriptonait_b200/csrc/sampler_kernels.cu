@@ -388,6 +388,29 @@ __device__ uint32_t acquire_full_slot(const KParams& P) {
     return 0xffffffffu;
 }
 
+// Runs step(value, index) over vals[0..n) in order, identically on every lane of the calling warp:
+// the values come from global memory 32 at a time (one coalesced request, the next chunk requested
+// before the current one is used) and are handed round with shuffles, so a chain of dependent f32
+// operations over a whole row costs its own latency and not one memory round trip per term.
+// step returns false to stop; the index where it stopped is returned (n if it ran through).
+template <class Step>
+__device__ __forceinline__ uint32_t warp_chain(const float* vals, uint32_t n, Step step) {
+    const unsigned lane = threadIdx.x & 31u;
+    float next = lane < n ? __ldcg(&vals[lane]) : 0.0f;
+    for (uint32_t i0 = 0; i0 < n; i0 += 32u) {
+        const float cur = next;
+        const uint32_t ahead = i0 + 32u + lane;
+        next = ahead < n ? __ldcg(&vals[ahead]) : 0.0f;
+#pragma unroll 8
+        for (uint32_t j = 0; j < 32u; ++j) {
+            const float v = __shfl_sync(FULL_MASK, cur, (int)j);
+            if (i0 + j >= n) return n;
+            if (!step(v, i0 + j)) return i0 + j;
+        }
+    }
+    return n;
+}
+
 __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullShared& F, uint32_t* hkeys, uint32_t* hcnt) {
     const uint32_t tid = threadIdx.x;
     const uint32_t V = P.vocab;
@@ -503,15 +526,17 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
         mx = q_at(0);
         for (uint32_t i = tid; i < n; i += THREADS) __stcg(&vals[i], exp_f32(__fsub_rn(q_at(i), mx)));
         cta_sync();
-        if (tid == 0) {
+        if (tid < 32u) {  // warp 0 runs the sequential chains, every lane alike
             float s = 0.0f;
-            for (uint32_t i = 0; i < n; ++i) {
-                const float e = __ldcg(&vals[i]);
-                if (e < 5.9604644775390625e-08f && s >= 1.0f) break;
+            warp_chain(vals, n, [&](float e, uint32_t) {
+                if (e < 5.9604644775390625e-08f && s >= 1.0f) return false;  // this and every later term is a no-op
                 s = __fadd_rn(s, e);
+                return true;
+            });
+            if (tid == 0) {
+                F.sum = s;
+                F.keep = n;
             }
-            F.sum = s;
-            F.keep = n;
         }
         cta_sync();
         const float sum = F.sum;
@@ -542,7 +567,7 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
                 }
                 cta_sync();
             }
-            if (tid == 0) {
+            if (tid < 32u) {
                 const uint32_t keep_minp = F.keep;
                 uint32_t keep = keep_minp;
                 float total = 0.0f;
@@ -550,55 +575,53 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
                 const float tiny = __fmul_rn(p0, 1.4901161193847656e-08f);  // 2^-26 of the leader: below half an ulp of any running sum
                 if (rc.top_p < 1.0f) {
                     float cum = 0.0f;
-                    for (uint32_t i = 0; i < keep_minp; ++i) {
-                        const float p = __ldcg(&vals[i]);
-                        if (p < tiny) break;  // this and all later terms leave cum unchanged: top_p is never reached
+                    const float top_p = rc.top_p;
+                    warp_chain(vals, keep_minp, [&](float p, uint32_t i) {
+                        if (p < tiny) return false;  // this and all later terms leave cum unchanged: top_p is never reached
                         cum = __fadd_rn(cum, p);
-                        if (cum >= rc.top_p) {
+                        if (cum >= top_p) {
                             keep = i + 1u;
-                            break;
+                            return false;
                         }
-                    }
+                        return true;
+                    });
                     total = cum;
                 } else {
-                    for (uint32_t i = 0; i < keep_minp; ++i) {
-                        const float p = __ldcg(&vals[i]);
-                        if (p < tiny) break;
+                    warp_chain(vals, keep_minp, [&](float p, uint32_t) {
+                        if (p < tiny) return false;
                         total = __fadd_rn(total, p);
-                    }
+                        return true;
+                    });
                 }
-                float u;
-                if (P.uniforms) {
-                    u = P.uniforms[b];
-                } else {
-                    const uint64_t seed = P.seeds ? P.seeds[b] : P.seed_base + (uint64_t)b;
-                    const uint64_t dn = P.draw_index ? P.draw_index[b] : 0ull;
-                    u = u24_to_f32(splitmix_output(seed, dn + 1ull));
-                }
+                const float u = row_uniform(P, b);
                 float rr = __fmul_rn(u, total);
-                F.total = total;
-                F.u = u;
-                F.r = rr;
+                const float r0 = rr;
                 uint32_t flags = LLM_CUDA_ROW_DRAW_CONSUMED;
-                uint32_t token = 0u;
                 bool found = false;
-                for (uint32_t i = 0; i < keep; ++i) {
-                    const float p = __ldcg(&vals[i]);
+                const uint32_t at = warp_chain(vals, keep, [&](float p, uint32_t) {
                     if (rr < p) {
-                        token = id_at(i);
                         found = true;
-                        break;
+                        return false;
                     }
                     rr = __fsub_rn(rr, p);
-                }
-                if (!found) {
+                    return true;
+                });
+                uint32_t token;
+                if (found) {
+                    token = id_at(at);
+                } else {
                     token = id_at(keep - 1u);
                     flags |= LLM_CUDA_ROW_FALLBACK_LAST;
                 }
-                F.token = token;
-                F.flags = flags;
-                F.keep = keep;
-                F.kept_n = keep;
+                if (tid == 0) {
+                    F.total = total;
+                    F.u = u;
+                    F.r = r0;
+                    F.token = token;
+                    F.flags = flags;
+                    F.keep = keep;
+                    F.kept_n = keep;
+                }
             }
         }
     }
