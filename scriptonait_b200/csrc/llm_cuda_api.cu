@@ -281,10 +281,10 @@ int32_t llm_cuda_sampler_create(int32_t device, uint32_t max_batch, uint32_t max
     if ((e = cudaSetDevice(device)) != cudaSuccess) return bail("cudaSetDevice", e);
     if ((e = configure_kernels(s->dev.max_dyn_smem)) != cudaSuccess) return bail("cudaFuncSetAttribute", e);
     s->sc_lists = max_batch > 4096u ? max_batch : 4096u;
-    s->vpad = pow2_ceil_u32(max_vocab);
-    // one slot per CTA that can be resident at a time would never make a row wait; two per SM is close
-    // to that and rows that need the full ordering are rare
-    s->nslots = 2u * s->dev.sm_count;
+    s->vpad = (max_vocab + 1023u) & ~1023u;
+    // one slot per SM: 20 bytes per column (two key/index array pairs and the probabilities); rows that
+    // need the full ordering are rare, and a CTA that finds every slot taken waits for one (bounded)
+    s->nslots = s->dev.sm_count;
     if (s->nslots > max_batch) s->nslots = max_batch;
     if ((e = cudaMalloc(&s->sc_q, kScratchEntries * 4u)) != cudaSuccess) return bail("cudaMalloc", e);
     if ((e = cudaMalloc(&s->sc_i, kScratchEntries * 4u)) != cudaSuccess) return bail("cudaMalloc", e);
@@ -292,7 +292,7 @@ int32_t llm_cuda_sampler_create(int32_t device, uint32_t max_batch, uint32_t max
     if ((e = cudaMalloc(&s->sc_maxkey, (size_t)s->sc_lists * 4u)) != cudaSuccess) return bail("cudaMalloc", e);
     if ((e = cudaMalloc(&s->sc_ticket, (size_t)max_batch * 4u)) != cudaSuccess) return bail("cudaMalloc", e);
     if ((e = cudaMalloc(&s->full_slots, (size_t)s->nslots * 4u)) != cudaSuccess) return bail("cudaMalloc", e);
-    if ((e = cudaMalloc(&s->full_keys, (size_t)s->nslots * s->vpad * 8u)) != cudaSuccess) return bail("cudaMalloc", e);
+    if ((e = cudaMalloc(&s->full_keys, (size_t)s->nslots * s->vpad * 16u)) != cudaSuccess) return bail("cudaMalloc", e);
     if ((e = cudaMalloc(&s->full_vals, (size_t)s->nslots * s->vpad * 4u)) != cudaSuccess) return bail("cudaMalloc", e);
     if ((e = cudaMemset(s->sc_ticket, 0, (size_t)max_batch * 4u)) != cudaSuccess) return bail("cudaMemset", e);
     if ((e = cudaMemset(s->full_slots, 0, (size_t)s->nslots * 4u)) != cudaSuccess) return bail("cudaMemset", e);

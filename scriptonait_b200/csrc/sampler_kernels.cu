@@ -358,8 +358,9 @@ __device__ uint32_t merge_lists(const KParams& P, uint32_t b, const RowCfg& rc, 
 // instruction cache): 0 = rows of either kind, 1 = every row runs in window mode, 2 = no row does.
 constexpr int STREAM_THREADS = THREADS + 32;  // THREADS consumers + one warp that only issues the bulk copies
 // ---------------------------------------------------------------------------
-// Full ordering of a row in global scratch (bitonic sort of 64-bit keys), then
-// the ordered tail exactly as the reference walks it. Slow and rarely needed:
+// Full ordering of a row in global scratch (stable radix sort of 32-bit keys with
+// the column index as payload, L2-resident), then the ordered tail exactly as the
+// reference walks it. Much slower than the streaming path and rarely needed:
 // rows whose window overflowed or whose kept set / walk left the window. Run by
 // the 256 consumer threads of the CTA that found the row undecided, in one of
 // P.full_nslots scratch slots; `hkeys/hcnt` is the CTA's id->count table
@@ -411,11 +412,11 @@ __device__ __forceinline__ uint32_t warp_chain(const float* vals, uint32_t n, St
     return n;
 }
 
-__device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullShared& F, uint32_t* hkeys, uint32_t* hcnt) {
+__device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullShared& F, uint32_t* work, uint32_t* hkeys,
+                                           uint32_t* hcnt) {
     const uint32_t tid = threadIdx.x;
+    const unsigned lane = tid & 31u, warp = tid >> 5;
     const uint32_t V = P.vocab;
-    uint32_t m = 1u;
-    while (m < V) m <<= 1;
     grid_dependency_wait();  // the scratch slots are shared with the previous launch
     if (!P.full_keys) {
         if (tid == 0) report_unresolved(P, b);
@@ -445,7 +446,12 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
         }
         return;
     }
-    uint64_t* keys = reinterpret_cast<uint64_t*>(P.full_keys) + (size_t)F.slot * P.full_vpad;
+    // a slot: two (key, index) array pairs for the radix passes to alternate between, and the probabilities
+    uint32_t* slot_base = reinterpret_cast<uint32_t*>(P.full_keys) + (size_t)F.slot * 4u * P.full_vpad;
+    uint32_t* sk = slot_base;                      // keys in
+    uint32_t* si = slot_base + P.full_vpad;        // column indices in
+    uint32_t* dk = slot_base + 2u * P.full_vpad;   // keys out
+    uint32_t* di = slot_base + 3u * P.full_vpad;   // column indices out
     float* vals = P.full_vals + (size_t)F.slot * P.full_vpad;
     if (rc.has_pen) {
         const uint32_t* hist = P.history + (size_t)b * P.hist_stride;
@@ -455,63 +461,112 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
         }
     }
     cta_sync();
-    // ---- keys: ascending u64 order == value descending, index ascending
+    // ---- keys: ~(ordered bits) ascending == value descending; a stable sort from column order gives
+    //      index ascending among equal values, which is the reference's order
     uint32_t myvalid = 0u;
-    for (uint32_t c = tid; c < m; c += THREADS) {
-        uint64_t key = ~0ull;
-        if (c < V) {
-            float x;
-            if (P.dtype == LLM_CUDA_DTYPE_BF16)
-                x = load_logit(reinterpret_cast<const uint16_t*>(P.logits) + (size_t)b * P.row_stride + c);
-            else
-                x = load_logit(reinterpret_cast<const float*>(P.logits) + (size_t)b * P.row_stride + c);
-            const uint32_t gid = P.col_offset + c;
-            if (id_blocked(P, gid)) x = neg_inf();
-            if (rc.has_pen) x = penalize(x, rc.pen, hash_count(hkeys, hcnt, P.hash_slots, gid));
-            const float q = temper(x, rc.T);
-            if (q == q) {
-                key = ((uint64_t)(~okey(q)) << 32) | (uint64_t)c;
-                ++myvalid;
-            }
+    for (uint32_t c = tid; c < V; c += THREADS) {
+        float x;
+        if (P.dtype == LLM_CUDA_DTYPE_BF16)
+            x = load_logit(reinterpret_cast<const uint16_t*>(P.logits) + (size_t)b * P.row_stride + c);
+        else
+            x = load_logit(reinterpret_cast<const float*>(P.logits) + (size_t)b * P.row_stride + c);
+        const uint32_t gid = P.col_offset + c;
+        if (id_blocked(P, gid)) x = neg_inf();
+        if (rc.has_pen) x = penalize(x, rc.pen, hash_count(hkeys, hcnt, P.hash_slots, gid));
+        const float q = temper(x, rc.T);
+        uint32_t key = 0xffffffffu;  // NaN: behind everything (no value maps here: ~okey(-inf) is 0xff800000)
+        if (q == q) {
+            key = ~okey(q);
+            ++myvalid;
         }
-        __stcg(&keys[c], key);
+        __stcg(&sk[c], key);
+        __stcg(&si[c], c);
     }
     if (myvalid) atomicAdd(&F.nvalid, myvalid);
     cta_sync();
-    const uint32_t half = m >> 1;
-    for (uint32_t size = 2u; size <= m; size <<= 1) {
-        for (uint32_t stride = size >> 1; stride > 0u; stride >>= 1) {
-            // the pairs of one pass are disjoint: four of them in flight per thread
-            for (uint32_t t0 = tid; t0 < half; t0 += 4u * THREADS) {
-                uint32_t lo[4];
-                uint64_t a[4], c[4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const uint32_t t = t0 + (uint32_t)u * THREADS;
-                    lo[u] = ((t & ~(stride - 1u)) << 1) | (t & (stride - 1u));
-                    if (t < half) {
-                        a[u] = __ldcg(&keys[lo[u]]);
-                        c[u] = __ldcg(&keys[lo[u] + stride]);
-                    }
-                }
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const uint32_t t = t0 + (uint32_t)u * THREADS;
-                    if (t < half) {
-                        const bool ascending = ((lo[u] & size) == 0u);
-                        if ((a[u] > c[u]) == ascending) {
-                            __stcg(&keys[lo[u]], c[u]);
-                            __stcg(&keys[lo[u] + stride], a[u]);
-                        }
-                    }
-                }
+    // ---- least-significant-digit radix sort, 8 bits per pass, by this CTA alone. Per pass: digit
+    //      histogram, exclusive scan, then a stable scatter in tiles of 1024 keys - warp w takes keys
+    //      [128 w, 128 w + 128) of the tile, 32 consecutive keys per step, so (warp, step, lane) order is
+    //      column order; a key's place is its digit's base + the same-digit keys of earlier warps + those
+    //      earlier in its own warp (`match_any` finds the lanes that share a digit).
+    {
+        uint32_t* hist = work;                  // [256]
+        uint32_t* base = work + 256;            // [256]
+        uint32_t* wtot = work + 512;            // [WARPS]
+        uint32_t* wrun = work + 512 + 32;       // [WARPS][256]
+        const uint32_t n_all = V;
+        for (uint32_t shift = 0; shift < 32u; shift += 8u) {
+            hist[tid] = 0u;
+            cta_sync();
+            for (uint32_t i0 = 0; i0 < n_all; i0 += THREADS) {
+                const uint32_t i = i0 + tid;
+                const bool have = i < n_all;
+                const uint32_t d = have ? ((__ldcg(&sk[i]) >> shift) & 255u) : 256u + lane;  // absent: a digit nobody shares
+                const unsigned peers = __match_any_sync(FULL_MASK, d);
+                if (have && (peers & ((1u << lane) - 1u)) == 0u) atomicAdd(&hist[d], (uint32_t)__popc(peers));
             }
             cta_sync();
+            const uint32_t mine = hist[tid];
+            if (cta_sync_or(mine == n_all ? 1 : 0)) continue;  // every key has the same digit: nothing moves
+            uint32_t incl = mine;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t y = __shfl_up_sync(FULL_MASK, incl, o);
+                if (lane >= (unsigned)o) incl += y;
+            }
+            if (lane == 31) wtot[warp] = incl;
+            cta_sync();
+            uint32_t pre = 0u;
+            for (uint32_t w = 0; w < warp; ++w) pre += wtot[w];
+            base[tid] = pre + incl - mine;
+            cta_sync();
+            for (uint32_t tile = 0; tile < n_all; tile += 1024u) {
+                for (uint32_t j = lane; j < 256u; j += 32u) wrun[warp * 256u + j] = 0u;
+                uint32_t k[4], id[4], d[4], rank[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const uint32_t i = tile + warp * 128u + (uint32_t)e * 32u + lane;
+                    const bool have = i < n_all;
+                    k[e] = have ? __ldcg(&sk[i]) : 0u;
+                    id[e] = have ? __ldcg(&si[i]) : 0u;
+                    d[e] = have ? ((k[e] >> shift) & 255u) : 256u + lane;
+                }
+                __syncwarp();
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const unsigned peers = __match_any_sync(FULL_MASK, d[e]);
+                    const uint32_t lower = (uint32_t)__popc(peers & ((1u << lane) - 1u));
+                    rank[e] = d[e] < 256u ? wrun[warp * 256u + d[e]] + lower : 0u;
+                    __syncwarp();
+                    if (d[e] < 256u && lower == 0u) wrun[warp * 256u + d[e]] += (uint32_t)__popc(peers);
+                    __syncwarp();
+                }
+                cta_sync();
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    if (d[e] < 256u) {
+                        uint32_t off = base[d[e]] + rank[e];
+                        for (uint32_t w = 0; w < warp; ++w) off += wrun[w * 256u + d[e]];
+                        __stcg(&dk[off], k[e]);
+                        __stcg(&di[off], id[e]);
+                    }
+                }
+                cta_sync();
+                {
+                    uint32_t add = 0u;
+#pragma unroll
+                    for (uint32_t w = 0; w < (uint32_t)WARPS; ++w) add += wrun[w * 256u + tid];
+                    base[tid] += add;
+                }
+                cta_sync();
+            }
+            uint32_t* t = sk; sk = dk; dk = t;
+            t = si; si = di; di = t;
         }
     }
     const uint32_t n = min(F.nvalid, rc.k_eff);
-    auto q_at = [&](uint32_t i) { return okey_to_float(~(uint32_t)(__ldcg(&keys[i]) >> 32)); };
-    auto id_at = [&](uint32_t i) { return P.col_offset + (uint32_t)(__ldcg(&keys[i]) & 0xffffffffull); };
+    auto q_at = [&](uint32_t i) { return okey_to_float(~__ldcg(&sk[i])); };
+    auto id_at = [&](uint32_t i) { return P.col_offset + __ldcg(&si[i]); };
     float mx = 0.f;
     bool done = false;
     if (rc.greedy || n == 0u) {
@@ -765,7 +820,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
             return;
         }
         __syncthreads();  // every thread has seen its stages land: the ring may be reused
-        if (warp < (unsigned)WARPS && shard == 0) full_sort_row(P, b, *reinterpret_cast<FullShared*>(ring), hkeys, hcnt);
+        if (warp < (unsigned)WARPS && shard == 0) full_sort_row(P, b, *reinterpret_cast<FullShared*>(ring), reinterpret_cast<uint32_t*>(ring + 512), hkeys, hcnt);
         return;
     }
     const float T = rc.T;
@@ -1239,7 +1294,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
 
     if (P.split == 1u) {
         if (finish_row(P, b, rc, n, overflow, qmax, S, cand_q, cand_i, scratch, window_filtered))
-            full_sort_row(P, b, *reinterpret_cast<FullShared*>(ring), hkeys, hcnt);
+            full_sort_row(P, b, *reinterpret_cast<FullShared*>(ring), reinterpret_cast<uint32_t*>(ring + 512), hkeys, hcnt);
         return;
     }
 
@@ -1288,7 +1343,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
     __threadfence();
     n = merge_lists(P, b, rc, P.split, S, cand_q, cand_i, overflow, qmax);
     if (finish_row(P, b, rc, n, overflow, qmax, S, cand_q, cand_i, scratch))
-        full_sort_row(P, b, *reinterpret_cast<FullShared*>(ring), hkeys, hcnt);
+        full_sort_row(P, b, *reinterpret_cast<FullShared*>(ring), reinterpret_cast<uint32_t*>(ring + 512), hkeys, hcnt);
 }
 
 // Ordered tail over gathered candidate lists: one CTA per row.

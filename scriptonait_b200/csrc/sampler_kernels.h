@@ -58,7 +58,7 @@ struct KParams {
     uint32_t force_full;
     uint32_t row_base;              // this launch handles rows row_base .. row_base + gridDim.y - 1
     // full ordering of the rare rows the stream cannot decide: scratch slots claimed by the row's own CTA
-    unsigned long long* full_keys;  // [full_nslots][full_vpad] 64-bit sort keys, or NULL = no such stage
+    unsigned long long* full_keys;  // [full_nslots][4][full_vpad] 32-bit words (keys in/out, column indices in/out), or NULL = no such stage
     float* full_vals;               // [full_nslots][full_vpad]
     uint32_t* full_slots;           // [full_nslots] 0 = free, 1 = taken; all zero between launches
     uint32_t full_vpad, full_nslots;
