@@ -389,24 +389,40 @@ __device__ uint32_t acquire_full_slot(const KParams& P) {
     return 0xffffffffu;
 }
 
-// Runs step(value, index) over vals[0..n) in order, identically on every lane of the calling warp:
-// the values come from global memory 32 at a time (one coalesced request, the next chunk requested
-// before the current one is used) and are handed round with shuffles, so a chain of dependent f32
-// operations over a whole row costs its own latency and not one memory round trip per term.
-// step returns false to stop; the index where it stopped is returned (n if it ran through).
-template <class Step>
-__device__ __forceinline__ uint32_t warp_chain(const float* vals, uint32_t n, Step step) {
+// A chain of dependent rounded f32 operations acc = op(acc, vals[i]) over vals[0..n), in order, run
+// identically on every lane of the calling warp. The values come from global memory 32 at a time (one
+// coalesced request, the next chunk requested before the current one is used) and are handed round
+// with shuffles, so the chain costs its own latency and not one memory round trip per term.
+//   hit(before, after, v)  evaluated for every element; the chain stops at the first element where it
+//                          holds: its index is returned and acc is left as it was after that element.
+//   rest_is_noop(v0, acc)  asked once per chunk with the chunk's first value: true means no later
+//                          element can change acc or hit (values are in descending order), so stop.
+// Returns n when nothing hit. Elements past n read as 0.0f, which op must leave acc unchanged for.
+template <class Op, class Hit, class Noop>
+__device__ __forceinline__ uint32_t warp_chain(const float* vals, uint32_t n, float& acc, Op op, Hit hit, Noop rest_is_noop) {
     const unsigned lane = threadIdx.x & 31u;
     float next = lane < n ? __ldcg(&vals[lane]) : 0.0f;
     for (uint32_t i0 = 0; i0 < n; i0 += 32u) {
         const float cur = next;
         const uint32_t ahead = i0 + 32u + lane;
         next = ahead < n ? __ldcg(&vals[ahead]) : 0.0f;
-#pragma unroll 8
-        for (uint32_t j = 0; j < 32u; ++j) {
-            const float v = __shfl_sync(FULL_MASK, cur, (int)j);
-            if (i0 + j >= n) return n;
-            if (!step(v, i0 + j)) return i0 + j;
+        if (rest_is_noop(__shfl_sync(FULL_MASK, cur, 0), acc)) return n;
+        float mine_before = 0.0f, mine_after = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const float v = __shfl_sync(FULL_MASK, cur, j);
+            const float before = acc;
+            acc = op(acc, v);
+            if ((int)lane == j) {
+                mine_before = before;
+                mine_after = acc;
+            }
+        }
+        const unsigned h = __ballot_sync(FULL_MASK, i0 + lane < n && hit(mine_before, mine_after, cur));
+        if (h) {
+            const int first = __ffs(h) - 1;
+            acc = __shfl_sync(FULL_MASK, mine_after, first);
+            return i0 + (uint32_t)first;
         }
     }
     return n;
@@ -464,23 +480,36 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
     // ---- keys: ~(ordered bits) ascending == value descending; a stable sort from column order gives
     //      index ascending among equal values, which is the reference's order
     uint32_t myvalid = 0u;
-    for (uint32_t c = tid; c < V; c += THREADS) {
-        float x;
-        if (P.dtype == LLM_CUDA_DTYPE_BF16)
-            x = load_logit(reinterpret_cast<const uint16_t*>(P.logits) + (size_t)b * P.row_stride + c);
-        else
-            x = load_logit(reinterpret_cast<const float*>(P.logits) + (size_t)b * P.row_stride + c);
-        const uint32_t gid = P.col_offset + c;
-        if (id_blocked(P, gid)) x = neg_inf();
-        if (rc.has_pen) x = penalize(x, rc.pen, hash_count(hkeys, hcnt, P.hash_slots, gid));
-        const float q = temper(x, rc.T);
-        uint32_t key = 0xffffffffu;  // NaN: behind everything (no value maps here: ~okey(-inf) is 0xff800000)
-        if (q == q) {
-            key = ~okey(q);
-            ++myvalid;
+    for (uint32_t c0 = tid; c0 < V; c0 += 4u * THREADS) {  // four columns per thread and round: their loads travel together
+        float x[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const uint32_t c = c0 + (uint32_t)u * THREADS;
+            x[u] = 0.0f;
+            if (c < V) {
+                if (P.dtype == LLM_CUDA_DTYPE_BF16)
+                    x[u] = load_logit(reinterpret_cast<const uint16_t*>(P.logits) + (size_t)b * P.row_stride + c);
+                else
+                    x[u] = load_logit(reinterpret_cast<const float*>(P.logits) + (size_t)b * P.row_stride + c);
+            }
         }
-        __stcg(&sk[c], key);
-        __stcg(&si[c], c);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const uint32_t c = c0 + (uint32_t)u * THREADS;
+            if (c >= V) continue;
+            const uint32_t gid = P.col_offset + c;
+            float xe = x[u];
+            if (id_blocked(P, gid)) xe = neg_inf();
+            if (rc.has_pen) xe = penalize(xe, rc.pen, hash_count(hkeys, hcnt, P.hash_slots, gid));
+            const float q = temper(xe, rc.T);
+            uint32_t key = 0xffffffffu;  // NaN: behind everything (no value maps here: ~okey(-inf) is 0xff800000)
+            if (q == q) {
+                key = ~okey(q);
+                ++myvalid;
+            }
+            __stcg(&sk[c], key);
+            __stcg(&si[c], c);
+        }
     }
     if (myvalid) atomicAdd(&F.nvalid, myvalid);
     cta_sync();
@@ -498,12 +527,18 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
         for (uint32_t shift = 0; shift < 32u; shift += 8u) {
             hist[tid] = 0u;
             cta_sync();
-            for (uint32_t i0 = 0; i0 < n_all; i0 += THREADS) {
-                const uint32_t i = i0 + tid;
-                const bool have = i < n_all;
-                const uint32_t d = have ? ((__ldcg(&sk[i]) >> shift) & 255u) : 256u + lane;  // absent: a digit nobody shares
-                const unsigned peers = __match_any_sync(FULL_MASK, d);
-                if (have && (peers & ((1u << lane) - 1u)) == 0u) atomicAdd(&hist[d], (uint32_t)__popc(peers));
+            for (uint32_t i0 = 0; i0 < n_all; i0 += 4u * THREADS) {
+                uint32_t d[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const uint32_t i = i0 + (uint32_t)u * THREADS + tid;
+                    d[u] = i < n_all ? ((__ldcg(&sk[i]) >> shift) & 255u) : 256u + lane;  // absent: a digit nobody shares
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const unsigned peers = __match_any_sync(FULL_MASK, d[u]);
+                    if (d[u] < 256u && (peers & ((1u << lane) - 1u)) == 0u) atomicAdd(&hist[d[u]], (uint32_t)__popc(peers));
+                }
             }
             cta_sync();
             const uint32_t mine = hist[tid];
@@ -579,15 +614,27 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
     }
     if (!done) {
         mx = q_at(0);
-        for (uint32_t i = tid; i < n; i += THREADS) __stcg(&vals[i], exp_f32(__fsub_rn(q_at(i), mx)));
+        for (uint32_t i0 = tid; i0 < n; i0 += 4u * THREADS) {
+            float q4[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t i = i0 + (uint32_t)u * THREADS;
+                q4[u] = i < n ? q_at(i) : 0.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t i = i0 + (uint32_t)u * THREADS;
+                if (i < n) __stcg(&vals[i], exp_f32(__fsub_rn(q4[u], mx)));
+            }
+        }
         cta_sync();
         if (tid < 32u) {  // warp 0 runs the sequential chains, every lane alike
+            // Once the sum is >= 1 a term below 2^-24 is under half an ulp and leaves it unchanged, and
+            // the terms only get smaller: adding such terms and stopping before them are the same thing.
             float s = 0.0f;
-            warp_chain(vals, n, [&](float e, uint32_t) {
-                if (e < 5.9604644775390625e-08f && s >= 1.0f) return false;  // this and every later term is a no-op
-                s = __fadd_rn(s, e);
-                return true;
-            });
+            warp_chain(
+                vals, n, s, [](float acc, float e) { return __fadd_rn(acc, e); }, [](float, float, float) { return false; },
+                [](float e0, float acc) { return e0 < 5.9604644775390625e-08f && acc >= 1.0f; });
             if (tid == 0) {
                 F.sum = s;
                 F.keep = n;
@@ -603,7 +650,19 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
             done = true;
         }
         if (!done) {
-            for (uint32_t i = tid; i < n; i += THREADS) __stcg(&vals[i], __fdiv_rn(__ldcg(&vals[i]), sum));
+            for (uint32_t i0 = tid; i0 < n; i0 += 4u * THREADS) {
+                float e4[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const uint32_t i = i0 + (uint32_t)u * THREADS;
+                    e4[u] = i < n ? __ldcg(&vals[i]) : 0.0f;
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const uint32_t i = i0 + (uint32_t)u * THREADS;
+                    if (i < n) __stcg(&vals[i], __fdiv_rn(e4[u], sum));
+                }
+            }
             cta_sync();
             if (rc.min_p > 0.0f) {
                 const float thr = __fmul_rn(rc.min_p, __ldcg(&vals[0]));
@@ -628,39 +687,26 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
                 float total = 0.0f;
                 const float p0 = __ldcg(&vals[0]);
                 const float tiny = __fmul_rn(p0, 1.4901161193847656e-08f);  // 2^-26 of the leader: below half an ulp of any running sum
+                // a term below `tiny` is under half an ulp of any running sum (which is at least the
+                // leader's share): it changes nothing, and neither does anything after it
+                auto add = [](float acc, float p) { return __fadd_rn(acc, p); };
+                auto below_tiny = [=](float p_first, float) { return p_first < tiny; };
                 if (rc.top_p < 1.0f) {
-                    float cum = 0.0f;
                     const float top_p = rc.top_p;
-                    warp_chain(vals, keep_minp, [&](float p, uint32_t i) {
-                        if (p < tiny) return false;  // this and all later terms leave cum unchanged: top_p is never reached
-                        cum = __fadd_rn(cum, p);
-                        if (cum >= top_p) {
-                            keep = i + 1u;
-                            return false;
-                        }
-                        return true;
-                    });
-                    total = cum;
+                    const uint32_t at = warp_chain(vals, keep_minp, total, add,
+                                                   [=](float, float after, float) { return after >= top_p; }, below_tiny);
+                    if (at < keep_minp) keep = at + 1u;  // the first index whose running sum reaches top_p
                 } else {
-                    warp_chain(vals, keep_minp, [&](float p, uint32_t) {
-                        if (p < tiny) return false;
-                        total = __fadd_rn(total, p);
-                        return true;
-                    });
+                    warp_chain(vals, keep_minp, total, add, [](float, float, float) { return false; }, below_tiny);
                 }
                 const float u = row_uniform(P, b);
                 float rr = __fmul_rn(u, total);
                 const float r0 = rr;
                 uint32_t flags = LLM_CUDA_ROW_DRAW_CONSUMED;
-                bool found = false;
-                const uint32_t at = warp_chain(vals, keep, [&](float p, uint32_t) {
-                    if (rr < p) {
-                        found = true;
-                        return false;
-                    }
-                    rr = __fsub_rn(rr, p);
-                    return true;
-                });
+                const uint32_t at = warp_chain(
+                    vals, keep, rr, [](float acc, float p) { return __fsub_rn(acc, p); },
+                    [](float before, float, float p) { return before < p; }, [](float, float) { return false; });
+                const bool found = at < keep;
                 uint32_t token;
                 if (found) {
                     token = id_at(at);
