@@ -1,0 +1,67 @@
+"""The full ordering (stable radix sort + warp chains) against the oracle, bit-exact: vocabularies
+that are not a multiple of the sort's tile, many equal values (the stable sort must keep ascending
+indices), -inf entries, a mask and a penalty inside the full ordering, bf16 rows, top-p and min-p
+cuts deep inside a flat row, and the greedy case."""
+import numpy as np
+import pytest
+
+import oracle
+import parity
+from scriptonait_b200 import native as N
+from scriptonait_b200.workloads import Workload, narrow_bf16
+
+pytestmark = pytest.mark.gpu
+
+
+def _wl(logits, **kw):
+    B = logits.shape[0]
+    kw.setdefault("seeds", np.arange(B, dtype=np.uint64) + np.uint64(991))
+    return Workload("full", logits, batch=B, **kw)
+
+
+def _check(sampler, w, allowed=None, **kw):
+    gpu = parity.run_gpu(sampler, w, kept_capacity=64, allowed=allowed, **kw)
+    orc = parity.run_oracle(w, oracle.EXP_CR, 64, allowed=allowed)
+    assert all(f & N.ROW_FULL_SORT for f in gpu.flags), "these rows are meant to take the full ordering"
+    assert np.array_equal(gpu.tokens, orc.tokens)
+    assert np.array_equal(gpu.kept_count, orc.kept_count)
+    assert np.array_equal(gpu.stats, orc.stats)
+    return gpu
+
+
+@pytest.mark.parametrize("vocab", [5001, 50257, 128256])
+def test_flat_rows_of_several_sizes(sampler, vocab):
+    g = np.random.default_rng(vocab)
+    x = g.normal(0.0, 0.3, (3, vocab)).astype(np.float32)
+    _check(sampler, _wl(x, temperature=1.0, top_k=0, top_p=0.9))
+    _check(sampler, _wl(x, temperature=1.3, top_k=0, top_p=1.0, min_p=0.2))
+
+
+def test_many_equal_values_keep_ascending_indices(sampler):
+    g = np.random.default_rng(3)
+    V = 30000
+    x = g.integers(0, 7, (3, V)).astype(np.float32) * np.float32(0.25)   # seven distinct values
+    x[2, ::3] = -np.inf
+    _check(sampler, _wl(x, temperature=1.0, top_k=0, top_p=0.5))
+    _check(sampler, _wl(narrow_bf16(x), temperature=0.7, top_k=0, top_p=0.8))
+
+
+def test_mask_and_penalty_inside_the_full_ordering(sampler):
+    g = np.random.default_rng(4)
+    V = 20011
+    x = g.normal(0.0, 0.2, (4, V)).astype(np.float32)
+    hist = g.integers(0, V, size=(4, 200), dtype=np.uint32)
+    hist[1, :50] = hist[1, 0]
+    allowed = g.random(V) < 0.7
+    w = _wl(x, temperature=0.9, top_k=0, top_p=0.95, repetition_penalty=1.4, history=hist)
+    _check(sampler, w, allowed=allowed)
+
+
+def test_forced_full_ordering_for_rank_cut_and_greedy_rows(sampler):
+    g = np.random.default_rng(5)
+    V = 9973
+    x = g.normal(0.0, 2.0, (5, V)).astype(np.float32)
+    hist = g.integers(0, V, size=(5, 64), dtype=np.uint32)
+    _check(sampler, _wl(x, temperature=0.8, top_k=300, top_p=0.9, repetition_penalty=1.2, history=hist), force_full_sort=True)
+    gpu = _check(sampler, _wl(x, temperature=0.0), force_full_sort=True)
+    assert list(gpu.tokens) == list(np.argmax(x, axis=1))
