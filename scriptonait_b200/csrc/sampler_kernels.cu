@@ -389,43 +389,73 @@ __device__ uint32_t acquire_full_slot(const KParams& P) {
     return 0xffffffffu;
 }
 
-// A chain of dependent rounded f32 operations acc = op(acc, vals[i]) over vals[0..n), in order, run
-// identically on every lane of the calling warp. The values come from global memory 32 at a time (one
-// coalesced request, the next chunk requested before the current one is used) and are handed round
-// with shuffles, so the chain costs its own latency and not one memory round trip per term.
+// A chain of dependent rounded f32 operations acc = op(acc, vals[i]) over vals[0..n), in order, run by
+// the calling warp: all lanes fetch 128 values at a time with one coalesced 16-byte load each (the
+// next chunk already requested) into a double-buffered shared-memory stage, and lane 0 walks the
+// stage with 16-byte shared loads, so the chain costs about its own dependent latency and not one
+// memory round trip per term. Every lane returns the same result.
 //   hit(before, after, v)  evaluated for every element; the chain stops at the first element where it
 //                          holds: its index is returned and acc is left as it was after that element.
 //   rest_is_noop(v0, acc)  asked once per chunk with the chunk's first value: true means no later
 //                          element can change acc or hit (values are in descending order), so stop.
 // Returns n when nothing hit. Elements past n read as 0.0f, which op must leave acc unchanged for.
+// `vals` is 16-byte aligned; `stage` holds 256 floats.
 template <class Op, class Hit, class Noop>
-__device__ __forceinline__ uint32_t warp_chain(const float* vals, uint32_t n, float& acc, Op op, Hit hit, Noop rest_is_noop) {
+__device__ __forceinline__ uint32_t warp_chain(const float* vals, uint32_t n, float& acc, Op op, Hit hit, Noop rest_is_noop,
+                                               float* stage) {
     const unsigned lane = threadIdx.x & 31u;
-    float next = lane < n ? __ldcg(&vals[lane]) : 0.0f;
-    for (uint32_t i0 = 0; i0 < n; i0 += 32u) {
-        const float cur = next;
-        const uint32_t ahead = i0 + 32u + lane;
-        next = ahead < n ? __ldcg(&vals[ahead]) : 0.0f;
-        if (rest_is_noop(__shfl_sync(FULL_MASK, cur, 0), acc)) return n;
-        float mine_before = 0.0f, mine_after = 0.0f;
+    auto fetch = [&](uint32_t i) {  // four consecutive values starting at i (a multiple of 4), zero past n
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i + 3u < n) {
+            v = __ldcg(reinterpret_cast<const float4*>(vals + i));
+        } else {
+            if (i < n) v.x = __ldcg(&vals[i]);
+            if (i + 1u < n) v.y = __ldcg(&vals[i + 1u]);
+            if (i + 2u < n) v.z = __ldcg(&vals[i + 2u]);
+        }
+        return v;
+    };
+    float4 next = fetch(lane * 4u);
+    uint32_t result = n;
+    for (uint32_t i0 = 0; i0 < n; i0 += 128u) {
+        float* buf = stage + ((i0 >> 7) & 1u) * 128u;
+        *reinterpret_cast<float4*>(buf + lane * 4u) = next;
+        __syncwarp();
+        next = fetch(i0 + 128u + lane * 4u);
+        int stop = 0;
+        if (lane == 0) {
+            if (rest_is_noop(buf[0], acc)) {
+                stop = 1;
+            } else {
+                const uint32_t m = min(128u, n - i0);
+                uint32_t first = 0xffffffffu;
+                float acc_at = acc;
+#pragma unroll 4
+                for (uint32_t j = 0; j < 128u; j += 4u) {
+                    const float4 v = *reinterpret_cast<const float4*>(buf + j);
+                    const float e[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-            const float v = __shfl_sync(FULL_MASK, cur, j);
-            const float before = acc;
-            acc = op(acc, v);
-            if ((int)lane == j) {
-                mine_before = before;
-                mine_after = acc;
+                    for (int c = 0; c < 4; ++c) {
+                        const float before = acc;
+                        acc = op(acc, e[c]);
+                        if (first == 0xffffffffu && j + (uint32_t)c < m && hit(before, acc, e[c])) {
+                            first = j + (uint32_t)c;
+                            acc_at = acc;
+                        }
+                    }
+                }
+                if (first != 0xffffffffu) {
+                    stop = 2;
+                    acc = acc_at;
+                    result = i0 + first;
+                }
             }
         }
-        const unsigned h = __ballot_sync(FULL_MASK, i0 + lane < n && hit(mine_before, mine_after, cur));
-        if (h) {
-            const int first = __ffs(h) - 1;
-            acc = __shfl_sync(FULL_MASK, mine_after, first);
-            return i0 + (uint32_t)first;
-        }
+        stop = __shfl_sync(FULL_MASK, stop, 0);
+        if (stop) break;
     }
-    return n;
+    acc = __shfl_sync(FULL_MASK, acc, 0);
+    return __shfl_sync(FULL_MASK, result, 0);
 }
 
 __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullShared& F, uint32_t* work, uint32_t* hkeys,
@@ -469,6 +499,7 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
     uint32_t* dk = slot_base + 2u * P.full_vpad;   // keys out
     uint32_t* di = slot_base + 3u * P.full_vpad;   // column indices out
     float* vals = P.full_vals + (size_t)F.slot * P.full_vpad;
+    float* chain_stage = reinterpret_cast<float*>(work + 4096);  // 256 floats, clear of the sort's tables
     if (rc.has_pen) {
         const uint32_t* hist = P.history + (size_t)b * P.hist_stride;
         for (uint32_t j = tid; j < rc.hlen; j += THREADS) {
@@ -634,7 +665,7 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
             float s = 0.0f;
             warp_chain(
                 vals, n, s, [](float acc, float e) { return __fadd_rn(acc, e); }, [](float, float, float) { return false; },
-                [](float e0, float acc) { return e0 < 5.9604644775390625e-08f && acc >= 1.0f; });
+                [](float e0, float acc) { return e0 < 5.9604644775390625e-08f && acc >= 1.0f; }, chain_stage);
             if (tid == 0) {
                 F.sum = s;
                 F.keep = n;
@@ -694,10 +725,10 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
                 if (rc.top_p < 1.0f) {
                     const float top_p = rc.top_p;
                     const uint32_t at = warp_chain(vals, keep_minp, total, add,
-                                                   [=](float, float after, float) { return after >= top_p; }, below_tiny);
+                                                   [=](float, float after, float) { return after >= top_p; }, below_tiny, chain_stage);
                     if (at < keep_minp) keep = at + 1u;  // the first index whose running sum reaches top_p
                 } else {
-                    warp_chain(vals, keep_minp, total, add, [](float, float, float) { return false; }, below_tiny);
+                    warp_chain(vals, keep_minp, total, add, [](float, float, float) { return false; }, below_tiny, chain_stage);
                 }
                 const float u = row_uniform(P, b);
                 float rr = __fmul_rn(u, total);
@@ -705,7 +736,7 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
                 uint32_t flags = LLM_CUDA_ROW_DRAW_CONSUMED;
                 const uint32_t at = warp_chain(
                     vals, keep, rr, [](float acc, float p) { return __fsub_rn(acc, p); },
-                    [](float before, float, float p) { return before < p; }, [](float, float) { return false; });
+                    [](float before, float, float p) { return before < p; }, [](float, float) { return false; }, chain_stage);
                 const bool found = at < keep;
                 uint32_t token;
                 if (found) {
