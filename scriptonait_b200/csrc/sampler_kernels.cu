@@ -185,7 +185,7 @@ __device__ __forceinline__ uint32_t warp_rth_largest(uint32_t key, uint32_t r, u
 // After all candidates of a row are in cand[0..n): final selection, ordering
 // and either the ordered tail (token out) or the candidate list out. `scratch`
 // is EPILOGUE_SCRATCH bytes of shared memory nothing else uses any more.
-__device__ bool finish_row(const KParams& P, uint32_t b, const RowCfg& rc, uint32_t n, bool overflow, float qmax, Shared& S,
+__device__ int finish_row(const KParams& P, uint32_t b, const RowCfg& rc, uint32_t n, bool overflow, float qmax, Shared& S,
                            float* cand_q, uint32_t* cand_i, unsigned char* scratch, bool window_filtered = false) {
     uint64_t* keys64 = reinterpret_cast<uint64_t*>(scratch);                     // THREADS 64-bit words
     float* probs = reinterpret_cast<float*>(scratch + (size_t)THREADS * 8u);     // up to MAX_SORT floats
@@ -205,10 +205,10 @@ __device__ bool finish_row(const KParams& P, uint32_t b, const RowCfg& rc, uint3
     // runs out of other values (fewer unmasked values than the rank cut, or nothing finite at all):
     // then the -inf entries belong to the kept set, and the full-sort kernel produces them.
     if (P.allowed_bits && !P.out_q && !overflow) {
-        if (!rc.windowed && n < rc.k_eff) overflow = true;
-        if (rc.windowed && qmax == neg_inf()) overflow = true;
+        if (!rc.windowed && n < rc.k_eff) return 2;
+        if (rc.windowed && qmax == neg_inf()) return 2;
     }
-    if (overflow) return true;
+    if (overflow) return 1;  // the candidates did not fit: the window tier in global memory can still take the row
     PHASE(3);
     sort_candidates(n, cand_q, cand_i, keys64);
     PHASE(4);
@@ -221,7 +221,7 @@ __device__ bool finish_row(const KParams& P, uint32_t b, const RowCfg& rc, uint3
             P.out_i[(size_t)b * P.out_stride + i] = cand_i[i];
         }
         if (threadIdx.x == 0) P.out_cnt[b] = min(n_use, P.out_stride);
-        return false;
+        return 0;
     }
     if (rc.greedy || n_use == 0u) {
         if (threadIdx.x == 0) {
@@ -233,14 +233,14 @@ __device__ bool finish_row(const KParams& P, uint32_t b, const RowCfg& rc, uint3
         }
         cta_sync();
         write_row_outputs(P, b, 0u, S, n_use ? cand_q[0] : 0.f, cand_i, probs, 0u);
-        return false;
+        return 0;
     }
     ordered_tail(P, b, rc, n_use, truncated, rc.k_eff, S, cand_q, cand_i, probs);
     PHASE(5);
-    if (S.out_flags & ROW_NEEDS_FULL) return true;
+    if (S.out_flags & ROW_NEEDS_FULL) return 2;  // the kept set or the walk leaves the window: the whole row is needed
     write_row_outputs(P, b, rc.windowed ? LLM_CUDA_ROW_WINDOWED : 0u, S, cand_q[0], cand_i, probs, S.keep);
     PHASE(6);
-    return false;
+    return 0;
 }
 
 // Pulls the candidate lists of `nsh` shards of row b into cand[] (compacting
@@ -368,7 +368,7 @@ constexpr int STREAM_THREADS = THREADS + 32;  // THREADS consumers + one warp th
 struct FullShared {
     RowCfg rc;
     uint32_t nvalid, keep, token, flags, kept_n, slot;
-    float sum, total, u, r, thr;
+    float sum, total, u, r, thr, mx;
 };
 
 constexpr uint32_t FULL_SLOT_ROUNDS = 1u << 14;
@@ -458,8 +458,12 @@ __device__ __forceinline__ uint32_t warp_chain(const float* vals, uint32_t n, fl
     return __shfl_sync(FULL_MASK, result, 0);
 }
 
+// `try_window` (window rows whose candidates did not fit in shared memory, `win_qmax` their exact
+// maximum after temperature): first only the row's significance window is ordered - usually a few
+// thousand values instead of the whole row - with the same rules about what such a truncated ordering
+// can and cannot decide as the shared-memory path; the whole row follows only if it cannot.
 __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullShared& F, uint32_t* work, uint32_t* hkeys,
-                                           uint32_t* hcnt) {
+                                           uint32_t* hcnt, bool try_window = false, float win_qmax = 0.0f) {
     const uint32_t tid = threadIdx.x;
     const unsigned lane = tid & 31u, warp = tid >> 5;
     const uint32_t V = P.vocab;
@@ -477,7 +481,7 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
         F.flags = 0u;
         F.kept_n = 0u;
         F.token = 0u;
-        F.sum = F.total = F.u = F.r = F.thr = 0.f;
+        F.sum = F.total = F.u = F.r = F.thr = F.mx = 0.f;
     }
     for (uint32_t i = tid; i < P.hash_slots; i += THREADS) {
         hkeys[i] = EMPTY_KEY;
@@ -508,9 +512,72 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
         }
     }
     cta_sync();
+    bool filter = try_window;  // this attempt orders the significance window only
+    for (;;) {
+    uint32_t n_all = V;        // keys to sort
     // ---- keys: ~(ordered bits) ascending == value descending; a stable sort from column order gives
     //      index ascending among equal values, which is the reference's order
     uint32_t myvalid = 0u;
+    if (filter) {
+        // the window's members, compacted in column order: chunks of 1024 columns in the sort's own
+        // (warp, step, lane) order, ballots inside a warp, warp totals across the CTA
+        uint32_t* wtot = work + 512;
+        uint32_t run_base = 0u;  // the same in every thread
+        for (uint32_t chunk = 0; chunk < V; chunk += 1024u) {
+            float x[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const uint32_t c = chunk + warp * 128u + (uint32_t)e * 32u + lane;
+                x[e] = 0.0f;
+                if (c < V) {
+                    if (P.dtype == LLM_CUDA_DTYPE_BF16)
+                        x[e] = load_logit(reinterpret_cast<const uint16_t*>(P.logits) + (size_t)b * P.row_stride + c);
+                    else
+                        x[e] = load_logit(reinterpret_cast<const float*>(P.logits) + (size_t)b * P.row_stride + c);
+                }
+            }
+            uint32_t key[4], pos[4], wcount = 0u;
+            bool in[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const uint32_t c = chunk + warp * 128u + (uint32_t)e * 32u + lane;
+                in[e] = false;
+                key[e] = 0u;
+                if (c < V) {
+                    const uint32_t gid = P.col_offset + c;
+                    float xe = x[e];
+                    if (id_blocked(P, gid)) xe = neg_inf();
+                    if (rc.has_pen) xe = penalize(xe, rc.pen, hash_count(hkeys, hcnt, P.hash_slots, gid));
+                    const float q = temper(xe, rc.T);
+                    in[e] = (__fsub_rn(q, win_qmax) >= WINDOW_EXACT) || (q == win_qmax);  // false for NaN
+                    key[e] = ~okey(q);
+                }
+                const unsigned m = __ballot_sync(FULL_MASK, in[e]);
+                pos[e] = wcount + (uint32_t)__popc(m & ((1u << lane) - 1u));
+                wcount += (uint32_t)__popc(m);
+            }
+            if (lane == 0) wtot[warp] = wcount;
+            cta_sync();
+            uint32_t off = run_base, total = 0u;
+#pragma unroll
+            for (uint32_t w = 0; w < (uint32_t)WARPS; ++w) {
+                const uint32_t t = wtot[w];
+                if (w < warp) off += t;
+                total += t;
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                if (in[e]) {
+                    __stcg(&sk[off + pos[e]], key[e]);
+                    __stcg(&si[off + pos[e]], chunk + warp * 128u + (uint32_t)e * 32u + lane);
+                }
+            }
+            run_base += total;
+            cta_sync();
+        }
+        n_all = run_base;
+        if (tid == 0) myvalid = n_all;
+    } else
     for (uint32_t c0 = tid; c0 < V; c0 += 4u * THREADS) {  // four columns per thread and round: their loads travel together
         float x[4];
 #pragma unroll
@@ -554,7 +621,6 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
         uint32_t* base = work + 256;            // [256]
         uint32_t* wtot = work + 512;            // [WARPS]
         uint32_t* wrun = work + 512 + 32;       // [WARPS][256]
-        const uint32_t n_all = V;
         for (uint32_t shift = 0; shift < 32u; shift += 8u) {
             hist[tid] = 0u;
             cta_sync();
@@ -631,6 +697,9 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
         }
     }
     const uint32_t n = min(F.nvalid, rc.k_eff);
+    // window attempt: the reference's ordering continues past these n entries with values outside the
+    // significance window; what that leaves undecided is handled as in the shared-memory path
+    const bool truncated = filter && n < rc.k_eff;
     auto q_at = [&](uint32_t i) { return okey_to_float(~__ldcg(&sk[i])); };
     auto id_at = [&](uint32_t i) { return P.col_offset + __ldcg(&si[i]); };
     float mx = 0.f;
@@ -645,6 +714,7 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
     }
     if (!done) {
         mx = q_at(0);
+        if (tid == 0) F.mx = mx;
         for (uint32_t i0 = tid; i0 < n; i0 += 4u * THREADS) {
             float q4[4];
 #pragma unroll
@@ -712,10 +782,15 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
                 }
                 cta_sync();
             }
+            // every window entry passed min-p and more entries follow: whether those pass is only
+            // certain when the threshold is at least 2^-24 of the leader
+            const bool unknown_tail = truncated && rc.min_p > 0.0f && F.keep == n && rc.min_p < 5.9604644775390625e-08f;
+            const bool open_tail = truncated && F.keep == n && !(rc.min_p > 0.0f);  // the kept set continues past the window
             if (tid < 32u) {
                 const uint32_t keep_minp = F.keep;
                 uint32_t keep = keep_minp;
                 float total = 0.0f;
+                bool reached = false;
                 const float p0 = __ldcg(&vals[0]);
                 const float tiny = __fmul_rn(p0, 1.4901161193847656e-08f);  // 2^-26 of the leader: below half an ulp of any running sum
                 // a term below `tiny` is under half an ulp of any running sum (which is at least the
@@ -726,7 +801,10 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
                     const float top_p = rc.top_p;
                     const uint32_t at = warp_chain(vals, keep_minp, total, add,
                                                    [=](float, float after, float) { return after >= top_p; }, below_tiny, chain_stage);
-                    if (at < keep_minp) keep = at + 1u;  // the first index whose running sum reaches top_p
+                    if (at < keep_minp) {
+                        keep = at + 1u;  // the first index whose running sum reaches top_p
+                        reached = true;
+                    }
                 } else {
                     warp_chain(vals, keep_minp, total, add, [](float, float, float) { return false; }, below_tiny, chain_stage);
                 }
@@ -738,9 +816,14 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
                     vals, keep, rr, [](float acc, float p) { return __fsub_rn(acc, p); },
                     [](float before, float, float p) { return before < p; }, [](float, float) { return false; }, chain_stage);
                 const bool found = at < keep;
-                uint32_t token;
+                // entries past the window add less than half an ulp to the running sums, so `total` is final
+                const bool tail_kept = open_tail && !reached;
+                uint32_t token = 0u;
                 if (found) {
                     token = id_at(at);
+                    if (unknown_tail) flags = ROW_NEEDS_FULL;
+                } else if (tail_kept || unknown_tail) {
+                    flags = ROW_NEEDS_FULL;  // the walk continues into entries the window dropped
                 } else {
                     token = id_at(keep - 1u);
                     flags |= LLM_CUDA_ROW_FALLBACK_LAST;
@@ -752,12 +835,31 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
                     F.token = token;
                     F.flags = flags;
                     F.keep = keep;
-                    F.kept_n = keep;
+                    F.kept_n = tail_kept ? rc.k_eff : keep;
                 }
             }
         }
     }
     cta_sync();
+    if (filter && (F.flags & ROW_NEEDS_FULL)) {
+        // the window could not settle the row: once more over the whole row
+        cta_sync();  // everyone has seen the flags
+        if (tid == 0) {
+            F.nvalid = 0u;
+            F.keep = 0u;
+            F.flags = 0u;
+            F.kept_n = 0u;
+            F.token = 0u;
+            F.sum = F.total = F.u = F.r = F.thr = F.mx = 0.f;
+        }
+        cta_sync();
+        filter = false;
+        continue;
+    }
+    break;
+    }  // attempts
+    const float mx = F.mx;
+    auto id_at = [&](uint32_t i) { return P.col_offset + __ldcg(&si[i]); };
     const uint32_t flags = F.flags | LLM_CUDA_ROW_FULL_SORT;
     if (tid == 0) {
         P.tokens[b] = F.token;
@@ -1170,6 +1272,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
     }
     cta_sync();
     bool window_filtered = false;  // the candidates already are exactly the window
+    uint32_t flagged_vectors = 0u; // vectors the sweep flagged: an upper bound of the window's size in vectors
     PHASE(7);
     {
         // the sweep fixed the threshold: the penalised ids, the leading / trailing elements and the
@@ -1269,6 +1372,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
         }
         cta_sync();
         const uint32_t nq = S.keep;
+        flagged_vectors = nq;
         // everything appended so far plus every element of every flagged vector: if even that fits,
         // the buffer cannot fill up and the final selection sees it all at once
         can_overflow = (uint64_t)S.count + (uint64_t)nq * (uint32_t)VEC > (uint64_t)P.ccap;
@@ -1370,8 +1474,11 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
     }
 
     if (P.split == 1u) {
-        if (finish_row(P, b, rc, n, overflow, qmax, S, cand_q, cand_i, scratch, window_filtered))
-            full_sort_row(P, b, *reinterpret_cast<FullShared*>(ring), reinterpret_cast<uint32_t*>(ring + 512), hkeys, hcnt);
+        const int undecided = finish_row(P, b, rc, n, overflow, qmax, S, cand_q, cand_i, scratch, window_filtered);
+        if (undecided)
+            // the window alone is tried first unless the sweep flagged most of the row anyway
+            full_sort_row(P, b, *reinterpret_cast<FullShared*>(ring), reinterpret_cast<uint32_t*>(ring + 512), hkeys, hcnt,
+                          undecided == 1 && rc.windowed && !(S.error & 4u) && qmax > neg_inf() && flagged_vectors < nvi / 2u, qmax);
         return;
     }
 
@@ -1419,8 +1526,10 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
     if (tid == 0) P.sc_ticket[b] = 0u;  // re-armed for the next launch on this stream
     __threadfence();
     n = merge_lists(P, b, rc, P.split, S, cand_q, cand_i, overflow, qmax);
-    if (finish_row(P, b, rc, n, overflow, qmax, S, cand_q, cand_i, scratch))
-        full_sort_row(P, b, *reinterpret_cast<FullShared*>(ring), reinterpret_cast<uint32_t*>(ring + 512), hkeys, hcnt);
+    const int undecided = finish_row(P, b, rc, n, overflow, qmax, S, cand_q, cand_i, scratch);
+    if (undecided)
+        full_sort_row(P, b, *reinterpret_cast<FullShared*>(ring), reinterpret_cast<uint32_t*>(ring + 512), hkeys, hcnt,
+                      undecided == 1 && rc.windowed && !(S.error & 4u) && qmax > neg_inf(), qmax);
 }
 
 // Ordered tail over gathered candidate lists: one CTA per row.

@@ -65,3 +65,23 @@ def test_forced_full_ordering_for_rank_cut_and_greedy_rows(sampler):
     _check(sampler, _wl(x, temperature=0.8, top_k=300, top_p=0.9, repetition_penalty=1.2, history=hist), force_full_sort=True)
     gpu = _check(sampler, _wl(x, temperature=0.0), force_full_sort=True)
     assert list(gpu.tokens) == list(np.argmax(x, axis=1))
+
+
+@pytest.mark.parametrize("vocab", [50257, 128256])
+def test_windows_too_large_for_shared_memory_but_far_from_the_whole_row(sampler, vocab):
+    """Rows whose significance window holds thousands of values, not all of them: ordered from the
+    window alone where that decides the row, from the whole row where it cannot (an open tail the
+    draw walks into, a min-p threshold below 2^-24 of the leader)."""
+    g = np.random.default_rng(vocab + 1)
+    x = g.normal(0.0, 4.0, (6, vocab)).astype(np.float32)
+    x[:, 7] = x.max(axis=1) + np.float32(5.0)   # a leader well above the bulk: the window ends inside the bulk's upper tail
+    wide = x.astype(np.float64)
+    inside = ((wide - wide.max(axis=1, keepdims=True)) >= -17.4).sum(axis=1)
+    assert (inside > 2048).all() and (inside < vocab // 4).all(), inside
+    _check(sampler, _wl(x, temperature=1.0, top_k=0, top_p=0.9))
+    _check(sampler, _wl(x, temperature=1.0, top_k=0, top_p=1.0))                 # open tail
+    _check(sampler, _wl(x, temperature=1.0, top_k=0, top_p=0.999, min_p=1e-9))   # threshold below 2^-24
+    _check(sampler, _wl(x, temperature=1.0, top_k=0, top_p=1.0, min_p=0.001))
+    _check(sampler, _wl(x, temperature=1.0, top_k=vocab - 5, top_p=0.95))        # a rank cut beyond exact selection
+    hist = g.integers(0, vocab, size=(6, 100), dtype=np.uint32)
+    _check(sampler, _wl(narrow_bf16(x), temperature=1.1, top_k=0, top_p=0.9, repetition_penalty=1.2, history=hist))
