@@ -458,6 +458,172 @@ __device__ __forceinline__ uint32_t warp_chain(const float* vals, uint32_t n, fl
     return __shfl_sync(FULL_MASK, result, 0);
 }
 
+// The members of a row's significance window, as (key, column) pairs compacted in column order into
+// sk / si; returns their number (the same in every thread). Chunks of 1024 columns in the radix
+// sort's own (warp, step, lane) order, ballots inside a warp, warp totals across the CTA.
+__device__ __noinline__ uint32_t build_window_keys(const KParams& P, uint32_t b, const RowCfg& rc, float win_qmax, uint32_t* sk,
+                                                   uint32_t* si, const uint32_t* hkeys, const uint32_t* hcnt, uint32_t* work) {
+    const uint32_t tid = threadIdx.x;
+    const unsigned lane = tid & 31u, warp = tid >> 5;
+    const uint32_t V = P.vocab;
+    // the window's members, compacted in column order: chunks of 1024 columns in the sort's own
+    // (warp, step, lane) order, ballots inside a warp, warp totals across the CTA
+    uint32_t* wtot = work + 512;
+    uint32_t run_base = 0u;  // the same in every thread
+    for (uint32_t chunk = 0; chunk < V; chunk += 1024u) {
+        float x[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const uint32_t c = chunk + warp * 128u + (uint32_t)e * 32u + lane;
+            x[e] = 0.0f;
+            if (c < V) {
+                if (P.dtype == LLM_CUDA_DTYPE_BF16)
+                    x[e] = load_logit(reinterpret_cast<const uint16_t*>(P.logits) + (size_t)b * P.row_stride + c);
+                else
+                    x[e] = load_logit(reinterpret_cast<const float*>(P.logits) + (size_t)b * P.row_stride + c);
+            }
+        }
+        uint32_t key[4], pos[4], wcount = 0u;
+        bool in[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const uint32_t c = chunk + warp * 128u + (uint32_t)e * 32u + lane;
+            in[e] = false;
+            key[e] = 0u;
+            if (c < V) {
+                const uint32_t gid = P.col_offset + c;
+                float xe = x[e];
+                if (id_blocked(P, gid)) xe = neg_inf();
+                if (rc.has_pen) xe = penalize(xe, rc.pen, hash_count(hkeys, hcnt, P.hash_slots, gid));
+                const float q = temper(xe, rc.T);
+                in[e] = (__fsub_rn(q, win_qmax) >= WINDOW_EXACT) || (q == win_qmax);  // false for NaN
+                key[e] = ~okey(q);
+            }
+            const unsigned m = __ballot_sync(FULL_MASK, in[e]);
+            pos[e] = wcount + (uint32_t)__popc(m & ((1u << lane) - 1u));
+            wcount += (uint32_t)__popc(m);
+        }
+        if (lane == 0) wtot[warp] = wcount;
+        cta_sync();
+        uint32_t off = run_base, total = 0u;
+#pragma unroll
+        for (uint32_t w = 0; w < (uint32_t)WARPS; ++w) {
+            const uint32_t t = wtot[w];
+            if (w < warp) off += t;
+            total += t;
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            if (in[e]) {
+                __stcg(&sk[off + pos[e]], key[e]);
+                __stcg(&si[off + pos[e]], chunk + warp * 128u + (uint32_t)e * 32u + lane);
+            }
+        }
+        run_base += total;
+        cta_sync();
+    }
+    return run_base;
+}
+
+//  least-significant-digit radix sort, 8 bits per pass, by this CTA alone. Per pass: digit
+// histogram, exclusive scan, then a stable scatter in tiles of 1024 keys - warp w takes keys
+// [128 w, 128 w + 128) of the tile, 32 consecutive keys per step, so (warp, step, lane) order is
+// column order; a key's place is its digit's base + the same-digit keys of earlier warps + those
+// earlier in its own warp (`match_any` finds the lanes that share a digit).
+// Sorts n_all (key, column) pairs; the pointers are exchanged so that sk / si hold the result.
+__device__ __noinline__ void radix_sort_row(uint32_t n_all, uint32_t*& sk_io, uint32_t*& si_io, uint32_t*& dk_io, uint32_t*& di_io,
+                                            uint32_t* work) {
+    const uint32_t tid = threadIdx.x;
+    const unsigned lane = tid & 31u, warp = tid >> 5;
+    // local copies: the stores below must not be taken for stores to the caller's pointer variables
+    uint32_t* __restrict__ sk = sk_io;
+    uint32_t* __restrict__ si = si_io;
+    uint32_t* __restrict__ dk = dk_io;
+    uint32_t* __restrict__ di = di_io;
+    uint32_t* hist = work;                  // [256]
+    uint32_t* base = work + 256;            // [256]
+    uint32_t* wtot = work + 512;            // [WARPS]
+    uint32_t* wrun = work + 512 + 32;       // [WARPS][256]
+    for (uint32_t shift = 0; shift < 32u; shift += 8u) {
+        hist[tid] = 0u;
+        cta_sync();
+        for (uint32_t i0 = 0; i0 < n_all; i0 += 4u * THREADS) {
+            uint32_t d[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t i = i0 + (uint32_t)u * THREADS + tid;
+                d[u] = i < n_all ? ((__ldcg(&sk[i]) >> shift) & 255u) : 256u + lane;  // absent: a digit nobody shares
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const unsigned peers = __match_any_sync(FULL_MASK, d[u]);
+                if (d[u] < 256u && (peers & ((1u << lane) - 1u)) == 0u) atomicAdd(&hist[d[u]], (uint32_t)__popc(peers));
+            }
+        }
+        cta_sync();
+        const uint32_t mine = hist[tid];
+        if (cta_sync_or(mine == n_all ? 1 : 0)) continue;  // every key has the same digit: nothing moves
+        uint32_t incl = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t y = __shfl_up_sync(FULL_MASK, incl, o);
+            if (lane >= (unsigned)o) incl += y;
+        }
+        if (lane == 31) wtot[warp] = incl;
+        cta_sync();
+        uint32_t pre = 0u;
+        for (uint32_t w = 0; w < warp; ++w) pre += wtot[w];
+        base[tid] = pre + incl - mine;
+        cta_sync();
+        for (uint32_t tile = 0; tile < n_all; tile += 1024u) {
+            for (uint32_t j = lane; j < 256u; j += 32u) wrun[warp * 256u + j] = 0u;
+            uint32_t k[4], id[4], d[4], rank[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const uint32_t i = tile + warp * 128u + (uint32_t)e * 32u + lane;
+                const bool have = i < n_all;
+                k[e] = have ? __ldcg(&sk[i]) : 0u;
+                id[e] = have ? __ldcg(&si[i]) : 0u;
+                d[e] = have ? ((k[e] >> shift) & 255u) : 256u + lane;
+            }
+            __syncwarp();
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const unsigned peers = __match_any_sync(FULL_MASK, d[e]);
+                const uint32_t lower = (uint32_t)__popc(peers & ((1u << lane) - 1u));
+                rank[e] = d[e] < 256u ? wrun[warp * 256u + d[e]] + lower : 0u;
+                __syncwarp();
+                if (d[e] < 256u && lower == 0u) wrun[warp * 256u + d[e]] += (uint32_t)__popc(peers);
+                __syncwarp();
+            }
+            cta_sync();
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                if (d[e] < 256u) {
+                    uint32_t off = base[d[e]] + rank[e];
+                    for (uint32_t w = 0; w < warp; ++w) off += wrun[w * 256u + d[e]];
+                    __stcg(&dk[off], k[e]);
+                    __stcg(&di[off], id[e]);
+                }
+            }
+            cta_sync();
+            {
+                uint32_t add = 0u;
+#pragma unroll
+                for (uint32_t w = 0; w < (uint32_t)WARPS; ++w) add += wrun[w * 256u + tid];
+                base[tid] += add;
+            }
+            cta_sync();
+        }
+        uint32_t* t = sk; sk = dk; dk = t;
+        t = si; si = di; di = t;
+    }
+    sk_io = sk;
+    si_io = si;
+    dk_io = dk;
+    di_io = di;
+}
+
 // `try_window` (window rows whose candidates did not fit in shared memory, `win_qmax` their exact
 // maximum after temperature): first only the row's significance window is ordered - usually a few
 // thousand values instead of the whole row - with the same rules about what such a truncated ordering
@@ -465,7 +631,6 @@ __device__ __forceinline__ uint32_t warp_chain(const float* vals, uint32_t n, fl
 __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullShared& F, uint32_t* work, uint32_t* hkeys,
                                            uint32_t* hcnt, bool try_window = false, float win_qmax = 0.0f) {
     const uint32_t tid = threadIdx.x;
-    const unsigned lane = tid & 31u, warp = tid >> 5;
     const uint32_t V = P.vocab;
     grid_dependency_wait();  // the scratch slots are shared with the previous launch
     if (!P.full_keys) {
@@ -519,63 +684,7 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
     //      index ascending among equal values, which is the reference's order
     uint32_t myvalid = 0u;
     if (filter) {
-        // the window's members, compacted in column order: chunks of 1024 columns in the sort's own
-        // (warp, step, lane) order, ballots inside a warp, warp totals across the CTA
-        uint32_t* wtot = work + 512;
-        uint32_t run_base = 0u;  // the same in every thread
-        for (uint32_t chunk = 0; chunk < V; chunk += 1024u) {
-            float x[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const uint32_t c = chunk + warp * 128u + (uint32_t)e * 32u + lane;
-                x[e] = 0.0f;
-                if (c < V) {
-                    if (P.dtype == LLM_CUDA_DTYPE_BF16)
-                        x[e] = load_logit(reinterpret_cast<const uint16_t*>(P.logits) + (size_t)b * P.row_stride + c);
-                    else
-                        x[e] = load_logit(reinterpret_cast<const float*>(P.logits) + (size_t)b * P.row_stride + c);
-                }
-            }
-            uint32_t key[4], pos[4], wcount = 0u;
-            bool in[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const uint32_t c = chunk + warp * 128u + (uint32_t)e * 32u + lane;
-                in[e] = false;
-                key[e] = 0u;
-                if (c < V) {
-                    const uint32_t gid = P.col_offset + c;
-                    float xe = x[e];
-                    if (id_blocked(P, gid)) xe = neg_inf();
-                    if (rc.has_pen) xe = penalize(xe, rc.pen, hash_count(hkeys, hcnt, P.hash_slots, gid));
-                    const float q = temper(xe, rc.T);
-                    in[e] = (__fsub_rn(q, win_qmax) >= WINDOW_EXACT) || (q == win_qmax);  // false for NaN
-                    key[e] = ~okey(q);
-                }
-                const unsigned m = __ballot_sync(FULL_MASK, in[e]);
-                pos[e] = wcount + (uint32_t)__popc(m & ((1u << lane) - 1u));
-                wcount += (uint32_t)__popc(m);
-            }
-            if (lane == 0) wtot[warp] = wcount;
-            cta_sync();
-            uint32_t off = run_base, total = 0u;
-#pragma unroll
-            for (uint32_t w = 0; w < (uint32_t)WARPS; ++w) {
-                const uint32_t t = wtot[w];
-                if (w < warp) off += t;
-                total += t;
-            }
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                if (in[e]) {
-                    __stcg(&sk[off + pos[e]], key[e]);
-                    __stcg(&si[off + pos[e]], chunk + warp * 128u + (uint32_t)e * 32u + lane);
-                }
-            }
-            run_base += total;
-            cta_sync();
-        }
-        n_all = run_base;
+        n_all = build_window_keys(P, b, rc, win_qmax, sk, si, hkeys, hcnt, work);
         if (tid == 0) myvalid = n_all;
     } else
     for (uint32_t c0 = tid; c0 < V; c0 += 4u * THREADS) {  // four columns per thread and round: their loads travel together
@@ -611,91 +720,7 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
     }
     if (myvalid) atomicAdd(&F.nvalid, myvalid);
     cta_sync();
-    // ---- least-significant-digit radix sort, 8 bits per pass, by this CTA alone. Per pass: digit
-    //      histogram, exclusive scan, then a stable scatter in tiles of 1024 keys - warp w takes keys
-    //      [128 w, 128 w + 128) of the tile, 32 consecutive keys per step, so (warp, step, lane) order is
-    //      column order; a key's place is its digit's base + the same-digit keys of earlier warps + those
-    //      earlier in its own warp (`match_any` finds the lanes that share a digit).
-    {
-        uint32_t* hist = work;                  // [256]
-        uint32_t* base = work + 256;            // [256]
-        uint32_t* wtot = work + 512;            // [WARPS]
-        uint32_t* wrun = work + 512 + 32;       // [WARPS][256]
-        for (uint32_t shift = 0; shift < 32u; shift += 8u) {
-            hist[tid] = 0u;
-            cta_sync();
-            for (uint32_t i0 = 0; i0 < n_all; i0 += 4u * THREADS) {
-                uint32_t d[4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const uint32_t i = i0 + (uint32_t)u * THREADS + tid;
-                    d[u] = i < n_all ? ((__ldcg(&sk[i]) >> shift) & 255u) : 256u + lane;  // absent: a digit nobody shares
-                }
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const unsigned peers = __match_any_sync(FULL_MASK, d[u]);
-                    if (d[u] < 256u && (peers & ((1u << lane) - 1u)) == 0u) atomicAdd(&hist[d[u]], (uint32_t)__popc(peers));
-                }
-            }
-            cta_sync();
-            const uint32_t mine = hist[tid];
-            if (cta_sync_or(mine == n_all ? 1 : 0)) continue;  // every key has the same digit: nothing moves
-            uint32_t incl = mine;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const uint32_t y = __shfl_up_sync(FULL_MASK, incl, o);
-                if (lane >= (unsigned)o) incl += y;
-            }
-            if (lane == 31) wtot[warp] = incl;
-            cta_sync();
-            uint32_t pre = 0u;
-            for (uint32_t w = 0; w < warp; ++w) pre += wtot[w];
-            base[tid] = pre + incl - mine;
-            cta_sync();
-            for (uint32_t tile = 0; tile < n_all; tile += 1024u) {
-                for (uint32_t j = lane; j < 256u; j += 32u) wrun[warp * 256u + j] = 0u;
-                uint32_t k[4], id[4], d[4], rank[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const uint32_t i = tile + warp * 128u + (uint32_t)e * 32u + lane;
-                    const bool have = i < n_all;
-                    k[e] = have ? __ldcg(&sk[i]) : 0u;
-                    id[e] = have ? __ldcg(&si[i]) : 0u;
-                    d[e] = have ? ((k[e] >> shift) & 255u) : 256u + lane;
-                }
-                __syncwarp();
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const unsigned peers = __match_any_sync(FULL_MASK, d[e]);
-                    const uint32_t lower = (uint32_t)__popc(peers & ((1u << lane) - 1u));
-                    rank[e] = d[e] < 256u ? wrun[warp * 256u + d[e]] + lower : 0u;
-                    __syncwarp();
-                    if (d[e] < 256u && lower == 0u) wrun[warp * 256u + d[e]] += (uint32_t)__popc(peers);
-                    __syncwarp();
-                }
-                cta_sync();
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    if (d[e] < 256u) {
-                        uint32_t off = base[d[e]] + rank[e];
-                        for (uint32_t w = 0; w < warp; ++w) off += wrun[w * 256u + d[e]];
-                        __stcg(&dk[off], k[e]);
-                        __stcg(&di[off], id[e]);
-                    }
-                }
-                cta_sync();
-                {
-                    uint32_t add = 0u;
-#pragma unroll
-                    for (uint32_t w = 0; w < (uint32_t)WARPS; ++w) add += wrun[w * 256u + tid];
-                    base[tid] += add;
-                }
-                cta_sync();
-            }
-            uint32_t* t = sk; sk = dk; dk = t;
-            t = si; si = di; di = t;
-        }
-    }
+    radix_sort_row(n_all, sk, si, dk, di, work);
     const uint32_t n = min(F.nvalid, rc.k_eff);
     // window attempt: the reference's ordering continues past these n entries with values outside the
     // significance window; what that leaves undecided is handled as in the shared-memory path
@@ -1272,7 +1297,6 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
     }
     cta_sync();
     bool window_filtered = false;  // the candidates already are exactly the window
-    uint32_t flagged_vectors = 0u; // vectors the sweep flagged: an upper bound of the window's size in vectors
     PHASE(7);
     {
         // the sweep fixed the threshold: the penalised ids, the leading / trailing elements and the
@@ -1372,7 +1396,6 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
         }
         cta_sync();
         const uint32_t nq = S.keep;
-        flagged_vectors = nq;
         // everything appended so far plus every element of every flagged vector: if even that fits,
         // the buffer cannot fill up and the final selection sees it all at once
         can_overflow = (uint64_t)S.count + (uint64_t)nq * (uint32_t)VEC > (uint64_t)P.ccap;
@@ -1465,6 +1488,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
     if (wait_failed) atomicOr(&S.error, 4u);
     cta_sync();
 
+    const uint32_t found_total = S.count;  // every value that passed the exact test was counted, whether or not it still fitted
     uint32_t n = min(S.count, P.ccap);
     bool overflow = (S.error & 3u) != 0u;  // window too large, or an append fell off the buffer
     float qmax = temper(okey_to_float(S.max_key), T);
@@ -1476,9 +1500,9 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
     if (P.split == 1u) {
         const int undecided = finish_row(P, b, rc, n, overflow, qmax, S, cand_q, cand_i, scratch, window_filtered);
         if (undecided)
-            // the window alone is tried first unless the sweep flagged most of the row anyway
+            // the window alone is tried first, unless it is most of the row anyway
             full_sort_row(P, b, *reinterpret_cast<FullShared*>(ring), reinterpret_cast<uint32_t*>(ring + 512), hkeys, hcnt,
-                          undecided == 1 && rc.windowed && !(S.error & 4u) && qmax > neg_inf() && flagged_vectors < nvi / 2u, qmax);
+                          undecided == 1 && rc.windowed && !(S.error & 4u) && qmax > neg_inf() && found_total < ncols / 2u, qmax);
         return;
     }
 
