@@ -371,7 +371,7 @@ struct FullShared {
     float sum, total, u, r, thr, mx;
 };
 
-constexpr uint32_t FULL_SLOT_ROUNDS = 1u << 14;
+constexpr uint32_t FULL_SLOT_ROUNDS = 1u << 16;  // seconds of polling: thousands of rows can queue for the slots of a launch
 
 // Claims a free scratch slot. Every holder is a running CTA of this same grid that releases its
 // slot without waiting for anyone, so a bounded poll is enough; 0xffffffff when the bound runs out.

@@ -85,3 +85,12 @@ def test_windows_too_large_for_shared_memory_but_far_from_the_whole_row(sampler,
     _check(sampler, _wl(x, temperature=1.0, top_k=vocab - 5, top_p=0.95))        # a rank cut beyond exact selection
     hist = g.integers(0, vocab, size=(6, 100), dtype=np.uint32)
     _check(sampler, _wl(narrow_bf16(x), temperature=1.1, top_k=0, top_p=0.9, repetition_penalty=1.2, history=hist))
+
+
+def test_more_rows_than_scratch_slots_queue_for_them(sampler):
+    """One scratch slot per SM: with more undecided rows than that in a launch, CTAs wait for a slot
+    (bounded polling) and every row is still resolved."""
+    g = np.random.default_rng(17)
+    B, V = 400, 5001
+    x = g.normal(0.0, 0.1, (B, V)).astype(np.float32)
+    _check(sampler, _wl(x, temperature=1.0, top_k=0, top_p=0.9))
