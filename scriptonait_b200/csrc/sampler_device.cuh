@@ -416,6 +416,20 @@ __device__ __forceinline__ void sort_candidates(uint32_t n, float* cand_q, uint3
 // the significance window (window mode only). Thread 0 owns the sequential
 // chains; everything else is data parallel. Returns through S: token, flags,
 // kept_n and the stage statistics.
+// Eight consecutive values of a 16-byte aligned shared-memory array starting at i0 (a multiple of 8),
+// 0.0f past n: two 16-byte loads for a whole batch.
+__device__ __forceinline__ void load_batch8(const float* vals, uint32_t i0, uint32_t n, float (&e)[8]) {
+    if (i0 + 8u <= n) {
+        const float4 a = *reinterpret_cast<const float4*>(vals + i0);
+        const float4 b = *reinterpret_cast<const float4*>(vals + i0 + 4u);
+        e[0] = a.x; e[1] = a.y; e[2] = a.z; e[3] = a.w;
+        e[4] = b.x; e[5] = b.y; e[6] = b.z; e[7] = b.w;
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) e[j] = (i0 + j < n) ? vals[i0 + j] : 0.0f;
+    }
+}
+
 // The uniform the row's draw consumes: output `draw_index + 1` of its SplitMix64 stream
 // (rng.rs:31-34), or the caller's pinned value.
 __device__ __forceinline__ float row_uniform(const KParams& P, uint32_t b) {
@@ -446,8 +460,7 @@ __device__ __forceinline__ void ordered_tail(const KParams& P, uint32_t b, const
         float s = 0.0f;
         for (uint32_t i0 = 0; i0 < n; i0 += 8u) {
             float e[8];  // the loads of a batch do not depend on the running sum
-#pragma unroll
-            for (int j = 0; j < 8; ++j) e[j] = (i0 + j < n) ? probs[i0 + j] : 0.0f;
+            load_batch8(probs, i0, n, e);
             if (e[0] < 5.9604644775390625e-08f && s >= 1.0f) break;  // this and every later term is a no-op
 #pragma unroll
             for (int j = 0; j < 8; ++j) s = __fadd_rn(s, e[j]);       // adding 0.0f past the end changes nothing
@@ -502,8 +515,7 @@ __device__ __forceinline__ void ordered_tail(const KParams& P, uint32_t b, const
             float cum = 0.0f;
             for (uint32_t i0 = 0; i0 < keep_minp && !reached; i0 += 8u) {
                 float p[8], c[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) p[j] = (i0 + j < keep_minp) ? probs[i0 + j] : 0.0f;
+                load_batch8(probs, i0, keep_minp, p);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     cum = __fadd_rn(cum, p[j]);
@@ -522,8 +534,7 @@ __device__ __forceinline__ void ordered_tail(const KParams& P, uint32_t b, const
         } else {
             for (uint32_t i0 = 0; i0 < keep_minp; i0 += 8u) {
                 float p[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) p[j] = (i0 + j < keep_minp) ? probs[i0 + j] : 0.0f;
+                load_batch8(probs, i0, keep_minp, p);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) total = __fadd_rn(total, p[j]);
             }
@@ -540,8 +551,7 @@ __device__ __forceinline__ void ordered_tail(const KParams& P, uint32_t b, const
         bool found = false;
         for (uint32_t i0 = 0; i0 < keep && !found; i0 += 8u) {  // :413-418, in batches of 8
             float p[8], rr[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) p[j] = (i0 + j < keep) ? probs[i0 + j] : 0.0f;
+            load_batch8(probs, i0, keep, p);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 rr[j] = r;                 // r before entry i0+j is examined
