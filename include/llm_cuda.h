@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define LLM_CUDA_ABI_VERSION 1u
+#define LLM_CUDA_ABI_VERSION 2u
 
 /* status codes */
 #define LLM_CUDA_OK 0
@@ -36,6 +36,12 @@ extern "C" {
 #define LLM_CUDA_ERR_CUDA (-3)          /* a CUDA runtime call failed; see llm_cuda_last_error */
 #define LLM_CUDA_ERR_UNSUPPORTED (-4)   /* e.g. vocabulary sharding with top_k == 0 */
 #define LLM_CUDA_ERR_NO_DEVICE (-5)     /* no CUDA device / wrong architecture */
+#define LLM_CUDA_ERR_TIMEOUT (-6)       /* a bounded wait inside a kernel ran out (llm_cuda_device_status); the rows it hit carry LLM_CUDA_ROW_INVALID */
+
+/* bits of the device status word (llm_cuda_device_status) */
+#define LLM_CUDA_STATUS_COPY_TIMEOUT 1u /* a bulk copy into shared memory did not complete within its wait limit */
+#define LLM_CUDA_STATUS_SLOT_TIMEOUT 2u /* no full-ordering scratch slot came free within the wait limit */
+#define LLM_CUDA_STATUS_CHECK_FAILED 4u /* checked builds only: a computed shared-memory or scratch index left its bounds (the access was skipped) */
 
 /* logits element types */
 #define LLM_CUDA_DTYPE_F32 0u
@@ -88,10 +94,14 @@ typedef struct llm_cuda_sample_args {
     float top_p;
     float min_p;
     float repetition_penalty;
-    uint32_t overlap_previous;  /* nonzero: this launch may start reading its inputs while the previous
-                                 * llm_cuda_sample_batch launch on the same stream is still finishing (its
-                                 * writes still come after that launch has completed). Only for a call whose
-                                 * input arrays are not outputs of that previous call; 0 = strict stream order */
+    uint32_t overlap_previous;  /* nonzero: this launch may begin reading its INPUTS (logits, history, seeds,
+                                 * draw_index, uniforms, every *_rows array, allowed_bits) before the operation
+                                 * that precedes it on the stream has completed; its writes still come after.
+                                 * Set it only when none of those arrays is written by that preceding
+                                 * operation - e.g. consecutive llm_cuda_sample_batch calls over independent
+                                 * batches. Not behind the kernel that produced the logits, and not behind
+                                 * llm_cuda_advance_rows (it writes draw_index and history). 0 = strict stream
+                                 * order. llm_cuda_sample_batch_static ignores the flag (always strict). */
     const float* temperature_rows;        /* device [batch] or NULL */
     const uint32_t* top_k_rows;           /* device [batch] or NULL */
     const float* top_p_rows;              /* device [batch] or NULL */
@@ -130,6 +140,11 @@ typedef struct llm_cuda_sample_args {
     uint32_t split;              /* CTAs per row; 0 = choose */
     uint32_t force_full_sort;    /* testing aid: resolve every row by ordering the whole row */
     void* stream;                /* cudaStream_t */
+
+    float* penalized_out;        /* optional, device [batch, history_stride]: entry (r, j), j < history length of row r, receives
+                                  * the value of logit history[r, j] after the allowed mask and every penalty application and
+                                  * before temperature (generate.rs:333-352); NaN for ids outside this matrix's columns.
+                                  * Written for rows the streaming path samples (not for NaN-parameter or force_full_sort rows) */
 } llm_cuda_sample_args;
 
 /* Reference defaults (generate.rs:82-95). */
@@ -179,7 +194,8 @@ int32_t llm_cuda_sample(llm_cuda_sampler* s, const float* logits, uint32_t vocab
  * - the ordering of generate.rs:364-367 - into
  * cand_values[batch, cand_stride] / cand_ids[batch, cand_stride], with the
  * number written in cand_count[batch]. Requires 0 < top_k <= cand_stride; greedy
- * rows (temperature <= 0) send one candidate. No reference counterpart (the
+ * rows (temperature <= 0) send one candidate. A shard with vocab == 0 (past the end of
+ * a small vocabulary) is legal and writes empty lists. No reference counterpart (the
  * reference is single-device); exact because the global top-k is a subset of
  * the union of per-shard top-k lists and the softmax runs over the kept k only
  * (generate.rs:368-380). */
@@ -198,12 +214,28 @@ int32_t llm_cuda_merge_draw(llm_cuda_sampler* s, const llm_cuda_sample_args* arg
                             const uint32_t* cand_ids, const uint32_t* cand_count, uint32_t n_shards,
                             uint32_t cand_stride);
 
+/* The same two steps with ONE buffer per rank, so that the exchange between them is a single
+ * all-gather: a packed block holds, for `batch` rows, the values [batch, cand_stride] (f32), then the
+ * global ids [batch, cand_stride] (u32), then the counts [batch] (u32) -
+ * llm_cuda_packed_candidates_bytes(batch, cand_stride) bytes (16.5 KB for 32 rows of 64 candidates).
+ * llm_cuda_shard_select_packed writes this GPU's block; llm_cuda_merge_draw_packed reads `n_shards`
+ * such blocks laid end to end, which is exactly what an all-gather of the ranks' blocks produces
+ * (ncclAllGather over NVLink). Same requirements, results and errors as the three-pointer forms.
+ * No reference counterpart (the reference is single-device). */
+size_t llm_cuda_packed_candidates_bytes(uint32_t batch, uint32_t cand_stride);
+int32_t llm_cuda_shard_select_packed(llm_cuda_sampler* s, const llm_cuda_sample_args* args, void* packed_out,
+                                     uint32_t cand_stride);
+int32_t llm_cuda_merge_draw_packed(llm_cuda_sampler* s, const llm_cuda_sample_args* args, const void* packed_all,
+                                   uint32_t n_shards, uint32_t cand_stride);
+
 /* Device-side decode-loop glue (Generator::step / recent_tokens,
  * crates/llm-core/src/generate.rs:157-182; the EOS test of
  * crates/wasm-app/src/inference.rs:326-333): for each row that is not finished,
- * appends tokens[r] to its history ring (history[r, (history_pos[r]) % history_stride]),
- * bumps history_pos / history_len (capped at the window), adds one to
- * draw_index[r] when row_flags[r] has DRAW_CONSUMED, and sets finished[r] when the
+ * appends tokens[r] to its history ring, which holds the last cap = min(window, history_stride)
+ * tokens of the row in history[r, 0 .. cap): while history_len[r] < cap the token goes to slot
+ * history_len[r]; once the ring is full it replaces the oldest entry, at slot history_pos[r] % cap
+ * (history_pos is required whenever history is given: LLM_CUDA_ERR_BAD_ARGUMENT without it).
+ * Adds one to draw_index[r] when row_flags[r] has DRAW_CONSUMED, and sets finished[r] when the
  * token is eos_id (the token is then not appended, as step() returns None).
  * All pointers are device pointers; asynchronous on `stream`. */
 int32_t llm_cuda_advance_rows(llm_cuda_sampler* s, uint32_t batch, const uint32_t* tokens, const uint32_t* row_flags,
@@ -216,6 +248,22 @@ int32_t llm_cuda_advance_rows(llm_cuda_sampler* s, uint32_t batch, const uint32_
  * `allowed_bits` expects: ceil(n/32) words. `bits_out` is a device pointer. */
 int32_t llm_cuda_pack_allowed(llm_cuda_sampler* s, const uint8_t* allowed_host, uint32_t n, uint32_t* bits_out,
                               void* stream);
+
+/* Reads and clears the handle's device status word after `stream` has drained (this call synchronises
+ * the stream). The kernels never wait without a limit: a wait that runs out gives the row up
+ * (LLM_CUDA_ROW_INVALID, token 0) and sets a LLM_CUDA_STATUS_* bit here instead of hanging or guessing.
+ * Returns LLM_CUDA_OK when the word is 0 and LLM_CUDA_ERR_TIMEOUT when a wait ran out; `bits_out` (optional)
+ * receives the word either way. The reference's analogue turns a lost device into an Err
+ * (crates/llm-gpu/src/buffers.rs:58-86, consumed at crates/wasm-app/src/inference.rs:203-214).
+ * llm_cuda_sample_batch_host, llm_cuda_sample_with and llm_cuda_sample check it themselves before they return. */
+int32_t llm_cuda_device_status(llm_cuda_sampler* s, void* stream, uint32_t* bits_out);
+
+/* Testing aid for the status path, safe by construction: `hold` != 0 marks every full-ordering scratch slot
+ * as taken (0 releases them), and `wait_rounds` != 0 shortens the slot wait of later launches to that many
+ * polls of about 4 us (0 restores the default). A launch whose rows need the full ordering then finds no
+ * slot, gives those rows up after the shortened wait and reports LLM_CUDA_STATUS_SLOT_TIMEOUT; nothing
+ * faults, traps or waits without a limit. Synchronises `stream`. No reference counterpart. */
+int32_t llm_cuda_test_hold_full_sort_slots(llm_cuda_sampler* s, uint32_t hold, uint32_t wait_rounds, void* stream);
 
 /* Launch statistics of the last call on this handle (for benchmarks): how many
  * kernels it launched and the CTAs-per-row split it chose. */
@@ -241,7 +289,8 @@ int32_t llm_cuda_last_launch_info(const llm_cuda_sampler* s, uint32_t* kernels_l
  *     (one stream, or events between streams);
  *   - the first call on a device looks up the array's device address and raises the kernels'
  *     shared-memory limit; make that first call before any stream capture begins.
- * Same arguments and results as llm_cuda_sample_batch otherwise (asynchronous on args->stream).
+ * Same arguments and results as llm_cuda_sample_batch otherwise (asynchronous on args->stream;
+ * overlap_previous is ignored: every launch keeps strict stream order).
  * Errors: llm_cuda_static_last_error(). */
 int32_t llm_cuda_sample_batch_static(int32_t device, const llm_cuda_sample_args* args);
 const char* llm_cuda_static_last_error(void);

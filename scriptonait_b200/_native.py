@@ -9,7 +9,7 @@ import os
 
 from . import _build
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 OK = 0
 ERR_BAD_ARGUMENT = -1
@@ -17,6 +17,11 @@ ERR_CAPACITY = -2
 ERR_CUDA = -3
 ERR_UNSUPPORTED = -4
 ERR_NO_DEVICE = -5
+ERR_TIMEOUT = -6
+
+STATUS_COPY_TIMEOUT = 1
+STATUS_SLOT_TIMEOUT = 2
+STATUS_CHECK_FAILED = 4
 
 DTYPE_F32 = 0
 DTYPE_BF16 = 1
@@ -37,6 +42,8 @@ EXPORTS = [
     "llm_cuda_last_error", "llm_cuda_sample_batch", "llm_cuda_sample_batch_host", "llm_cuda_sample_with",
     "llm_cuda_sample", "llm_cuda_shard_select", "llm_cuda_merge_draw", "llm_cuda_advance_rows",
     "llm_cuda_pack_allowed", "llm_cuda_last_launch_info", "llm_cuda_sample_batch_static", "llm_cuda_static_last_error",
+    "llm_cuda_device_status", "llm_cuda_test_hold_full_sort_slots", "llm_cuda_packed_candidates_bytes",
+    "llm_cuda_shard_select_packed", "llm_cuda_merge_draw_packed",
 ]
 STATIC_MAX_BATCH, STATIC_MAX_TOP_K, STATIC_MAX_HISTORY = 64, 256, 512
 
@@ -66,6 +73,7 @@ class SampleArgs(C.Structure):
         ("kept_capacity", C.c_uint32), ("reserved1", C.c_uint32), ("row_stats", C.c_void_p),
         ("column_offset", C.c_uint32), ("vocab_global", C.c_uint32),
         ("split", C.c_uint32), ("force_full_sort", C.c_uint32), ("stream", C.c_void_p),
+        ("penalized_out", C.c_void_p),
     ]
 
 
@@ -120,6 +128,16 @@ def load() -> C.CDLL:
     L.llm_cuda_pack_allowed.argtypes = [vp, vp, u32, vp, vp]
     L.llm_cuda_last_launch_info.restype = i32
     L.llm_cuda_last_launch_info.argtypes = [vp, C.POINTER(u32), C.POINTER(u32)]
+    L.llm_cuda_packed_candidates_bytes.restype = C.c_size_t
+    L.llm_cuda_packed_candidates_bytes.argtypes = [u32, u32]
+    L.llm_cuda_shard_select_packed.restype = i32
+    L.llm_cuda_shard_select_packed.argtypes = [vp, C.POINTER(SampleArgs), vp, u32]
+    L.llm_cuda_merge_draw_packed.restype = i32
+    L.llm_cuda_merge_draw_packed.argtypes = [vp, C.POINTER(SampleArgs), vp, u32, u32]
+    L.llm_cuda_device_status.restype = i32
+    L.llm_cuda_device_status.argtypes = [vp, vp, C.POINTER(u32)]
+    L.llm_cuda_test_hold_full_sort_slots.restype = i32
+    L.llm_cuda_test_hold_full_sort_slots.argtypes = [vp, u32, u32, vp]
     L.llm_cuda_sample_batch_static.restype = i32
     L.llm_cuda_sample_batch_static.argtypes = [i32, C.POINTER(SampleArgs)]
     L.llm_cuda_static_last_error.restype = C.c_char_p

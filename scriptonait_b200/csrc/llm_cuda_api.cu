@@ -21,6 +21,7 @@ namespace {
 constexpr uint32_t kMaxKcap = 2048;           // must match MAX_KCAP
 constexpr uint64_t kScratchEntries = 1u << 22;  // candidate entries shared by the CTAs of split rows (32 MiB)
 constexpr uint64_t kGamma = 0x9E3779B97F4A7C15ull;
+constexpr uint32_t kSlotRounds = 1u << 16;  // a quarter of a second of polling: thousands of rows can queue for the slots of a launch
 
 char g_create_error[512] = "";
 
@@ -31,6 +32,39 @@ uint32_t pow2_ceil_u32(uint32_t x) {
 }
 
 }  // namespace
+
+namespace llmc {
+
+int validate_sample_args(const llm_cuda_sample_args* a, bool needs_logits, char* err, size_t err_len) {
+    auto bad = [&](const char* fmt, unsigned long long x = 0, unsigned long long y = 0) {
+        snprintf(err, err_len, fmt, x, y);
+        return LLM_CUDA_ERR_BAD_ARGUMENT;
+    };
+    if (!a) return bad("args is NULL");
+    if (a->struct_size != sizeof(llm_cuda_sample_args))
+        return bad("struct_size %llu, expected %llu", a->struct_size, sizeof(llm_cuda_sample_args));
+    if (a->logits_dtype != LLM_CUDA_DTYPE_F32 && a->logits_dtype != LLM_CUDA_DTYPE_BF16)
+        return bad("unknown logits_dtype %llu", a->logits_dtype);
+    if (needs_logits) {
+        if (a->batch && !a->logits) return bad("logits is NULL");
+        if (a->vocab == 0) return bad("vocab is 0");
+        if (a->row_stride_elems != 0 && a->row_stride_elems < a->vocab)
+            return bad("row_stride_elems %llu < vocab %llu", a->row_stride_elems, a->vocab);
+        // rows are read as 16-byte vectors from the first 16-byte boundary on, element by element before
+        // it: that only works out when the matrix starts on an element boundary
+        const uintptr_t esz = a->logits_dtype == LLM_CUDA_DTYPE_BF16 ? 2 : 4;
+        if (reinterpret_cast<uintptr_t>(a->logits) % esz) return bad("logits pointer not element aligned");
+        if (a->history && a->history_len > a->history_stride)
+            return bad("history_len %llu > history_stride %llu", a->history_len, a->history_stride);
+    }
+    if (a->temperature_rows == nullptr && a->temperature != a->temperature) return bad("temperature is NaN");
+    if (a->repetition_penalty_rows == nullptr && a->repetition_penalty != a->repetition_penalty)
+        return bad("repetition_penalty is NaN");
+    if ((a->kept_ids || a->kept_probs) && a->kept_capacity == 0) return bad("kept_ids/kept_probs given with kept_capacity 0");
+    return LLM_CUDA_OK;
+}
+
+}  // namespace llmc
 
 struct llm_cuda_sampler {
     int device = 0;
@@ -48,8 +82,11 @@ struct llm_cuda_sampler {
     uint64_t* full_keys = nullptr;
     float* full_vals = nullptr;
     uint32_t vpad = 0, nslots = 0;
-    uint32_t* device_errors = nullptr;  // bit 0: a bulk copy timed out in some launch
-    unsigned long long* phase_ns = nullptr;  // development aid: per-CTA phase timestamps, set by llm_cuda_debug_phase_buffer
+    uint32_t* device_errors = nullptr;  // LLM_CUDA_STATUS_* bits set by kernels whose bounded waits ran out
+    uint32_t slot_rounds = kSlotRounds;
+#ifdef LLMC_DEV
+    unsigned long long* phase_ns = nullptr;  // development builds only: per-CTA phase timestamps
+#endif
     // staging for the host-buffer entry points (grown on demand)
     unsigned char* arena = nullptr;
     size_t arena_bytes = 0;
@@ -89,34 +126,18 @@ void free_all(llm_cuda_sampler* s) {
 // Shared validation + parameter block for the three device-buffer entry points.
 int32_t fill_params(llm_cuda_sampler* s, const llm_cuda_sample_args* a, bool needs_logits, KParams* P) {
     if (!s) return fail(nullptr, LLM_CUDA_ERR_BAD_ARGUMENT, "sampler handle is NULL");
-    if (!a) return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "args is NULL");
-    if (a->struct_size != sizeof(llm_cuda_sample_args))
-        return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "struct_size %u, expected %zu", a->struct_size, sizeof(llm_cuda_sample_args));
-    if (a->logits_dtype != LLM_CUDA_DTYPE_F32 && a->logits_dtype != LLM_CUDA_DTYPE_BF16)
-        return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "unknown logits_dtype %u", a->logits_dtype);
+    {
+        const int32_t rc = validate_sample_args(a, needs_logits, s->err, sizeof(s->err));
+        if (rc != LLM_CUDA_OK) return rc;
+    }
     if (a->batch > s->max_batch) return fail(s, LLM_CUDA_ERR_CAPACITY, "batch %u > max_batch %u", a->batch, s->max_batch);
     if (needs_logits) {
-        if (a->batch && !a->logits) return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "logits is NULL");
-        if (a->vocab == 0) return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "vocab is 0");
         if (a->vocab > s->max_vocab) return fail(s, LLM_CUDA_ERR_CAPACITY, "vocab %u > max_vocab %u", a->vocab, s->max_vocab);
-        if (a->row_stride_elems != 0 && a->row_stride_elems < a->vocab)
-            return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "row_stride_elems %llu < vocab %u", (unsigned long long)a->row_stride_elems, a->vocab);
-        const uintptr_t esz = a->logits_dtype == LLM_CUDA_DTYPE_BF16 ? 2 : 4;
-        if (reinterpret_cast<uintptr_t>(a->logits) % esz) return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "logits pointer not element aligned");
         if (a->history) {
-            if (a->history_len > a->history_stride)
-                return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "history_len %u > history_stride %u", a->history_len, a->history_stride);
             const uint32_t hmax = a->history_len_rows ? a->history_stride : a->history_len;
             if (hmax > s->max_history) return fail(s, LLM_CUDA_ERR_CAPACITY, "history %u > max_history %u", hmax, s->max_history);
         }
     }
-    if (a->batch && !a->tokens && needs_logits == false) return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "tokens is NULL");
-    if (a->temperature_rows == nullptr && a->temperature != a->temperature)
-        return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "temperature is NaN");
-    if (a->repetition_penalty_rows == nullptr && a->repetition_penalty != a->repetition_penalty)
-        return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "repetition_penalty is NaN");
-    if ((a->kept_ids || a->kept_probs) && a->kept_capacity == 0)
-        return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "kept_ids/kept_probs given with kept_capacity 0");
 
     memset(P, 0, sizeof(*P));
     P->logits = a->logits;
@@ -156,7 +177,11 @@ int32_t fill_params(llm_cuda_sampler* s, const llm_cuda_sample_args* a, bool nee
     P->vocab_global = a->vocab_global ? a->vocab_global : a->vocab;
     P->force_full = a->force_full_sort;
     P->device_errors = s->device_errors;
+    P->full_slot_rounds = s->slot_rounds;
+    P->penalized_out = a->penalized_out;
+#ifdef LLMC_DEV
     P->phase_ns = s->phase_ns;
+#endif
     return LLM_CUDA_OK;
 }
 
@@ -179,18 +204,7 @@ int32_t run_select(llm_cuda_sampler* s, const llm_cuda_sample_args* a, KParams& 
     if (max_lists > s->sc_lists) max_lists = s->sc_lists;
     if (plan_launch(s->dev, P, k_known, k_hint, s->max_top_k, s->max_history, a->split, (uint32_t)max_lists, &plan) != 0)
         return fail(s, LLM_CUDA_ERR_CAPACITY, "shared-memory layout does not fit (vocab %u, history %u)", a->vocab, s->max_history);
-    P.split = plan.split;
-    P.shard_cols = plan.shard_cols;
-    P.kcap = plan.kcap;
-    P.ccap = plan.ccap;
-    P.limit = plan.limit;
-    P.hash_slots = plan.hash_slots;
-    P.bitmap_words = plan.bitmap_words;
-    P.lane_top_words = plan.lane_top_words;
-    P.cand_off = plan.cand_off;
-    P.scratch_off = plan.scratch_off;
-    P.tables_off = plan.tables_off;
-    P.vlist_cap = plan.vlist_cap;
+    apply_plan(plan, &P);
     P.sc_q = s->sc_q;
     P.sc_i = s->sc_i;
     P.sc_cnt = s->sc_cnt;
@@ -198,6 +212,8 @@ int32_t run_select(llm_cuda_sampler* s, const llm_cuda_sample_args* a, KParams& 
     P.sc_ticket = s->sc_ticket;
     P.sc_stride = plan.limit;
     P.sc_rows = P.batch;
+    P.sc_shard_words = P.sc_rows * P.sc_stride;
+    P.sc_cnt_shard = P.sc_rows;
     cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
     s->last_kernels = 0;
     s->last_split = plan.split;
@@ -312,6 +328,35 @@ int32_t llm_cuda_sampler_destroy(llm_cuda_sampler* s) {
     return LLM_CUDA_OK;
 }
 
+int32_t llm_cuda_device_status(llm_cuda_sampler* s, void* stream, uint32_t* bits_out) {
+    if (!s) return fail(nullptr, LLM_CUDA_ERR_BAD_ARGUMENT, "sampler handle is NULL");
+    CUDA_TRY(s, cudaSetDevice(s->device));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    uint32_t bits = 0u;
+    CUDA_TRY(s, cudaMemcpyAsync(&bits, s->device_errors, 4u, cudaMemcpyDeviceToHost, st));
+    CUDA_TRY(s, cudaStreamSynchronize(st));
+    if (bits) CUDA_TRY(s, cudaMemsetAsync(s->device_errors, 0, 4u, st));
+    if (bits_out) *bits_out = bits;
+    if (bits)
+        return fail(s, LLM_CUDA_ERR_TIMEOUT, "device status 0x%x:%s%s%s", bits,
+                    (bits & LLM_CUDA_STATUS_COPY_TIMEOUT) ? " a bulk copy did not complete within its wait limit;" : "",
+                    (bits & LLM_CUDA_STATUS_SLOT_TIMEOUT) ? " no full-ordering slot came free within the wait limit;" : "",
+                    (bits & LLM_CUDA_STATUS_CHECK_FAILED) ? " an index check failed;" : "");
+    return LLM_CUDA_OK;
+}
+
+int32_t llm_cuda_test_hold_full_sort_slots(llm_cuda_sampler* s, uint32_t hold, uint32_t wait_rounds, void* stream) {
+    if (!s) return fail(nullptr, LLM_CUDA_ERR_BAD_ARGUMENT, "sampler handle is NULL");
+    CUDA_TRY(s, cudaSetDevice(s->device));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    CUDA_TRY(s, cudaStreamSynchronize(st));  // no launch is using the slots
+    // every byte 1 makes a word nonzero = taken; only 0 counts as free
+    CUDA_TRY(s, cudaMemsetAsync(s->full_slots, hold ? 1 : 0, (size_t)s->nslots * 4u, st));
+    CUDA_TRY(s, cudaStreamSynchronize(st));
+    s->slot_rounds = wait_rounds ? wait_rounds : kSlotRounds;
+    return LLM_CUDA_OK;
+}
+
 int32_t llm_cuda_last_launch_info(const llm_cuda_sampler* s, uint32_t* kernels_launched, uint32_t* split_used) {
     if (!s) return LLM_CUDA_ERR_BAD_ARGUMENT;
     if (kernels_launched) *kernels_launched = s->last_kernels;
@@ -319,12 +364,15 @@ int32_t llm_cuda_last_launch_info(const llm_cuda_sampler* s, uint32_t* kernels_l
     return LLM_CUDA_OK;
 }
 
-// Development aid (not part of the public header): per-CTA phase timestamps of the streaming kernel.
+#ifdef LLMC_DEV
+// Development builds only (never in the product library): phase timestamps and launch-plan overrides.
 int32_t llm_cuda_debug_phase_buffer(llm_cuda_sampler* s, unsigned long long* device_buffer) {
     if (!s) return LLM_CUDA_ERR_BAD_ARGUMENT;
     s->phase_ns = device_buffer;
     return LLM_CUDA_OK;
 }
+void llm_cuda_dev_set(int32_t key, int32_t value) { llmc::dev_override(key, value); }
+#endif
 
 int32_t llm_cuda_sample_batch(llm_cuda_sampler* s, const llm_cuda_sample_args* a) {
     KParams P;
@@ -339,6 +387,16 @@ int32_t llm_cuda_sample_batch(llm_cuda_sampler* s, const llm_cuda_sample_args* a
 
 int32_t llm_cuda_shard_select(llm_cuda_sampler* s, const llm_cuda_sample_args* a, float* cand_values, uint32_t* cand_ids,
                               uint32_t* cand_count, uint32_t cand_stride) {
+    if (s && a && a->struct_size == sizeof(llm_cuda_sample_args) && a->vocab == 0 && cand_count) {
+        // a shard past the end of a small vocabulary holds no columns: it contributes empty lists, so that
+        // every rank still reaches the exchange
+        if (a->batch > s->max_batch) return fail(s, LLM_CUDA_ERR_CAPACITY, "batch %u > max_batch %u", a->batch, s->max_batch);
+        CUDA_TRY(s, cudaSetDevice(s->device));
+        if (a->batch)
+            CUDA_TRY(s, cudaMemsetAsync(cand_count, 0, (size_t)a->batch * 4u, static_cast<cudaStream_t>(a->stream)));
+        s->last_kernels = 0;
+        return LLM_CUDA_OK;
+    }
     KParams P;
     int32_t rc = fill_params(s, a, true, &P);
     if (rc != LLM_CUDA_OK) return rc;
@@ -361,8 +419,12 @@ int32_t llm_cuda_shard_select(llm_cuda_sampler* s, const llm_cuda_sample_args* a
     return run_select(s, a, P, true);
 }
 
-int32_t llm_cuda_merge_draw(llm_cuda_sampler* s, const llm_cuda_sample_args* a, const float* cand_values,
-                            const uint32_t* cand_ids, const uint32_t* cand_count, uint32_t n_shards, uint32_t cand_stride) {
+namespace {
+
+// The merge step over lists laid out as the two public forms describe.
+int32_t run_merge(llm_cuda_sampler* s, const llm_cuda_sample_args* a, const float* cand_values, const uint32_t* cand_ids,
+                  const uint32_t* cand_count, uint32_t n_shards, uint32_t cand_stride, uint64_t shard_words,
+                  uint64_t cnt_shard) {
     KParams P;
     int32_t rc = fill_params(s, a, false, &P);
     if (rc != LLM_CUDA_OK) return rc;
@@ -373,6 +435,8 @@ int32_t llm_cuda_merge_draw(llm_cuda_sampler* s, const llm_cuda_sample_args* a, 
     if (!scalar_greedy(a) && (a->top_k == 0 || a->top_k > kMaxKcap))
         return fail(s, LLM_CUDA_ERR_UNSUPPORTED, "vocabulary sharding needs 0 < top_k <= %u", kMaxKcap);
     if (P.vocab_global == 0) return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "vocab_global (or vocab) must be set");
+    if (shard_words > 0xffffffffull || cnt_shard > 0xffffffffull)
+        return fail(s, LLM_CUDA_ERR_CAPACITY, "candidate lists of one shard exceed 2^32 words");
     const uint32_t k = scalar_greedy(a) ? 1u : a->top_k;
     const uint32_t k_eff = k >= P.vocab_global ? P.vocab_global : k;
     LaunchPlan plan{};
@@ -391,6 +455,8 @@ int32_t llm_cuda_merge_draw(llm_cuda_sampler* s, const llm_cuda_sample_args* a, 
     P.sc_maxkey = nullptr;
     P.sc_stride = cand_stride;
     P.sc_rows = a->batch;
+    P.sc_shard_words = (uint32_t)shard_words;
+    P.sc_cnt_shard = (uint32_t)cnt_shard;
     P.force_full = 0;
     s->last_kernels = 0;
     s->last_split = n_shards;
@@ -401,12 +467,47 @@ int32_t llm_cuda_merge_draw(llm_cuda_sampler* s, const llm_cuda_sample_args* a, 
     return LLM_CUDA_OK;
 }
 
+}  // namespace
+
+int32_t llm_cuda_merge_draw(llm_cuda_sampler* s, const llm_cuda_sample_args* a, const float* cand_values,
+                            const uint32_t* cand_ids, const uint32_t* cand_count, uint32_t n_shards, uint32_t cand_stride) {
+    const uint64_t B = a ? a->batch : 0u;
+    return run_merge(s, a, cand_values, cand_ids, cand_count, n_shards, cand_stride, B * cand_stride, B);
+}
+
+size_t llm_cuda_packed_candidates_bytes(uint32_t batch, uint32_t cand_stride) {
+    return ((size_t)2u * batch * cand_stride + batch) * 4u;
+}
+
+int32_t llm_cuda_shard_select_packed(llm_cuda_sampler* s, const llm_cuda_sample_args* a, void* packed_out, uint32_t cand_stride) {
+    if (!s) return fail(nullptr, LLM_CUDA_ERR_BAD_ARGUMENT, "sampler handle is NULL");
+    if (!a || !packed_out) return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "args or packed_out is NULL");
+    float* values = static_cast<float*>(packed_out);
+    uint32_t* ids = reinterpret_cast<uint32_t*>(values) + (size_t)a->batch * cand_stride;
+    uint32_t* counts = ids + (size_t)a->batch * cand_stride;
+    return llm_cuda_shard_select(s, a, values, ids, counts, cand_stride);
+}
+
+int32_t llm_cuda_merge_draw_packed(llm_cuda_sampler* s, const llm_cuda_sample_args* a, const void* packed_all, uint32_t n_shards,
+                                   uint32_t cand_stride) {
+    if (!s) return fail(nullptr, LLM_CUDA_ERR_BAD_ARGUMENT, "sampler handle is NULL");
+    if (!a || !packed_all) return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "args or packed_all is NULL");
+    const uint64_t B = a->batch;
+    const uint64_t block = 2u * B * cand_stride + B;  // words per shard
+    const float* values = static_cast<const float*>(packed_all);
+    const uint32_t* ids = reinterpret_cast<const uint32_t*>(values) + B * cand_stride;
+    const uint32_t* counts = ids + B * cand_stride;
+    return run_merge(s, a, values, ids, counts, n_shards, cand_stride, block, block);
+}
+
 int32_t llm_cuda_advance_rows(llm_cuda_sampler* s, uint32_t batch, const uint32_t* tokens, const uint32_t* row_flags,
                               uint32_t* history, uint32_t history_stride, uint32_t window, uint32_t* history_len,
                               uint32_t* history_pos, uint64_t* draw_index, uint8_t* finished, uint32_t eos_id, void* stream) {
     if (!s) return fail(nullptr, LLM_CUDA_ERR_BAD_ARGUMENT, "sampler handle is NULL");
     if (batch && !tokens) return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "tokens is NULL");
     if (history && !history_len) return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "history given without history_len");
+    // without a write position a full ring could only ever replace one slot and the window would go stale
+    if (history && !history_pos) return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "history given without history_pos");
     CUDA_TRY(s, cudaSetDevice(s->device));
     CUDA_TRY(s, launch_advance_rows(batch, tokens, row_flags, history, history_stride, window, history_len, history_pos,
                                     draw_index, finished, eos_id, static_cast<cudaStream_t>(stream)));
@@ -474,6 +575,7 @@ int32_t llm_cuda_sample_batch_host(llm_cuda_sampler* s, const llm_cuda_sample_ar
         d.kept_ids = h->kept_ids ? (uint32_t*)c.take(kept_elems * 4) : nullptr;
         d.kept_probs = h->kept_probs ? (float*)c.take(kept_elems * 4) : nullptr;
         d.row_stats = h->row_stats ? (float*)c.take(B * LLM_CUDA_ROW_STATS * 4) : nullptr;
+        d.penalized_out = (h->penalized_out && h->history) ? (float*)c.take(hist_bytes) : nullptr;
         if (pass == 0 && c.off > s->arena_bytes) {
             CUDA_TRY(s, cudaStreamSynchronize(st));
             cudaFree(s->arena);
@@ -502,7 +604,7 @@ int32_t llm_cuda_sample_batch_host(llm_cuda_sampler* s, const llm_cuda_sample_ar
     int32_t rc = llm_cuda_sample_batch(s, &d);
     if (rc != LLM_CUDA_OK) return rc;
     auto down = [&](void* dst, const void* src, size_t bytes) -> cudaError_t {
-        if (!dst || bytes == 0) return cudaSuccess;
+        if (!dst || !src || bytes == 0) return cudaSuccess;
         return cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, st);
     };
     CUDA_TRY(s, down(h->tokens, d.tokens, B * 4));
@@ -511,8 +613,9 @@ int32_t llm_cuda_sample_batch_host(llm_cuda_sampler* s, const llm_cuda_sample_ar
     CUDA_TRY(s, down(h->kept_ids, d.kept_ids, kept_elems * 4));
     CUDA_TRY(s, down(h->kept_probs, d.kept_probs, kept_elems * 4));
     CUDA_TRY(s, down(h->row_stats, d.row_stats, B * LLM_CUDA_ROW_STATS * 4));
-    CUDA_TRY(s, cudaStreamSynchronize(st));
-    return LLM_CUDA_OK;
+    CUDA_TRY(s, down(h->penalized_out, d.penalized_out, hist_bytes));
+    // synchronises the stream; a bounded wait that ran out inside the kernel becomes LLM_CUDA_ERR_TIMEOUT
+    return llm_cuda_device_status(s, h->stream, nullptr);
 }
 
 int32_t llm_cuda_sample_with(llm_cuda_sampler* s, const float* logits, uint32_t vocab, const llm_cuda_sampling_config* cfg,

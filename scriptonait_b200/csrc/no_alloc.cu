@@ -40,7 +40,7 @@ constexpr size_t kOffIds = kOffValues + (size_t)kMaxLists * kListLen * 4u;
 constexpr size_t kOffCounts = kOffIds + (size_t)kMaxLists * kListLen * 4u;
 constexpr size_t kOffMaxima = kOffCounts + (size_t)kMaxLists * 4u;
 constexpr size_t kOffTickets = kOffMaxima + (size_t)kMaxLists * 4u;
-constexpr size_t kScratchBytes = kOffTickets + (size_t)kMaxBatch * 4u;  // 1 051 136 bytes
+constexpr size_t kScratchBytes = kOffTickets + (size_t)kMaxBatch * 4u;  // 1 050 880 bytes
 
 // The scratch itself. In host code this name is only a stand-in for the symbol - it is not
 // a device address and must never be handed to a kernel; device_scratch() below asks the
@@ -93,20 +93,18 @@ extern "C" {
 const char* llm_cuda_static_last_error(void) { return g_static_error; }
 
 int32_t llm_cuda_sample_batch_static(int32_t device, const llm_cuda_sample_args* a) {
-    if (!a) return fail(LLM_CUDA_ERR_BAD_ARGUMENT, "args is NULL%s");
-    if (a->struct_size != sizeof(llm_cuda_sample_args)) return fail(LLM_CUDA_ERR_BAD_ARGUMENT, "struct_size mismatch%s");
-    if (a->logits_dtype != LLM_CUDA_DTYPE_F32 && a->logits_dtype != LLM_CUDA_DTYPE_BF16)
-        return fail(LLM_CUDA_ERR_BAD_ARGUMENT, "unknown logits_dtype%s");
+    {   // the checks the handle-based entry point makes too: pointers and their alignment, strides, NaN scalars
+        const int32_t rc = validate_sample_args(a, true, g_static_error, sizeof(g_static_error));
+        if (rc != LLM_CUDA_OK) return rc;
+    }
     if (a->batch == 0) return LLM_CUDA_OK;
-    if (!a->logits || !a->tokens || a->vocab == 0) return fail(LLM_CUDA_ERR_BAD_ARGUMENT, "logits, tokens or vocab missing%s");
-    if (a->row_stride_elems != 0 && a->row_stride_elems < a->vocab) return fail(LLM_CUDA_ERR_BAD_ARGUMENT, "row_stride_elems < vocab%s");
+    if (!a->tokens) return fail(LLM_CUDA_ERR_BAD_ARGUMENT, "tokens is NULL%s");
     // ---- the limits of the fixed scratch, stated in the header
     if (a->batch > kMaxBatch)
         return fail(LLM_CUDA_ERR_CAPACITY, "batch %s%llu exceeds the static limit %llu", "", a->batch, kMaxBatch);
     if (a->top_k_rows || a->temperature_rows)
         return fail(LLM_CUDA_ERR_UNSUPPORTED, "per-row top_k / temperature arrays are not available without a handle%s");
     const bool greedy = a->temperature <= 0.0f;
-    if (a->temperature != a->temperature) return fail(LLM_CUDA_ERR_BAD_ARGUMENT, "temperature is NaN%s");
     if (!greedy && (a->top_k == 0 || a->top_k > kMaxTopK))
         return fail(LLM_CUDA_ERR_CAPACITY, "top_k %s%llu outside 1..%llu: rows that need the window or the full-sort stage need a handle", "",
                     a->top_k, kMaxTopK);
@@ -115,11 +113,9 @@ int32_t llm_cuda_sample_batch_static(int32_t device, const llm_cuda_sample_args*
         return fail(LLM_CUDA_ERR_UNSUPPORTED, "full-sort and vocabulary sharding need a handle%s");
     uint32_t hist = 0;
     if (a->history) {
-        if (a->history_len > a->history_stride) return fail(LLM_CUDA_ERR_BAD_ARGUMENT, "history_len > history_stride%s");
         hist = a->history_len_rows ? a->history_stride : a->history_len;
         if (hist > kMaxHistory) return fail(LLM_CUDA_ERR_CAPACITY, "history %s%llu exceeds the static limit %llu", "", hist, kMaxHistory);
     }
-    if ((a->kept_ids || a->kept_probs) && a->kept_capacity == 0) return fail(LLM_CUDA_ERR_BAD_ARGUMENT, "kept_capacity is 0%s");
 
     PerDevice* d = nullptr;
     int32_t rc = device_scratch(device, &d);
@@ -171,18 +167,8 @@ int32_t llm_cuda_sample_batch_static(int32_t device, const llm_cuda_sample_args*
     // as long as it leaves room for the kept set
     const uint32_t limit = plan.limit < kListLen ? plan.limit : kListLen;
     if (limit < 2u * plan.kcap) return fail(LLM_CUDA_ERR_CAPACITY, "candidate lists exceed the static scratch%s");
-    P.split = plan.split;
-    P.shard_cols = plan.shard_cols;
-    P.kcap = plan.kcap;
-    P.ccap = plan.ccap;
+    apply_plan(plan, &P);
     P.limit = limit;
-    P.hash_slots = plan.hash_slots;
-    P.bitmap_words = plan.bitmap_words;
-    P.lane_top_words = plan.lane_top_words;
-    P.cand_off = plan.cand_off;
-    P.scratch_off = plan.scratch_off;
-    P.tables_off = plan.tables_off;
-    P.vlist_cap = plan.vlist_cap;
     P.sc_q = reinterpret_cast<float*>(d->scratch + kOffValues);
     P.sc_i = reinterpret_cast<uint32_t*>(d->scratch + kOffIds);
     P.sc_cnt = reinterpret_cast<uint32_t*>(d->scratch + kOffCounts);
@@ -190,6 +176,8 @@ int32_t llm_cuda_sample_batch_static(int32_t device, const llm_cuda_sample_args*
     P.sc_ticket = reinterpret_cast<uint32_t*>(d->scratch + kOffTickets);
     P.sc_stride = limit;
     P.sc_rows = P.batch;
+    P.sc_shard_words = P.sc_rows * P.sc_stride;
+    P.sc_cnt_shard = P.sc_rows;
     cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
     // the tickets are the one part of the shared array that must start at zero
     e = cudaMemsetAsync(P.sc_ticket, 0, (size_t)kMaxBatch * 4u, stream);

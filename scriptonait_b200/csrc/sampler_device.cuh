@@ -15,6 +15,24 @@
 
 namespace llmc {
 
+// Development builds only (-DLLMC_DEV; the product build never sets it): per-CTA phase marks, 16 per
+// CTA: slots 0 and 11 hold the global timer (the CTA's start and end), the others the SM's cycle counter.
+#ifdef LLMC_DEV
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define PHASE(slot)                                                                                              \
+    do {                                                                                                         \
+        if (P.phase_ns && threadIdx.x == 0)                                                                      \
+            P.phase_ns[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 16u + (slot)] =                            \
+                ((slot) == 0 || (slot) == 11) ? global_ns() : (unsigned long long)clock64();                                       \
+    } while (0)
+#else
+#define PHASE(slot) do { } while (0)
+#endif
+
 constexpr int THREADS = 256;             // threads per CTA of the streaming kernel
 constexpr int WARPS = THREADS / 32;
 constexpr uint32_t STAGE_BYTES = 12288;  // one ring stage = one tile: the logits consumed between two capacity checks
@@ -190,6 +208,7 @@ struct Shared {
     uint32_t keep;
     uint32_t error;        // internal consistency failures (buffer overrun guard)
     uint32_t last;         // this CTA merges the row
+    uint32_t sortmax;      // ordered key of the largest candidate, found while the small sort stages its keys
     uint32_t wkth[WARPS];   // per-warp lower bounds for the first tile's threshold
     float u_pre;              // the row's uniform, fetched early by kernels that can (u_pre_valid != 0)
     uint32_t u_pre_valid;
@@ -356,31 +375,57 @@ __device__ __forceinline__ uint32_t keep_top_k(uint32_t n, uint32_t k, Shared& S
         n, [=](float q, uint32_t id) { return (composite(q, id) >> shift) >= thr; }, S, cand_q, cand_i);
 }
 
-// Sorts cand[0..n) into the reference ordering. Up to THREADS entries: every
-// thread ranks its entry against all others (composite keys staged in `keys64`,
-// which must hold n 64-bit words) and scatters - two barriers. Larger sets: bitonic
-// sort; slots [n, m) (m the next power of two) are filled with entries that sort last.
-__device__ __forceinline__ void sort_candidates(uint32_t n, float* cand_q, uint32_t* cand_i, uint64_t* keys64) {
-    if (n <= (uint32_t)THREADS) {
-        float q = 0.f;
-        uint32_t id = 0u;
-        uint64_t mine = 0ull;
-        if (threadIdx.x < n) {
-            q = cand_q[threadIdx.x];
-            id = cand_i[threadIdx.x];
-            mine = composite(q, id);
-            keys64[threadIdx.x] = mine;
-        }
-        cta_sync();
-        if (threadIdx.x < n) {
-            uint32_t rank = 0u;
-            for (uint32_t j = 0; j < n; ++j) rank += (keys64[j] > mine) ? 1u : 0u;  // keys are distinct
-            cand_q[rank] = q;
-            cand_i[rank] = id;
-        }
-        cta_sync();
-        return;
+// Sorts cand[0..n), n <= THREADS, into the reference ordering by ranking: an entry's place is the
+// number of entries that come before it. With n <= 128 the comparisons of one entry are split over
+// 2, 4 or 8 threads (partial ranks meet in `rank_acc`, THREADS words of scratch). With `want_exp`, probs[rank] = exp(q - max) is computed alongside (the maximum
+// is found while the keys are staged; S.sortmax must be 0 on entry), which is generate.rs:372-373
+// for the sorted set: the double-precision exp runs while the ranks are counted.
+__device__ __forceinline__ void sort_small(uint32_t n, Shared& S, float* cand_q, uint32_t* cand_i, uint64_t* keys64,
+                                           uint32_t* rank_acc, float* probs, bool want_exp) {
+    const uint32_t tid = threadIdx.x;
+    const unsigned lane = tid & 31u;
+    float q = 0.f;
+    uint32_t id = 0u;
+    const bool have = tid < n;
+    if (have) {
+        q = cand_q[tid];
+        id = cand_i[tid];
+        keys64[tid] = composite(q, id);
     }
+    uint32_t parts = 1u;
+    while (parts < 8u && n * 2u * parts <= (uint32_t)THREADS) parts <<= 1;
+    if (parts > 1u) rank_acc[tid] = 0u;
+    if (want_exp) {
+        const uint32_t wk = __reduce_max_sync(FULL_MASK, have ? okey(q) : 0u);
+        if (lane == 0 && wk) atomicMax(&S.sortmax, wk);
+    }
+    cta_sync();
+    const uint32_t npad = (uint32_t)THREADS / parts;
+    const uint32_t elem = tid & (npad - 1u), part = tid / npad;
+    uint32_t rank = 0u;
+    if (elem < n) {
+        const uint64_t mine = keys64[elem];
+        const uint32_t chunk = (n + parts - 1u) / parts;
+        const uint32_t j0 = part * chunk, j1 = min(n, j0 + chunk);
+#pragma unroll 4
+        for (uint32_t j = j0; j < j1; ++j) rank += (keys64[j] > mine) ? 1u : 0u;  // keys are distinct
+        if (parts > 1u && part > 0u && rank) atomicAdd(&rank_acc[elem], rank);
+    }
+    float e = 0.f;
+    if (want_exp && have) e = exp_f32(__fsub_rn(q, okey_to_float(S.sortmax)));
+    if (parts > 1u) cta_sync();
+    if (have) {
+        if (parts > 1u) rank += rank_acc[tid];  // tid < n <= npad: this thread is part 0 of its own entry
+        cand_q[rank] = q;
+        cand_i[rank] = id;
+        if (want_exp) probs[rank] = e;
+    }
+    cta_sync();
+}
+
+// Sorts cand[0..n), n > THREADS, into the reference ordering with a bitonic network; slots [n, m)
+// (m the next power of two) are filled with entries that sort last.
+__device__ __forceinline__ void sort_candidates(uint32_t n, float* cand_q, uint32_t* cand_i) {
     uint32_t m = 1u;
     while (m < n) m <<= 1;
     for (uint32_t i = n + threadIdx.x; i < m; i += THREADS) {
@@ -439,11 +484,15 @@ __device__ __forceinline__ float row_uniform(const KParams& P, uint32_t b) {
     return u24_to_f32(splitmix_output(seed, done + 1ull));
 }
 
+// `probs_ready`: probs[i] already holds exp(q_i - max) (the small sort computes it alongside the ranks).
+// The chains of thread 0 run in batches of 8 with the next batch's loads already in flight: the
+// additions stay strictly sequential, only loads and comparisons leave the dependent chain.
 __device__ __forceinline__ void ordered_tail(const KParams& P, uint32_t b, const RowCfg& rc, uint32_t n, bool truncated,
                                              uint32_t k_total, Shared& S, const float* cand_q, const uint32_t* cand_i,
-                                             float* probs) {
+                                             float* probs, bool probs_ready = false) {
     const float mx = cand_q[0];  // generate.rs:372 (the ordering is NaN-free, so the fold is its first element)
-    for (uint32_t i = threadIdx.x; i < n; i += THREADS) probs[i] = exp_f32(__fsub_rn(cand_q[i], mx));  // :373
+    if (!probs_ready)
+        for (uint32_t i = threadIdx.x; i < n; i += THREADS) probs[i] = exp_f32(__fsub_rn(cand_q[i], mx));  // :373
     if (threadIdx.x == 0) {
         S.keep = n;
         S.out_flags = 0u;
@@ -454,20 +503,26 @@ __device__ __forceinline__ void ordered_tail(const KParams& P, uint32_t b, const
         S.kept_n = 0u;
     }
     cta_sync();
+    PHASE(8);
     if (threadIdx.x == 0) {
         // :374 left-to-right f32 sum. Once the sum is >= 1 a term below 2^-24 is under
         // half an ulp and leaves it unchanged, and the terms only get smaller.
         float s = 0.0f;
+        float e[8], nx[8];
+        load_batch8(probs, 0u, n, e);
         for (uint32_t i0 = 0; i0 < n; i0 += 8u) {
-            float e[8];  // the loads of a batch do not depend on the running sum
-            load_batch8(probs, i0, n, e);
+            if (i0 + 8u < n) load_batch8(probs, i0 + 8u, n, nx);
             if (e[0] < 5.9604644775390625e-08f && s >= 1.0f) break;  // this and every later term is a no-op
 #pragma unroll
             for (int j = 0; j < 8; ++j) s = __fadd_rn(s, e[j]);       // adding 0.0f past the end changes nothing
+#pragma unroll
+            for (int j = 0; j < 8; ++j) e[j] = nx[j];
         }
         S.f_sum = s;
     }
+    const float e_first = probs[0];  // read before anyone normalises it (the barrier below comes first)
     cta_sync();
+    PHASE(9);
     const float sum = S.f_sum;
     const bool degenerate = (sum <= 0.0f) || !(fabsf(sum) <= 3.402823466e38f);  // :375 (catches NaN and inf)
     if (degenerate) {
@@ -478,44 +533,38 @@ __device__ __forceinline__ void ordered_tail(const KParams& P, uint32_t b, const
         cta_sync();
         return;
     }
-    for (uint32_t i = threadIdx.x; i < n; i += THREADS) probs[i] = __fdiv_rn(probs[i], sum);  // :378-380
-    cta_sync();
-    // :384-395 min-p: leading run with p >= min_p * p[0], never empty
-    bool unknown_tail = false;  // kept set may reach past the window in a way the window cannot settle
-    if (rc.min_p > 0.0f) {
-        const float thr = __fmul_rn(rc.min_p, probs[0]);
+    // :378-380 normalise, and :384-395 min-p in the same sweep: the leading run with p >= min_p * p[0],
+    // never empty. Every thread derives p[0] itself, so no barrier separates the two.
+    const float thr = __fmul_rn(rc.min_p, __fdiv_rn(e_first, sum));
+    {
         uint32_t first_fail = n;
         for (uint32_t i = threadIdx.x; i < n; i += THREADS) {
-            if (!(probs[i] >= thr)) {
-                first_fail = i;
-                break;
-            }
+            const float pi = __fdiv_rn(probs[i], sum);
+            probs[i] = pi;
+            if (rc.min_p > 0.0f && !(pi >= thr) && first_fail == n) first_fail = i;
         }
         if (first_fail < n) atomicMin(&S.keep, first_fail);
-        cta_sync();
-        if (threadIdx.x == 0) {
-            S.f_thr = thr;
-            if (S.keep < 1u) S.keep = 1u;
-        }
-        cta_sync();
-        // every window entry passed and more entries follow: whether those pass is
-        // only certain when the threshold is at least 2^-24 of the leader
-        if (truncated && S.keep == n && rc.min_p < 5.9604644775390625e-08f) unknown_tail = true;
     }
-    const uint32_t keep_minp = S.keep;
-    const bool open_tail = truncated && keep_minp == n && !(rc.min_p > 0.0f);  // kept set continues past the window
+    cta_sync();
+    PHASE(10);
     if (threadIdx.x == 0) {
+        const uint32_t keep_minp = max(S.keep, 1u);
+        // every window entry passed min-p and more entries follow: whether those pass is only certain
+        // when the threshold is at least 2^-24 of the leader
+        const bool unknown_tail = rc.min_p > 0.0f && truncated && keep_minp == n && rc.min_p < 5.9604644775390625e-08f;
+        const bool open_tail = truncated && keep_minp == n && !(rc.min_p > 0.0f);  // kept set continues past the window
+        if (rc.min_p > 0.0f) S.f_thr = thr;
         uint32_t keep = keep_minp;
         float total = 0.0f;
         bool reached = false;
+        float p[8], nx[8];
+        load_batch8(probs, 0u, keep_minp, p);
         if (rc.top_p < 1.0f) {
-            // :397-409; the later re-summation of the kept prefix (:411) repeats the same additions.
-            // Batches of 8: the additions stay strictly sequential, only the loads and the
-            // comparisons are taken off the dependent chain.
+            // :397-409; the later re-summation of the kept prefix (:411) repeats the same additions
             float cum = 0.0f;
             for (uint32_t i0 = 0; i0 < keep_minp && !reached; i0 += 8u) {
-                float p[8], c[8];
-                load_batch8(probs, i0, keep_minp, p);
+                if (i0 + 8u < keep_minp) load_batch8(probs, i0 + 8u, keep_minp, nx);
+                float c[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     cum = __fadd_rn(cum, p[j]);
@@ -530,13 +579,16 @@ __device__ __forceinline__ void ordered_tail(const KParams& P, uint32_t b, const
                     }
                 }
                 if (!reached) total = cum;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) p[j] = nx[j];
             }
         } else {
             for (uint32_t i0 = 0; i0 < keep_minp; i0 += 8u) {
-                float p[8];
-                load_batch8(probs, i0, keep_minp, p);
+                if (i0 + 8u < keep_minp) load_batch8(probs, i0 + 8u, keep_minp, nx);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) total = __fadd_rn(total, p[j]);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) p[j] = nx[j];
             }
         }
         // entries past the window add less than half an ulp to `cum`/`total`, so both are final
@@ -549,9 +601,10 @@ __device__ __forceinline__ void ordered_tail(const KParams& P, uint32_t b, const
         uint32_t flags = LLM_CUDA_ROW_DRAW_CONSUMED;
         uint32_t token = 0u;
         bool found = false;
+        load_batch8(probs, 0u, keep, p);
         for (uint32_t i0 = 0; i0 < keep && !found; i0 += 8u) {  // :413-418, in batches of 8
-            float p[8], rr[8];
-            load_batch8(probs, i0, keep, p);
+            if (i0 + 8u < keep) load_batch8(probs, i0 + 8u, keep, nx);
+            float rr[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 rr[j] = r;                 // r before entry i0+j is examined
@@ -564,6 +617,8 @@ __device__ __forceinline__ void ordered_tail(const KParams& P, uint32_t b, const
                     found = true;
                 }
             }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) p[j] = nx[j];
         }
         if (!found) {
             if (tail_kept || unknown_tail) {

@@ -126,17 +126,6 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     return false;
 }
 
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-#define PHASE(slot)                                                                                              \
-    do {                                                                                                         \
-        if (P.phase_ns && threadIdx.x == 0)                                                                      \
-            P.phase_ns[((size_t)(blockIdx.y + P.row_base) * gridDim.x + blockIdx.x) * 8u + (slot)] = global_ns();              \
-    } while (0)
-
 // A row that needs the full ordering where no full-sort scratch exists (the allocation-free
 // entry point, candidate lists gathered from other GPUs): reported, not guessed.
 __device__ __forceinline__ void report_unresolved(const KParams& P, uint32_t b) {
@@ -153,11 +142,7 @@ __device__ __forceinline__ void report_unresolved(const KParams& P, uint32_t b) 
 __device__ __forceinline__ float window_stream_bound(float qmax) {
     return __fsub_rn(__fsub_rn(qmax, WINDOW_STREAM), __fmul_rn(fabsf(qmax), 2.384185791015625e-07f));
 }
-#ifdef LLMC_EXPERIMENT_NO_DIV
-__device__ __forceinline__ float temper(float x, float T) { return x; }
-#else
 __device__ __forceinline__ float temper(float x, float T) { return (T == 1.0f) ? x : __fdiv_rn(x, T); }  // generate.rs:357-359
-#endif
 
 // The r-th largest of the 32 lanes' keys (1 <= r <= 32), returned to every lane. Keys are ordered
 // keys of floats, all above 0, so 0 serves as "taken".
@@ -210,7 +195,13 @@ __device__ int finish_row(const KParams& P, uint32_t b, const RowCfg& rc, uint32
     }
     if (overflow) return 1;  // the candidates did not fit: the window tier in global memory can still take the row
     PHASE(3);
-    sort_candidates(n, cand_q, cand_i, keys64);
+    // sets of up to THREADS entries are ranked directly, the exponentials computed alongside
+    const bool small = n <= (uint32_t)THREADS;
+    const bool small_tail = small && !P.out_q && !rc.greedy;
+    if (small)
+        sort_small(n, S, cand_q, cand_i, keys64, S.hist[0], probs, small_tail);
+    else
+        sort_candidates(n, cand_q, cand_i);
     PHASE(4);
     const uint32_t n_use = min(n, rc.k_eff);
     const bool truncated = rc.windowed && (n_use < rc.k_eff);
@@ -235,11 +226,13 @@ __device__ int finish_row(const KParams& P, uint32_t b, const RowCfg& rc, uint32
         write_row_outputs(P, b, 0u, S, n_use ? cand_q[0] : 0.f, cand_i, probs, 0u);
         return 0;
     }
-    ordered_tail(P, b, rc, n_use, truncated, rc.k_eff, S, cand_q, cand_i, probs);
+    const uint32_t wflag = rc.windowed ? LLM_CUDA_ROW_WINDOWED : 0u;
+    ordered_tail(P, b, rc, n_use, truncated, rc.k_eff, S, cand_q, cand_i, probs, small_tail);
     PHASE(5);
     if (S.out_flags & ROW_NEEDS_FULL) return 2;  // the kept set or the walk leaves the window: the whole row is needed
-    write_row_outputs(P, b, rc.windowed ? LLM_CUDA_ROW_WINDOWED : 0u, S, cand_q[0], cand_i, probs, S.keep);
+    write_row_outputs(P, b, wflag, S, cand_q[0], cand_i, probs, S.keep);
     PHASE(6);
+    PHASE(11);
     return 0;
 }
 
@@ -268,7 +261,7 @@ __device__ uint32_t merge_lists(const KParams& P, uint32_t b, const RowCfg& rc, 
     const uint32_t k = rc.k_eff;
     const uint32_t r = (k + nsh - 1u) / nsh;
     for (uint32_t s = threadIdx.x; s < nsh; s += THREADS) {
-        const size_t at = (size_t)s * P.sc_rows + b;
+        const size_t at = (size_t)s * P.sc_cnt_shard + b;
         if (P.sc_maxkey) atomicMax(&S.max_key, __ldcg(&P.sc_maxkey[at]));
         const uint32_t raw = __ldcg(&P.sc_cnt[at]);
         if (raw == 0xffffffffu) {
@@ -278,7 +271,7 @@ __device__ uint32_t merge_lists(const KParams& P, uint32_t b, const RowCfg& rc, 
             atomicAdd(&S.newcount, cnt);
             if (!rc.windowed) {
                 const bool sorted = all_sorted || (raw & LIST_SORTED);
-                const float* sq = P.sc_q + at * P.sc_stride;
+                const float* sq = P.sc_q + (size_t)s * P.sc_shard_words + (size_t)b * P.sc_stride;
                 if (sorted && cnt >= k) atomicMax(&S.tau_key, okey(__ldcg(&sq[k - 1u])));
                 atomicMin(&S.minkey, (sorted && cnt >= r) ? okey(__ldcg(&sq[r - 1u])) : LOWEST);
             }
@@ -293,12 +286,11 @@ __device__ uint32_t merge_lists(const KParams& P, uint32_t b, const RowCfg& rc, 
         const uint32_t thr = rc.windowed ? LOWEST : max(S.tau_key, S.minkey == 0xffffffffu ? LOWEST : S.minkey);
         const uint32_t lane = threadIdx.x & 31u;
         for (uint32_t s = threadIdx.x >> 5; s < nsh; s += WARPS) {
-            const size_t at = (size_t)s * P.sc_rows + b;
-            const uint32_t raw = __ldcg(&P.sc_cnt[at]);
+            const uint32_t raw = __ldcg(&P.sc_cnt[(size_t)s * P.sc_cnt_shard + b]);
             const uint32_t cnt = min(raw & LIST_COUNT, P.sc_stride);
             const bool sorted = all_sorted || (raw & LIST_SORTED);
-            const float* sq = P.sc_q + at * P.sc_stride;
-            const uint32_t* si = P.sc_i + at * P.sc_stride;
+            const float* sq = P.sc_q + (size_t)s * P.sc_shard_words + (size_t)b * P.sc_stride;
+            const uint32_t* si = P.sc_i + (size_t)s * P.sc_shard_words + (size_t)b * P.sc_stride;
             for (uint32_t i0 = 0; i0 < cnt; i0 += 32u) {
                 const uint32_t i = i0 + lane;
                 const float q = i < cnt ? __ldcg(&sq[i]) : 0.0f;
@@ -322,8 +314,7 @@ __device__ uint32_t merge_lists(const KParams& P, uint32_t b, const RowCfg& rc, 
         return S.count;
     }
     for (uint32_t s = 0; s < nsh && !overflow; ++s) {
-        const size_t at = (size_t)s * P.sc_rows + b;
-        const uint32_t cnt = min(__ldcg(&P.sc_cnt[at]) & LIST_COUNT, P.sc_stride);
+        const uint32_t cnt = min(__ldcg(&P.sc_cnt[(size_t)s * P.sc_cnt_shard + b]) & LIST_COUNT, P.sc_stride);
         uint32_t n = S.count;
         if (n + cnt > P.ccap) {
             if (!rc.windowed) {
@@ -335,8 +326,8 @@ __device__ uint32_t merge_lists(const KParams& P, uint32_t b, const RowCfg& rc, 
             if (n + cnt > P.ccap) overflow = true;
         }
         if (overflow) break;
-        const float* sq = P.sc_q + at * P.sc_stride;
-        const uint32_t* si = P.sc_i + at * P.sc_stride;
+        const float* sq = P.sc_q + (size_t)s * P.sc_shard_words + (size_t)b * P.sc_stride;
+        const uint32_t* si = P.sc_i + (size_t)s * P.sc_shard_words + (size_t)b * P.sc_stride;
         for (uint32_t i = threadIdx.x; i < cnt; i += THREADS) {
             const float q = __ldcg(&sq[i]);
             cand_q[n + i] = q;
@@ -371,7 +362,6 @@ struct FullShared {
     float sum, total, u, r, thr, mx;
 };
 
-constexpr uint32_t FULL_SLOT_ROUNDS = 1u << 16;  // seconds of polling: thousands of rows can queue for the slots of a launch
 
 // Claims a free scratch slot. Every holder is a running CTA of this same grid that releases its
 // slot without waiting for anyone, so a bounded poll is enough; 0xffffffff when the bound runs out.
@@ -379,7 +369,7 @@ __device__ uint32_t acquire_full_slot(const KParams& P) {
     const uint32_t n = P.full_nslots;
     if (!P.full_slots || n == 0u) return 0xffffffffu;
     uint32_t i = (blockIdx.y * gridDim.x + blockIdx.x) % n;
-    for (uint32_t round = 0; round < FULL_SLOT_ROUNDS; ++round) {
+    for (uint32_t round = 0; round < P.full_slot_rounds; ++round) {
         for (uint32_t k = 0; k < n; ++k) {
             if (atomicCAS(&P.full_slots[i], 0u, 1u) == 0u) return i;
             i = (i + 1u == n) ? 0u : i + 1u;
@@ -914,6 +904,42 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
     }
 }
 
+// Optional per-stage output: the edited value (allowed mask, every penalty application; before temperature)
+// at each history position whose id lies in this CTA's columns [gid0, gid0 + ncols); NaN for ids outside
+// the matrix. `table`: the id -> edited value table exists (penalty rows of kernels built with tables).
+// Not inlined: rarely asked for, and kept out of the streaming kernel's register allocation.
+template <typename ElemT>
+__device__ __noinline__ void write_penalized(const KParams& P, uint32_t b, uint32_t hlen, uint32_t gid0, uint32_t ncols, bool shard0,
+                                             bool table, const uint32_t* hkeys, const uint32_t* hcnt) {
+    const uint32_t* hist = P.history + (size_t)b * P.hist_stride;
+    float* out = P.penalized_out + (size_t)b * P.hist_stride;
+    const ElemT* row = reinterpret_cast<const ElemT*>(P.logits) + (size_t)b * P.row_stride;
+    for (uint32_t j = threadIdx.x; j < hlen; j += THREADS) {
+        const uint32_t id = __ldg(&hist[j]);
+        if (id >= gid0 && id - gid0 < ncols) {
+            float v;
+            if (table) {
+                v = __uint_as_float(0x7fc00000u);
+                const uint32_t mask = P.hash_slots - 1u;
+                uint32_t h = hash_slot(id, mask);
+                for (uint32_t probe = 0; probe < P.hash_slots; ++probe) {
+                    if (hkeys[h] == id) {
+                        v = __uint_as_float(hcnt[h]);
+                        break;
+                    }
+                    h = (h + 1u) & mask;
+                }
+            } else {
+                v = load_logit(row + (id - P.col_offset));
+                if (id_blocked(P, id)) v = neg_inf();
+            }
+            out[j] = v;
+        } else if (shard0 && !(id >= P.col_offset && id - P.col_offset < P.vocab)) {
+            out[j] = __uint_as_float(0x7fc00000u);
+        }
+    }
+}
+
 template <typename ElemT, bool BITS, int MODE, int U>
 __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const __grid_constant__ KParams P) {
     constexpr int VEC = Traits<ElemT>::VEC;
@@ -935,7 +961,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
     float* lane_top = reinterpret_cast<float*>(hcnt + P.hash_slots);  // rank cuts above 256: every lane's best values
     uint32_t* grp_max = reinterpret_cast<uint32_t*>(lane_top + P.lane_top_words);  // one flag word per 32 vectors
 
-    const uint32_t b = blockIdx.y + P.row_base, shard = blockIdx.x, tid = threadIdx.x;
+    const uint32_t b = blockIdx.y, shard = blockIdx.x, tid = threadIdx.x;
     const unsigned lane = tid & 31u, warp = tid >> 5;
     const uint32_t LOWEST = 0x007fffffu;  // okey(-inf)
     // A launch that asked to overlap its predecessor is released by the producer lane of every CTA
@@ -1001,12 +1027,15 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
         S.max_key = LOWEST;
         S.error = 0u;
         S.last = 0u;
+        S.sortmax = 0u;
+        S.keep = 0u;
     }
     __syncthreads();  // the one barrier all STREAM_THREADS threads share
     RowCfg rc = S.rc;
     if (MODE == 1) rc.windowed = 1u;  // lets the compiler drop the exact-selection code
     if (MODE == 2) rc.windowed = 0u;  // ... or the window code
     PHASE(0);
+    PHASE(12);
     if (rc.invalid || P.force_full) {
         // the stages already requested must have landed before this CTA's shared memory is given up
         for (uint32_t tt = 0; tt < first_stages; ++tt) (void)mbar_wait_bounded(&full_bar[tt], 0u);
@@ -1184,6 +1213,12 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
     const bool sweep_k = !rc.windowed;
     const uint32_t m_lane = sweep_k ? (rc.k_eff + (uint32_t)THREADS - 1u) / (uint32_t)THREADS : 1u;  // 1..8
     uint32_t tau_k = LOWEST;  // this warp's view of the running lower bound (ordered key, pre-temperature domain)
+    // The bound is a pre-temperature value, the reference ranks by x / T (generate.rs:357-367): with T != 1
+    // neighbouring floats can round to the same quotient, and one of them with a lower index then comes
+    // before the bound's own element. Filters therefore use the bound lowered by four floats (no more
+    // than two or three values share a quotient); the exact selection afterwards works on the quotients.
+    const uint32_t tau_slack = (T == 1.0f) ? 0u : 4u;
+    auto lowered = [&](uint32_t key) { return key > LOWEST + tau_slack ? key - tau_slack : LOWEST; };
     float lmin = neg_inf();   // m_lane > 1: the lane's m-th best so far
     if (m_lane > 1u)
         for (uint32_t i = 0; i < m_lane; ++i) lane_top[i * THREADS + tid] = neg_inf();
@@ -1280,7 +1315,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
                 const uint32_t lo = __reduce_min_sync(FULL_MASK, vol_load(&S.wkth[lane & (WARPS - 1u)]));
                 tau_k = max(tau_k, max(lo, LOWEST));
             }
-            tau_run = okey_to_float(tau_k);
+            tau_run = okey_to_float(lowered(tau_k));
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
@@ -1294,23 +1329,22 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
         // covers rows too short for a whole vector: only the leading / trailing elements exist
         const uint32_t wk = __reduce_max_sync(FULL_MASK, okey(tmax));
         if (lane == 0) atomicMax(&S.max_key, wk);
+    } else {
+        // every lane's final values go into its warp's bound (a warp still sweeping that reads it early
+        // only sees a bound that is valid already)
+        const uint32_t kth = warp_bound();
+        if (lane == 0) *(volatile uint32_t*)&S.wkth[warp] = kth;
     }
     cta_sync();
     bool window_filtered = false;  // the candidates already are exactly the window
     PHASE(7);
+    if (P.penalized_out && P.history) {
+        grid_dependency_wait();
+        write_penalized<ElemT>(P, b, rc.hlen, gid0, ncols, shard == 0u, BITS && rc.has_pen, hkeys, hcnt);
+    }
     {
         // the sweep fixed the threshold: the penalised ids, the leading / trailing elements and the
         // vectors flagged during the sweep (read again, from L2) are tested exactly and appended
-        if (sweep_k) {
-            // every lane's final values go into its warp's bound
-            const uint32_t kth = warp_bound();
-            if (lane == 0) S.wkth[warp] = kth;
-        }
-        if (tid == 0) {
-            S.keep = 0u;
-            S.last = 0u;
-        }
-        cta_sync();
         // every thread derives the final threshold itself: from the row's maximum (window rows), or
         // as the minimum of the warps' bounds (a lower bound of the k-th largest value)
         const float qmaxf = temper(okey_to_float(S.max_key), T);
@@ -1319,7 +1353,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
             uint32_t lo = S.wkth[0];
 #pragma unroll
             for (int w = 1; w < WARPS; ++w) lo = min(lo, S.wkth[w]);
-            tau = okey_to_float(max(lo, LOWEST));
+            tau = okey_to_float(lowered(max(lo, LOWEST)));
         } else {
             tau = okey_to_float(raw_threshold_key(window_stream_bound(qmaxf), T));
         }
@@ -1368,6 +1402,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
         // (3) the flagged vectors
         const uint32_t ngroups = (nvi + 31u) / 32u;
         const uint4* gv = reinterpret_cast<const uint4*>(vbase);
+        const uint4 nothing = make_uint4(0u, 0u, 0u, 0u);
         uint32_t* vlist = reinterpret_cast<uint32_t*>(scratch);
         const uint32_t VLIST_CAP = P.vlist_cap;
         // list them: one shared-memory atomic per warp step (prefix sums inside the warp)
@@ -1395,10 +1430,18 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
             }
         }
         cta_sync();
+        PHASE(13);
         const uint32_t nq = S.keep;
-        // everything appended so far plus every element of every flagged vector: if even that fits,
-        // the buffer cannot fill up and the final selection sees it all at once
-        can_overflow = (uint64_t)S.count + (uint64_t)nq * (uint32_t)VEC > (uint64_t)P.ccap;
+        // a round of an exact-selection row appends at most 1024 entries: 1024/VEC vectors
+        const uint32_t ROUND = sweep_k ? 1024u / (uint32_t)VEC : (uint32_t)THREADS;
+        // the rounds take their vectors from the list, or straight from the flag words when the list
+        // could not hold them all
+        const bool listed = nq <= VLIST_CAP;
+        const uint32_t rounds = listed ? (nq + ROUND - 1u) / ROUND : (ngroups + ROUND / 32u - 1u) / (ROUND / 32u);
+        // everything appended so far (at most half the table's slots and one warp's worth of leading /
+        // trailing elements) plus every element of every flagged vector: if even that fits, the buffer
+        // cannot fill up and the final selection sees it all at once
+        can_overflow = (uint64_t)(BITS ? P.hash_slots / 2u : 0u) + 32u + (uint64_t)nq * (uint32_t)VEC > (uint64_t)P.ccap;
         // read a flagged vector again (L2) and append the elements that matter; the appends of a
         // warp step share one atomic
         auto examine = [&](bool have, uint32_t v, const uint4& data) {
@@ -1447,39 +1490,34 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
                 }
             }
         };
-        // a round of an exact-selection row appends at most 1024 entries: 1024/VEC vectors
-        const uint32_t ROUND = sweep_k ? 1024u / (uint32_t)VEC : (uint32_t)THREADS;
-        const uint4 nothing = make_uint4(0u, 0u, 0u, 0u);
-        if (nq <= VLIST_CAP) {
-            // four rounds' loads are issued together: they may miss L2 by now, and one trip to memory
-            // is better than four
-            for (uint32_t i0 = 0; i0 < nq; i0 += 4u * ROUND) {
-                uint32_t v[4];
-                uint4 d[4];
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const uint32_t i = i0 + (uint32_t)k * ROUND + tid;
-                    v[k] = (tid < ROUND && i < nq) ? vlist[i] : 0xffffffffu;
-                    d[k] = v[k] < nvi ? __ldg(gv + v[k]) : nothing;
-                }
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    if (i0 + (uint32_t)k * ROUND < nq) {  // the same for every thread
-                        examine(v[k] < nvi, v[k], d[k]);
-                        settle();
-                    }
-                }
+        // the vector of round r for this thread; the load of the next round is issued before the current
+        // round is examined, so a row pays one trip to L2 (or to memory: the vector may have left L2)
+        auto fetch = [&](uint32_t r, uint32_t& v, uint4& d) {
+            bool have;
+            if (listed) {
+                const uint32_t i = r * ROUND + tid;
+                v = (r < rounds && tid < ROUND && i < nq) ? vlist[i] : 0xffffffffu;
+                have = v < nvi;
+            } else {
+                const uint32_t wr = ROUND / 32u;  // warps taking part in a round
+                const uint32_t g = r * wr + warp;
+                const unsigned m = (r < rounds && warp < wr && g < ngroups) ? grp_max[g] : 0u;  // same word for the whole warp
+                v = g * 32u + lane;
+                have = ((m >> lane) & 1u) && v < nvi;
+                if (!have) v = 0xffffffffu;
             }
-        } else {
-            const uint32_t wr = ROUND / 32u;  // warps taking part in a round
-            for (uint32_t g0 = 0; g0 < ngroups; g0 += wr) {
-                const uint32_t g = g0 + warp;
-                const unsigned m = (warp < wr && g < ngroups) ? grp_max[g] : 0u;  // same word for the whole warp
-                const uint32_t v = g * 32u + lane;
-                const bool have = ((m >> lane) & 1u) && v < nvi;
-                examine(have, v, have ? __ldg(gv + v) : nothing);
-                settle();
-            }
+            d = have ? __ldg(gv + v) : nothing;
+        };
+        uint32_t v_next;
+        uint4 d_next;
+        fetch(0u, v_next, d_next);
+#pragma unroll 1
+        for (uint32_t r = 0; r < rounds; ++r) {
+            const uint32_t v = v_next;
+            const uint4 d = d_next;
+            fetch(r + 1u, v_next, d_next);
+            examine(v < nvi, v, d);
+            settle();
         }
         cta_sync();
         window_filtered = rc.windowed && P.split == 1u;
@@ -1499,6 +1537,16 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
 
     if (P.split == 1u) {
         const int undecided = finish_row(P, b, rc, n, overflow, qmax, S, cand_q, cand_i, scratch, window_filtered);
+#ifdef LLMC_DEV_TWICE  // experiment: the same tail once more, now with its instructions cached
+        if (!undecided) {
+            cta_sync();
+            if (tid == 0) S.sortmax = 0u;
+            cta_sync();
+            PHASE(14);
+            (void)finish_row(P, b, rc, n, overflow, qmax, S, cand_q, cand_i, scratch, window_filtered);
+            PHASE(15);
+        }
+#endif
         if (undecided)
             // the window alone is tried first, unless it is most of the row anyway
             full_sort_row(P, b, *reinterpret_cast<FullShared*>(ring), reinterpret_cast<uint32_t*>(ring + 512), hkeys, hcnt,
@@ -1515,7 +1563,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
         if (n <= (uint32_t)THREADS) {
             // small enough for the rank sort: ordered (and cut at k) in two barriers; the merging CTA
             // uses the order to leave most of the list behind
-            sort_candidates(n, cand_q, cand_i, reinterpret_cast<uint64_t*>(scratch));
+            sort_small(n, S, cand_q, cand_i, reinterpret_cast<uint64_t*>(scratch), S.hist[0], nullptr, false);
             n = min(n, rc.k_eff);
             list_sorted = true;
         }
@@ -1568,6 +1616,7 @@ __global__ void __launch_bounds__(THREADS) merge_draw_kernel(const __grid_consta
         resolve_row(P, b, S.rc);
         S.error = 0u;
         S.u_pre_valid = 0u;
+        S.sortmax = 0u;
     }
     cta_sync();
     const RowCfg rc = S.rc;
@@ -1608,11 +1657,11 @@ __global__ void advance_rows_kernel(uint32_t batch, const uint32_t* tokens, cons
         if (len < cap) {  // still filling: keep chronological order in [0, len)
             history[(size_t)r * history_stride + len] = tok;
             history_len[r] = len + 1u;
-            if (history_pos) history_pos[r] = (len + 1u) % cap;
+            history_pos[r] = (len + 1u) % cap;
         } else {  // ring: overwrite the oldest entry (the penalty does not depend on the order)
-            const uint32_t pos = history_pos ? history_pos[r] % cap : 0u;
+            const uint32_t pos = history_pos[r] % cap;
             history[(size_t)r * history_stride + pos] = tok;
-            if (history_pos) history_pos[r] = (pos + 1u) % cap;
+            history_pos[r] = (pos + 1u) % cap;
         }
     }
 }
@@ -1628,8 +1677,12 @@ __global__ void pack_allowed_kernel(const uint8_t* allowed, uint32_t n, uint32_t
     bits[w] = word;
 }
 
+#ifndef LLMC_KERNELS_ONLY  // a translation unit that only wants some kernel instantiations stops here
 // ---------------------------------------------------------------------------
 // host side: launch plans
+#ifdef LLMC_DEV
+static int g_dev_stage_u = 0;
+#endif
 static uint32_t pow2_ceil(uint32_t x) {
     uint32_t p = 1u;
     while (p < x) p <<= 1;
@@ -1735,26 +1788,51 @@ int plan_launch(const DeviceInfo& dev, const KParams& base, bool top_k_known, ui
     bool alias3, alias4;
     layout(3u, &smem3, &alias3);
     layout(4u, &smem4, &alias4);
-    const bool big = smem4 <= dev.max_dyn_smem && resident(smem4) >= resident(smem3);
+    bool big = smem4 <= dev.max_dyn_smem && resident(smem4) >= resident(smem3);
+#ifdef LLMC_DEV
+    if (g_dev_stage_u == 3) big = false;
+    if (g_dev_stage_u == 4 && smem4 <= dev.max_dyn_smem) big = true;
+#endif
     plan->stage_u = big ? 4u : 3u;
     const bool aliased = big ? alias4 : alias3;
     const size_t ring_bytes = (size_t)RING_STAGES * plan->stage_u * THREADS * 16u;
+    const size_t smem_total = ring_bytes + tables_bytes + (aliased ? 0u : cand_bytes);
+    if (smem_total > dev.max_dyn_smem) return -1;
     if (aliased) {
         plan->cand_off = 0u;
         plan->scratch_off = (uint32_t)cand_bytes;
         plan->tables_off = (uint32_t)ring_bytes;
         plan->vlist_cap = (uint32_t)((ring_bytes - cand_bytes) / 4u);
-        plan->smem = ring_bytes + tables_bytes;
     } else {
         plan->cand_off = (uint32_t)ring_bytes;
         plan->scratch_off = 0u;
         plan->tables_off = (uint32_t)(ring_bytes + cand_bytes);
         plan->vlist_cap = (uint32_t)(ring_bytes / 4u);
-        plan->smem = ring_bytes + cand_bytes + tables_bytes;
     }
-    if (plan->smem > dev.max_dyn_smem) return -1;
+    plan->smem = smem_total;
     return 0;
 }
+
+void apply_plan(const LaunchPlan& plan, KParams* P) {
+    P->split = plan.split;
+    P->shard_cols = plan.shard_cols;
+    P->kcap = plan.kcap;
+    P->ccap = plan.ccap;
+    P->limit = plan.limit;
+    P->hash_slots = plan.hash_slots;
+    P->bitmap_words = plan.bitmap_words;
+    P->lane_top_words = plan.lane_top_words;
+    P->cand_off = plan.cand_off;
+    P->scratch_off = plan.scratch_off;
+    P->tables_off = plan.tables_off;
+    P->vlist_cap = plan.vlist_cap;
+}
+
+#ifdef LLMC_DEV
+void dev_override(int key, int value) {
+    if (key == 0) g_dev_stage_u = value;
+}
+#endif
 
 template <typename ElemT, bool BITS, int MODE, int U>
 static cudaError_t configure_one(int v) {
@@ -1788,9 +1866,9 @@ cudaError_t configure_kernels(size_t max_dyn_smem) {
 }
 
 template <typename ElemT, bool BITS, int MODE, int U>
-static cudaError_t launch_stream_t(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap, uint32_t rows) {
+static cudaError_t launch_stream_t(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap) {
     auto kern = stream_select_kernel<ElemT, BITS, MODE, U>;
-    dim3 grid(plan.split, rows, 1);
+    dim3 grid(plan.split, P.batch, 1);
     if (!overlap) {
         kern<<<grid, STREAM_THREADS, plan.smem, stream>>>(P);
         return cudaGetLastError();
@@ -1812,26 +1890,25 @@ static cudaError_t launch_stream_t(const KParams& P, const LaunchPlan& plan, cud
 }
 
 template <typename ElemT, bool BITS, int MODE>
-static cudaError_t launch_stream_u(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap, uint32_t rows) {
-    if (plan.stage_u == 4u) return launch_stream_t<ElemT, BITS, MODE, 4>(P, plan, stream, overlap, rows);
-    return launch_stream_t<ElemT, BITS, MODE, 3>(P, plan, stream, overlap, rows);
+static cudaError_t launch_stream_u(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap) {
+    if (plan.stage_u == 4u) return launch_stream_t<ElemT, BITS, MODE, 4>(P, plan, stream, overlap);
+    return launch_stream_t<ElemT, BITS, MODE, 3>(P, plan, stream, overlap);
 }
 
 template <typename ElemT, bool BITS>
-static cudaError_t launch_stream_m(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap, uint32_t rows) {
-    if (plan.mode == 1) return launch_stream_u<ElemT, BITS, 1>(P, plan, stream, overlap, rows);
-    if (plan.mode == 2) return launch_stream_u<ElemT, BITS, 2>(P, plan, stream, overlap, rows);
-    return launch_stream_u<ElemT, BITS, 0>(P, plan, stream, overlap, rows);
+static cudaError_t launch_stream_m(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap) {
+    if (plan.mode == 1) return launch_stream_u<ElemT, BITS, 1>(P, plan, stream, overlap);
+    if (plan.mode == 2) return launch_stream_u<ElemT, BITS, 2>(P, plan, stream, overlap);
+    return launch_stream_u<ElemT, BITS, 0>(P, plan, stream, overlap);
 }
 
-cudaError_t launch_stream_select(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap, uint32_t rows) {
-    if (rows == 0u) rows = P.batch;
+cudaError_t launch_stream_select(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap) {
     if (P.dtype == LLM_CUDA_DTYPE_BF16) {
-        return plan.bits ? launch_stream_m<uint16_t, true>(P, plan, stream, overlap, rows)
-                         : launch_stream_m<uint16_t, false>(P, plan, stream, overlap, rows);
+        return plan.bits ? launch_stream_m<uint16_t, true>(P, plan, stream, overlap)
+                         : launch_stream_m<uint16_t, false>(P, plan, stream, overlap);
     }
-    return plan.bits ? launch_stream_m<float, true>(P, plan, stream, overlap, rows)
-                     : launch_stream_m<float, false>(P, plan, stream, overlap, rows);
+    return plan.bits ? launch_stream_m<float, true>(P, plan, stream, overlap)
+                     : launch_stream_m<float, false>(P, plan, stream, overlap);
 }
 
 cudaError_t launch_merge_draw(const KParams& P, const LaunchPlan& plan, cudaStream_t stream) {
@@ -1855,5 +1932,7 @@ cudaError_t launch_pack_allowed(const uint8_t* allowed_dev, uint32_t n, uint32_t
     pack_allowed_kernel<<<(words + 127u) / 128u, 128, 0, stream>>>(allowed_dev, n, bits);
     return cudaGetLastError();
 }
+
+#endif  // LLMC_KERNELS_ONLY
 
 }  // namespace llmc

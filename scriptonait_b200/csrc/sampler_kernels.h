@@ -6,7 +6,15 @@
 #include <stddef.h>
 #include <stdint.h>
 
+struct llm_cuda_sample_args;
+
 namespace llmc {
+
+// Argument checks every entry point that takes a device-pointer argument block shares: block size,
+// dtype, pointers and their alignment, strides, history bounds, NaN scalars. Returns 0, or a negative
+// LLM_CUDA_ERR_* with its text in `err`. Limits that depend on who owns the scratch (batch, vocabulary,
+// history, rank cut) are checked by the callers.
+int validate_sample_args(const llm_cuda_sample_args* a, bool needs_logits, char* err, size_t err_len);
 
 struct KParams {
     const void* logits;
@@ -50,20 +58,27 @@ struct KParams {
     uint32_t* sc_maxkey;            // [shard][row] ordered key of the shard's maximum q
     uint32_t* sc_ticket;            // [row]
     uint32_t sc_stride, sc_rows;
+    // where shard s keeps its lists: values / ids of row b at sc_q / sc_i + s*sc_shard_words + b*sc_stride, its
+    // count at sc_cnt[s*sc_cnt_shard + b] (sc_rows*sc_stride and sc_rows for separate arrays; one packed block per
+    // shard - values, ids, counts - has the block's length in both)
+    uint32_t sc_shard_words, sc_cnt_shard;
     // candidate lists out (vocabulary sharding step 1); NULL = draw a token
     float* out_q;
     uint32_t* out_i;
     uint32_t* out_cnt;
     uint32_t out_stride;
     uint32_t force_full;
-    uint32_t row_base;              // this launch handles rows row_base .. row_base + gridDim.y - 1
     // full ordering of the rare rows the stream cannot decide: scratch slots claimed by the row's own CTA
     unsigned long long* full_keys;  // [full_nslots][4][full_vpad] 32-bit words (keys in/out, column indices in/out), or NULL = no such stage
     float* full_vals;               // [full_nslots][full_vpad]
     uint32_t* full_slots;           // [full_nslots] 0 = free, 1 = taken; all zero between launches
     uint32_t full_vpad, full_nslots;
+    uint32_t full_slot_rounds;      // polls (about 4 us each) a CTA spends looking for a free slot before it gives the row up
     uint32_t* device_errors;        // bit 0: a bulk copy did not complete within the wait limit; bit 1: no full-sort slot came free
-    unsigned long long* phase_ns;   // optional [CTAs][8] phase timestamps (development aid), or NULL
+    float* penalized_out;           // optional [batch][hist_stride]: post-mask, post-penalty, pre-temperature value at each history position
+#ifdef LLMC_DEV
+    unsigned long long* phase_ns;   // development builds only: optional [CTAs][8] phase timestamps, or NULL
+#endif
 };
 
 struct DeviceInfo {
@@ -89,9 +104,12 @@ int plan_launch(const DeviceInfo& dev, const KParams& base, bool top_k_known, ui
 
 // `overlap`: launch with programmatic stream serialization, so the grid may begin reading its inputs
 // while the previous kernel of the stream (if it is this kernel too) is still finishing.
-// `rows`: rows of this launch, starting at P.row_base (0 = all of P.batch).
-cudaError_t launch_stream_select(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap = false,
-                                 uint32_t rows = 0u);
+cudaError_t launch_stream_select(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap = false);
+// Copies the plan's geometry (split, capacities, shared-memory offsets) into the parameter block.
+void apply_plan(const LaunchPlan& plan, KParams* P);
+#ifdef LLMC_DEV
+void dev_override(int key, int value);  // development builds only: 0 = ring stage size (3 / 4 / 0 auto)
+#endif
 cudaError_t launch_merge_draw(const KParams& P, const LaunchPlan& plan, cudaStream_t stream);
 cudaError_t launch_advance_rows(uint32_t batch, const uint32_t* tokens, const uint32_t* row_flags, uint32_t* history,
                                 uint32_t history_stride, uint32_t window, uint32_t* history_len, uint32_t* history_pos,

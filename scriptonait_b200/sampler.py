@@ -75,6 +75,7 @@ class SampleResult:
     kept_ids: Optional["object"] = None
     kept_probs: Optional["object"] = None
     row_stats: Optional["object"] = None
+    penalized: Optional["object"] = None   # [B, H] post-mask, post-penalty, pre-temperature value at each history position
 
 
 class PreparedCall:
@@ -129,6 +130,22 @@ class Sampler:
     def _check(self, rc: int) -> None:
         if rc != N.OK:
             raise LlmCudaError(rc, self._lib.llm_cuda_last_error(self._h).decode())
+
+    def device_status(self, stream=None) -> int:
+        """Synchronises the stream, then reads and clears the device status word. Raises LlmCudaError
+        (ERR_TIMEOUT) when a bounded wait inside a kernel ran out; returns 0 otherwise."""
+        torch = _torch()
+        st = stream if stream is not None else torch.cuda.current_stream(torch.device(f"cuda:{self.device}")).cuda_stream
+        bits = C.c_uint32()
+        self._check(self._lib.llm_cuda_device_status(self._h, st, C.byref(bits)))
+        return bits.value
+
+    def hold_full_sort_slots(self, hold: bool, wait_rounds: int = 0, stream=None) -> None:
+        """Testing aid: marks every full-ordering scratch slot taken (or frees them) and shortens the
+        slot wait of later launches to `wait_rounds` polls (0 = default)."""
+        torch = _torch()
+        st = stream if stream is not None else torch.cuda.current_stream(torch.device(f"cuda:{self.device}")).cuda_stream
+        self._check(self._lib.llm_cuda_test_hold_full_sort_slots(self._h, 1 if hold else 0, wait_rounds, st))
 
     def last_launch_info(self) -> tuple[int, int]:
         k, s = C.c_uint32(), C.c_uint32()
@@ -217,15 +234,15 @@ class Sampler:
                      draw_index=None, seed_base: int = 0, uniforms=None, batch: Optional[int] = None,
                      row_stride: Optional[int] = None, trace: bool = False, kept_capacity: int = 64, split: int = 0,
                      force_full_sort: bool = False, out_tokens=None, stream=None, prepare_only: bool = False,
-                     overlap_previous: bool = False):
+                     overlap_previous: bool = False, want_penalized: bool = False):
         """Row r of `logits` ([B, V] CUDA tensor, float32 / bfloat16 / uint16 bf16 bits) is one
         `sample_with` call with Rng::seed_from_u64(seeds[r]) advanced by draw_index[r] outputs.
         Parameters are scalars or per-row arrays. Asynchronous on the current (or given) stream.
         With `prepare_only` nothing is launched: the returned PreparedCall re-issues the same call
         (same buffers, same stream) with one C-ABI call per `launch()`, which is what a decode
         loop over fixed buffers wants. `overlap_previous` lets the launch begin reading its inputs
-        while the previous sample_batch launch on the stream is finishing (outputs keep stream
-        order); only for calls whose inputs that previous call does not write."""
+        before the operation that precedes it on the stream has completed (outputs keep stream
+        order); only for calls none of whose inputs that operation writes."""
         torch = _torch()
         assert logits.is_cuda and logits.dim() == 2 and logits.stride(1) == 1, "logits: [B, V] CUDA tensor, unit column stride"
         if logits.dtype == torch.float32:
@@ -247,6 +264,9 @@ class Sampler:
                             force_full_sort=force_full_sort, stream=st, keep=keep)
         a.overlap_previous = 1 if overlap_previous else 0
         res = self._outputs(a, B, trace, kept_capacity, out_tokens, logits.device)
+        if want_penalized and a.history:
+            res.penalized = torch.full((B, int(a.history_stride)), float("nan"), dtype=torch.float32, device=logits.device)
+            a.penalized_out = res.penalized.data_ptr()
         res._keepalive = keep  # inputs must outlive the asynchronous launch
         call = PreparedCall(self, a, res)
         if prepare_only:
@@ -304,6 +324,77 @@ class Sampler:
                                                     cand_stride))
         self._keepalive = keep
         return vals, ids, cnt
+
+    def shard_select_packed(self, logits, *, column_offset: int, vocab_global: int, cand_stride: int,
+                            temperature: ParamT = 1.0, top_k: int = 0, repetition_penalty: ParamT = 1.0, history=None,
+                            history_len=None, allowed_bits=None, allowed_len: Optional[int] = None, eos_id: int = EOS,
+                            split: int = 0, out=None, stream=None, prepare_only: bool = False):
+        """Step 1 into ONE packed block (values, ids, counts; llm_cuda_shard_select_packed): a flat int32
+        tensor of 2*B*cand_stride + B words, ready for a single all-gather. `logits` may have zero columns
+        (a shard past the end of a small vocabulary): the block then holds empty lists."""
+        torch = _torch()
+        assert logits.is_cuda and logits.dim() == 2 and (logits.shape[1] == 0 or logits.stride(1) == 1)
+        dtype = N.DTYPE_F32 if logits.dtype == torch.float32 else N.DTYPE_BF16
+        B, V = int(logits.shape[0]), int(logits.shape[1])
+        st = stream if stream is not None else torch.cuda.current_stream(logits.device).cuda_stream
+        keep: list = [logits]
+        a = self._fill_args(logits=logits.data_ptr() if V else None, batch=B, vocab=V,
+                            row_stride=int(logits.stride(0)) if V else 0, dtype=dtype,
+                            temperature=temperature, top_k=top_k, top_p=1.0, min_p=0.0,
+                            repetition_penalty=repetition_penalty, history=history, history_len=history_len,
+                            allowed_bits=allowed_bits, allowed_len=allowed_len, eos_id=eos_id, seeds=None,
+                            draw_index=None, seed_base=0, uniforms=None, split=split, force_full_sort=False,
+                            stream=st, keep=keep)
+        a.column_offset = column_offset
+        a.vocab_global = vocab_global
+        words = 2 * B * cand_stride + B
+        packed = out if out is not None else torch.zeros(words, dtype=torch.int32, device=logits.device)
+        assert packed.numel() == words and packed.is_contiguous()
+        keep.append(packed)
+        fn, h, ref, ptr = self._lib.llm_cuda_shard_select_packed, self._h, C.byref(a), packed.data_ptr()
+
+        def launch():
+            rc = fn(h, ref, ptr, cand_stride)
+            if rc != N.OK:
+                self._check(rc)
+            return packed
+
+        launch._keepalive = (a, keep)
+        if prepare_only:
+            return launch
+        self._keepalive = keep
+        return launch()
+
+    def merge_draw_packed(self, packed_all, *, batch: int, cand_stride: int, vocab_global: int,
+                          temperature: ParamT = 1.0, top_k: int = 0, top_p: ParamT = 1.0, min_p: ParamT = 0.0,
+                          seeds=None, draw_index=None, seed_base: int = 0, uniforms=None, trace: bool = False,
+                          kept_capacity: int = 64, stream=None, prepare_only: bool = False):
+        """Step 2 over the all-gathered packed blocks [G, 2*B*cand_stride + B] (llm_cuda_merge_draw_packed)."""
+        torch = _torch()
+        G = int(packed_all.shape[0])
+        assert packed_all.is_contiguous() and packed_all.numel() == G * (2 * batch * cand_stride + batch)
+        st = stream if stream is not None else torch.cuda.current_stream(packed_all.device).cuda_stream
+        keep: list = [packed_all]
+        a = self._fill_args(logits=None, batch=batch, vocab=0, row_stride=0, dtype=N.DTYPE_F32, temperature=temperature,
+                            top_k=top_k, top_p=top_p, min_p=min_p, repetition_penalty=1.0, history=None,
+                            history_len=None, allowed_bits=None, allowed_len=None, eos_id=EOS, seeds=seeds,
+                            draw_index=draw_index, seed_base=seed_base, uniforms=uniforms, split=0,
+                            force_full_sort=False, stream=st, keep=keep)
+        a.vocab_global = vocab_global
+        res = self._outputs(a, batch, trace, kept_capacity, None, packed_all.device)
+        res._keepalive = keep
+        fn, h, ref, ptr = self._lib.llm_cuda_merge_draw_packed, self._h, C.byref(a), packed_all.data_ptr()
+
+        def launch():
+            rc = fn(h, ref, ptr, G, cand_stride)
+            if rc != N.OK:
+                self._check(rc)
+            return res
+
+        launch._keepalive = (a, keep)
+        if prepare_only:
+            return launch
+        return launch()
 
     def merge_draw(self, cand_values, cand_ids, cand_count, *, vocab_global: int, temperature: ParamT = 1.0,
                    top_k: int = 0, top_p: ParamT = 1.0, min_p: ParamT = 0.0, seeds=None, draw_index=None,

@@ -8,7 +8,7 @@ one `sample_with` per row returns (crates/llm-core/src/generate.rs:325-420).
   and its own RNG, so rank g takes rows [lo, hi) with their parameters and seeds and no
   data-path collective exists. Concatenating the ranks' tokens is the result.
 * Vocabulary sharding: rank g holds columns [lo, hi) of every row. Each rank selects its
-  best top_k candidates per row (step 1), one all-gather moves the fixed-size lists
+  best top_k candidates per row (step 1) into one packed block, ONE all-gather moves the blocks
   (NCCL over NVLink when the process group is NCCL), and every rank merges and draws
   (step 2) - all ranks obtain the same tokens. Exact because the global top-k is a
   subset of the union of per-shard top-k lists and the softmax runs over the kept k only
@@ -60,21 +60,33 @@ def gather_rows(local_tokens, batch: int, group=None):
     return torch.cat(parts)
 
 
-def all_gather_candidates(values, ids, counts, group=None):
-    """The one exchange of vocabulary sharding: fixed-size candidate lists [B, S] (+ counts
-    [B]) of every rank -> [G, B, S] / [G, B] on every rank. Three all-gathers of
-    B*S*4, B*S*4 and B*4 bytes per rank."""
+def packed_words(batch: int, cand_stride: int) -> int:
+    """32-bit words of one rank's packed candidate block: values [B, S] f32, ids [B, S] u32, counts [B] u32."""
+    return 2 * batch * cand_stride + batch
+
+
+def unpack_candidates(packed_all, batch: int, cand_stride: int):
+    """Views of an all-gathered [G, packed_words] int32 buffer: values [G, B, S] (f32), ids [G, B, S], counts [G, B]."""
+    import torch
+    G = packed_all.shape[0]
+    bs = batch * cand_stride
+    vals = packed_all[:, :bs].view(torch.float32).view(G, batch, cand_stride)
+    ids = packed_all[:, bs:2 * bs].view(G, batch, cand_stride)
+    cnt = packed_all[:, 2 * bs:]
+    return vals, ids, cnt
+
+
+def all_gather_packed(packed, group=None, out=None):
+    """The one exchange of vocabulary sharding: every rank's packed candidate block (a flat int32 tensor
+    of `packed_words` words, 16.5 KB for 32 rows of 64 candidates) -> [G, packed_words] on every rank, in
+    ONE all-gather (NCCL over NVLink for CUDA tensors, gloo for CPU tensors)."""
     import torch
     import torch.distributed as dist
     world = dist.get_world_size(group)
-    gv = torch.empty((world,) + tuple(values.shape), dtype=values.dtype, device=values.device)
-    gi = torch.empty((world,) + tuple(ids.shape), dtype=ids.dtype, device=ids.device)
-    gc = torch.empty((world,) + tuple(counts.shape), dtype=counts.dtype, device=counts.device)
-    # flat views: both NCCL and gloo accept "output = concatenation of the ranks' inputs"
-    dist.all_gather_into_tensor(gv.view(-1), values.contiguous().view(-1), group=group)
-    dist.all_gather_into_tensor(gi.view(-1), ids.contiguous().view(-1), group=group)
-    dist.all_gather_into_tensor(gc.view(-1), counts.contiguous().view(-1), group=group)
-    return gv, gi, gc
+    if out is None:
+        out = torch.empty((world, packed.numel()), dtype=packed.dtype, device=packed.device)
+    dist.all_gather_into_tensor(out.view(-1), packed.view(-1), group=group)
+    return out
 
 
 def sample_vocab_sharded(sampler, local_logits, *, column_offset: int, vocab_global: int, top_k: int,
@@ -85,9 +97,10 @@ def sample_vocab_sharded(sampler, local_logits, *, column_offset: int, vocab_glo
     all-gather the lists, merge and draw. Returns the merge's SampleResult (same tokens on
     every rank)."""
     stride = int(cand_stride or max(top_k, 1))
-    vals, ids, cnt = sampler.shard_select(local_logits, column_offset=column_offset, vocab_global=vocab_global,
-                                          cand_stride=stride, temperature=temperature, top_k=top_k,
-                                          repetition_penalty=repetition_penalty, history=history)
-    gv, gi, gc = all_gather_candidates(vals, ids, cnt, group=group)
-    return sampler.merge_draw(gv, gi, gc, vocab_global=vocab_global, temperature=temperature, top_k=top_k, top_p=top_p,
-                              min_p=min_p, seeds=seeds, draw_index=draw_index, seed_base=seed_base, trace=trace)
+    packed = sampler.shard_select_packed(local_logits, column_offset=column_offset, vocab_global=vocab_global,
+                                         cand_stride=stride, temperature=temperature, top_k=top_k,
+                                         repetition_penalty=repetition_penalty, history=history)
+    gathered = all_gather_packed(packed, group=group)
+    return sampler.merge_draw_packed(gathered, batch=int(local_logits.shape[0]), cand_stride=stride,
+                                     vocab_global=vocab_global, temperature=temperature, top_k=top_k, top_p=top_p,
+                                     min_p=min_p, seeds=seeds, draw_index=draw_index, seed_base=seed_base, trace=trace)

@@ -71,3 +71,53 @@ def test_product_package_never_touches_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h", ".hpp")):
                 text = open(os.path.join(dirpath, f)).read()
                 assert "import oracle" not in text and "from oracle" not in text and "liboracle" not in text, f
+
+
+def test_cpp_header_compiles_against_the_library(tmp_path):
+    """include/llm_cuda.hpp is a header-only C++ layer over the C ABI: it must compile with g++ and
+    link against libllm_cuda.so (the GPU suite also runs the program)."""
+    import subprocess
+    from scriptonait_b200 import native
+    native.load()
+    src = tmp_path / "hpp_link.cpp"
+    src.write_text('#include "llm_cuda.hpp"\n'
+                   'int main(int argc, char**) {\n'
+                   '    llm_cuda::SamplingConfig cfg;\n'
+                   '    auto rng = llm_cuda::Rng::seed_from_u64(1234);\n'
+                   '    if (argc > 100) { llm_cuda::Sampler s; return (int)s.sample({1.f, 2.f}, cfg.temperature, rng); }\n'
+                   '    return (rng.next_u64() == 0xbb0cf61b2f181cdbull && cfg.top_k == 40) ? 0 : 1;\n'
+                   '}\n')
+    exe = tmp_path / "hpp_link"
+    libdir = os.path.dirname(native.library_path())
+    subprocess.run(["g++", "-std=c++17", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe),
+                    "-L", libdir, "-lllm_cuda", f"-Wl,-rpath,{libdir}"], check=True)
+    assert subprocess.run([str(exe)]).returncode == 0  # SplitMix64's first output for seed 1234 (rng.rs:16-22)
+
+
+def test_static_entry_point_rejects_bad_arguments_before_touching_a_device():
+    """The allocation-free entry point makes the handle-based entry point's argument checks: a logits
+    pointer that is not element aligned, a NaN penalty or an impossible history come back as
+    LLM_CUDA_ERR_BAD_ARGUMENT, with nothing launched (this runs without a GPU)."""
+    from scriptonait_b200 import native as N
+    lib = N.load()
+    tokens = (ctypes.c_uint32 * 4)()
+
+    def args(**kw):
+        a = N.SampleArgs()
+        a.struct_size = ctypes.sizeof(N.SampleArgs)
+        a.logits_dtype = N.DTYPE_F32
+        a.logits = 0x10000
+        a.batch, a.vocab, a.row_stride_elems = 4, 1000, 1000
+        a.temperature, a.top_k, a.top_p, a.repetition_penalty = 1.0, 8, 1.0, 1.0
+        a.tokens = ctypes.addressof(tokens)
+        for k, v in kw.items():
+            setattr(a, k, v)
+        return a
+
+    for bad, text in [(args(logits=0x10002), b"aligned"), (args(logits=0x10001, logits_dtype=N.DTYPE_BF16), b"aligned"),
+                      (args(repetition_penalty=float("nan")), b"NaN"), (args(temperature=float("nan")), b"NaN"),
+                      (args(history=0x20000, history_stride=4, history_len=9), b"history_len"),
+                      (args(row_stride_elems=10), b"row_stride"), (args(struct_size=8), b"struct_size"),
+                      (args(logits_dtype=7), b"dtype"), (args(vocab=0), b"vocab")]:
+        assert lib.llm_cuda_sample_batch_static(0, ctypes.byref(bad)) == N.ERR_BAD_ARGUMENT
+        assert text in lib.llm_cuda_static_last_error(), lib.llm_cuda_static_last_error()

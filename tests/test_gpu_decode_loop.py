@@ -19,7 +19,7 @@ def test_batched_decode_loop_matches_a_host_loop_of_sample_with(sampler):
     prompt = g.integers(0, V, size=(B, 5), dtype=np.uint32)
     cfg = oracle.SamplingConfig(temperature=0.9, top_k=20, top_p=0.95, min_p=0.0, repetition_penalty=1.3)
     # host reference loop
-    expect = []
+    expect, expect_recent = [], []
     for r in range(B):
         rng = oracle.Rng(1000 + r)
         toks = list(prompt[r])
@@ -32,6 +32,7 @@ def test_batched_decode_loop_matches_a_host_loop_of_sample_with(sampler):
             toks.append(nxt)
             out.append(nxt)
         expect.append(out)
+        expect_recent.append(sorted(int(x) for x in toks[-window:]))  # recent_tokens (generate.rs:176-182)
     # device loop
     dev = "cuda:0"
     hist = torch.zeros((B, window), dtype=torch.int32, device=dev)
@@ -56,3 +57,20 @@ def test_batched_decode_loop_matches_a_host_loop_of_sample_with(sampler):
                 continue
             got[r].append(None if nf[r] else int(tk[r]))
     assert got == expect
+    # well past the window (5 + 40 tokens through a ring of 16): the ring holds exactly the last
+    # `window` tokens of every row, the set the next step's penalty would run over
+    hl, hh = hlen.cpu().numpy(), hist.cpu().numpy().view(np.uint32)
+    assert [sorted(int(x) for x in hh[r, :hl[r]]) for r in range(B)] == expect_recent
+
+
+def test_advance_rows_needs_a_write_position_for_the_ring(sampler):
+    import torch
+    import scriptonait_b200 as sb
+    from scriptonait_b200 import native as N
+    dev = "cuda:0"
+    tokens = torch.zeros(4, dtype=torch.int32, device=dev)
+    hist = torch.zeros((4, 8), dtype=torch.int32, device=dev)
+    hlen = torch.zeros(4, dtype=torch.int32, device=dev)
+    with pytest.raises(sb.LlmCudaError) as e:
+        sampler.advance_rows(tokens, None, history=hist, window=8, history_len=hlen, history_pos=None)
+    assert e.value.code == N.ERR_BAD_ARGUMENT

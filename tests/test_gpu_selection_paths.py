@@ -80,3 +80,44 @@ def test_bf16_rows_with_penalty_and_small_rank_cut(sampler):
     x = narrow_bf16(g.normal(0.0, 2.0, (5, V)).astype(np.float32))
     hist = g.integers(0, V, size=(5, 300), dtype=np.uint32)
     _check(sampler, _wl(x, temperature=0.7, top_k=50, top_p=0.9, min_p=0.02, repetition_penalty=1.15, history=hist))
+
+
+def _quotient_tie(T):
+    """A float x_k in [1, 2) whose lower neighbour rounds to the same quotient x / T (generate.rs:357-359)."""
+    T = np.float32(T)
+    for start in np.linspace(1.0, 2.0, 64, endpoint=False, dtype=np.float32):
+        x = np.float32(start)
+        for _ in range(64):
+            below = np.nextafter(x, np.float32(-np.inf))
+            if np.float32(x / T) == np.float32(below / T):
+                return x, below
+            x = np.nextafter(x, np.float32(np.inf))
+    raise AssertionError("no pair of neighbouring floats with equal quotient found")
+
+
+@pytest.mark.parametrize("T", [1.5, 0.7])
+@pytest.mark.parametrize("top_k,V", [(256, 1024), (8, 32), (64, 256)])
+def test_quotient_tie_below_a_tight_bound_keeps_the_lower_index(sampler, T, top_k, V):
+    """The rank cut works on x / T, ties go to the lower index (generate.rs:364-370). The row
+    makes the running bound tight: exactly top_k large values, one per 16-byte vector, the
+    smallest of them (x_k) at a high index. A value one float below x_k with the same
+    quotient sits at a lower index: the reference's top_k contains it and drops x_k."""
+    x_k, below = _quotient_tie(T)
+    rows = []
+    for variant in range(3):
+        g = np.random.default_rng(100 + variant)
+        x = np.full(V, -30.0, np.float32) + g.normal(0, 0.01, V).astype(np.float32)
+        slots = np.arange(top_k) * 4 + g.integers(0, 4, top_k)       # one large value per vector of four
+        large = (np.float32(2.0) + g.random(top_k).astype(np.float32)).astype(np.float32)
+        x[slots] = large
+        x[slots[-1]] = x_k                                           # the k-th value, at a high index
+        low = slots[variant] + (1 if slots[variant] % 4 != 3 else -1)  # a small slot inside an early vector
+        x[low] = below
+        rows.append(x)
+    x = np.stack(rows)
+    w = _wl(x, temperature=T, top_k=top_k, top_p=1.0)
+    ref = parity.run_oracle(w, oracle.EXP_CR, kept_capacity=top_k)
+    for r in range(3):  # the construction does what it says: the lower-index twin is kept, x_k is not
+        kept = set(ref.kept_ids[r, :ref.kept_count[r]].tolist())
+        assert int(np.flatnonzero(x[r] == below)[0]) in kept and int(np.flatnonzero(x[r] == x_k)[0]) not in kept
+    _check(sampler, w, kept_capacity=top_k)

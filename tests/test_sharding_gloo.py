@@ -56,16 +56,16 @@ def _row_worker(rank, world, port, q):
     dist.destroy_process_group()
 
 
-def _vocab_worker(rank, world, port, q):
+def _vocab_worker(rank, world, port, q, V=1000):
     import torch
     import torch.distributed as dist
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     g = np.random.default_rng(5)
-    B, V, K = 5, 1000, 16
+    B, K = 5, 16
     x = g.normal(0, 2, (B, V)).astype(np.float32)
-    lo, hi = sharding.vocab_shard_ranges(V, world)[rank]
+    lo, hi = sharding.vocab_shard_ranges(V, world)[rank]   # may be empty: a tiny vocabulary leaves trailing ranks without columns
     vals = np.full((B, K), -np.inf, np.float32)
     ids = np.zeros((B, K), np.int32)
     cnt = np.zeros(B, np.int32)
@@ -74,8 +74,12 @@ def _vocab_worker(rank, world, port, q):
         vals[b, :len(order)] = x[b, order]
         ids[b, :len(order)] = order
         cnt[b] = len(order)
-    gv, gi, gc = sharding.all_gather_candidates(torch.from_numpy(vals), torch.from_numpy(ids), torch.from_numpy(cnt))
-    assert tuple(gv.shape) == (world, B, K) and tuple(gc.shape) == (world, B)
+    # one packed block per rank (values, ids, counts), one all-gather
+    packed = torch.from_numpy(np.concatenate([vals.view(np.int32).ravel(), ids.ravel(), cnt]))
+    assert packed.numel() == sharding.packed_words(B, K)
+    gathered = sharding.all_gather_packed(packed)
+    gv, gi, gc = sharding.unpack_candidates(gathered, B, K)
+    assert tuple(gv.shape) == (world, B, K) and tuple(gi.shape) == (world, B, K) and tuple(gc.shape) == (world, B)
     merged = []
     for b in range(B):
         cand = [(float(gv[s, b, i]), int(gi[s, b, i])) for s in range(world) for i in range(int(gc[s, b]))]
@@ -83,6 +87,10 @@ def _vocab_worker(rank, world, port, q):
         merged.append([i for _, i in cand[:K]])
     q.put((rank, merged))
     dist.destroy_process_group()
+
+
+def _tiny_vocab_worker(rank, world, port, q):
+    _vocab_worker(rank, world, port, q, V=40)   # align 64: rank 1's shard is empty
 
 
 def _spawn(worker, world=2):
@@ -117,3 +125,16 @@ def test_vocab_sharded_candidate_merge_equals_global_top_k_world_size_2():
         tr = oracle.sample_with(x[b], oracle.SamplingConfig(temperature=1.0, top_k=16, top_p=1.0, repetition_penalty=1.0),
                                 [], oracle.Rng(0), trace=True)
         assert out[0][b] == out[1][b] == list(tr.kept_ids)
+
+
+@pytest.mark.timeout(300)
+def test_empty_shard_still_reaches_the_exchange_world_size_2():
+    """Vocabulary 40 over 2 ranks with 64-column alignment: rank 1 owns no columns, contributes empty
+    lists, and both ranks still complete the all-gather with the global top-k."""
+    assert sharding.vocab_shard_ranges(40, 2)[1] == (40, 40)
+    out = _spawn(_tiny_vocab_worker)
+    g = np.random.default_rng(5)
+    x = g.normal(0, 2, (5, 40)).astype(np.float32)
+    for b in range(5):
+        want = sorted(range(40), key=lambda i: (-float(x[b, i]), i))[:16]
+        assert out[0][b] == out[1][b] == want
