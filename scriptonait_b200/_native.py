@@ -77,26 +77,26 @@ class SampleArgs(C.Structure):
     ]
 
 
-_lib = None
+_libs: dict = {}
 
 
 def library_path() -> str:
     return _build.LIBRARY
 
 
-def load() -> C.CDLL:
-    """Builds (when stale and nvcc is present) and loads the CUDA library. Raises if it
-    cannot be produced or loaded; nothing else can stand in for it."""
-    global _lib
-    if _lib is not None:
-        return _lib
-    path = _build.LIBRARY
-    if _build.is_stale():
+def load(checked: bool = False) -> C.CDLL:
+    """Builds (when stale and nvcc is present) and loads the CUDA library - the product build, or with
+    `checked` the bounds-checked build of the same sources. Raises if it cannot be produced or loaded;
+    nothing else can stand in for it."""
+    if checked in _libs:
+        return _libs[checked]
+    path = _build.CHECKED_LIBRARY if checked else _build.LIBRARY
+    if _build.is_stale(path):
         try:
-            _build.build()
+            _build.build(checked=checked)
         except Exception as exc:  # keep a prebuilt library if the toolchain is missing
             if not os.path.exists(path):
-                raise RuntimeError(f"libllm_cuda.so is missing and could not be built: {exc}") from exc
+                raise RuntimeError(f"{os.path.basename(path)} is missing and could not be built: {exc}") from exc
     L = C.CDLL(path)
     vp, u32, i32 = C.c_void_p, C.c_uint32, C.c_int32
     L.llm_cuda_abi_version.restype = u32
@@ -144,5 +144,5 @@ def load() -> C.CDLL:
     L.llm_cuda_static_last_error.argtypes = []
     if L.llm_cuda_abi_version() != ABI_VERSION:
         raise RuntimeError("libllm_cuda.so ABI version mismatch")
-    _lib = L
+    _libs[checked] = L
     return L

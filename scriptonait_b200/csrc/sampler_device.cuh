@@ -33,6 +33,16 @@ __device__ __forceinline__ unsigned long long global_ns() {
 #define PHASE(slot) do { } while (0)
 #endif
 
+// Checked builds (-DLLM_CUDA_CHECKED, a second library the tests run the small and odd shapes against): every
+// store at a computed offset into the kernels' shared-memory regions or into scratch is compared with
+// the region's size first. An offset out of bounds sets LLM_CUDA_STATUS_CHECK_FAILED in the device status
+// word and the store is skipped - nothing traps. The product build compiles the test away.
+#ifdef LLM_CUDA_CHECKED
+#define IN_BOUNDS(idx, bound) llmc::in_bounds_or_report(P, (uint32_t)(idx), (uint32_t)(bound))
+#else
+#define IN_BOUNDS(idx, bound) true
+#endif
+
 constexpr int THREADS = 256;             // threads per CTA of the streaming kernel
 constexpr int WARPS = THREADS / 32;
 constexpr uint32_t STAGE_BYTES = 12288;  // one ring stage = one tile: the logits consumed between two capacity checks
@@ -70,6 +80,14 @@ __device__ __forceinline__ int cta_sync_or(int pred) {
         : "memory");
     return r;
 }
+
+#ifdef LLM_CUDA_CHECKED
+__device__ __forceinline__ bool in_bounds_or_report(const KParams& P, uint32_t idx, uint32_t bound) {
+    if (idx < bound) return true;
+    if (P.device_errors) atomicOr(P.device_errors, LLM_CUDA_STATUS_CHECK_FAILED);
+    return false;
+}
+#endif
 
 struct RowCfg {
     float T, top_p, min_p, pen;

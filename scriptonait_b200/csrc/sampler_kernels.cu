@@ -505,6 +505,7 @@ __device__ __noinline__ uint32_t build_window_keys(const KParams& P, uint32_t b,
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             if (in[e]) {
+                if (!IN_BOUNDS(off + pos[e], P.full_vpad)) continue;
                 __stcg(&sk[off + pos[e]], key[e]);
                 __stcg(&si[off + pos[e]], chunk + warp * 128u + (uint32_t)e * 32u + lane);
             }
@@ -521,7 +522,7 @@ __device__ __noinline__ uint32_t build_window_keys(const KParams& P, uint32_t b,
 // column order; a key's place is its digit's base + the same-digit keys of earlier warps + those
 // earlier in its own warp (`match_any` finds the lanes that share a digit).
 // Sorts n_all (key, column) pairs; the pointers are exchanged so that sk / si hold the result.
-__device__ __noinline__ void radix_sort_row(uint32_t n_all, uint32_t*& sk_io, uint32_t*& si_io, uint32_t*& dk_io, uint32_t*& di_io,
+__device__ __noinline__ void radix_sort_row(const KParams& P, uint32_t n_all, uint32_t*& sk_io, uint32_t*& si_io, uint32_t*& dk_io, uint32_t*& di_io,
                                             uint32_t* work) {
     const uint32_t tid = threadIdx.x;
     const unsigned lane = tid & 31u, warp = tid >> 5;
@@ -592,6 +593,7 @@ __device__ __noinline__ void radix_sort_row(uint32_t n_all, uint32_t*& sk_io, ui
                 if (d[e] < 256u) {
                     uint32_t off = base[d[e]] + rank[e];
                     for (uint32_t w = 0; w < warp; ++w) off += wrun[w * 256u + d[e]];
+                    if (!IN_BOUNDS(off, n_all)) continue;
                     __stcg(&dk[off], k[e]);
                     __stcg(&di[off], id[e]);
                 }
@@ -710,7 +712,7 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
     }
     if (myvalid) atomicAdd(&F.nvalid, myvalid);
     cta_sync();
-    radix_sort_row(n_all, sk, si, dk, di, work);
+    radix_sort_row(P, n_all, sk, si, dk, di, work);
     const uint32_t n = min(F.nvalid, rc.k_eff);
     // window attempt: the reference's ordering continues past these n entries with values outside the
     // significance window; what that leaves undecided is handled as in the shared-memory path
@@ -1097,7 +1099,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
                 if (id >= gid0 && id - gid0 < ncols) {  // ids outside the vocabulary are skipped (generate.rs:345)
                     hash_insert(hkeys, hcnt, P.hash_slots, id);
                     const uint32_t j2 = id - gid0 + lead;
-                    atomicOr(&bitmap[j2 >> 5], 1u << (j2 & 31u));
+                    if (IN_BOUNDS(j2 >> 5, P.bitmap_words)) atomicOr(&bitmap[j2 >> 5], 1u << (j2 & 31u));
                 }
             };
 #pragma unroll
@@ -1124,7 +1126,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
                             valid |= 1u << jb;
                     }
                     blocked &= valid;
-                    if (blocked) atomicOr(&bitmap[w], blocked);
+                    if (blocked && IN_BOUNDS(w, P.bitmap_words)) atomicOr(&bitmap[w], blocked);
                 }
             }
         }
@@ -1221,13 +1223,14 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
     auto lowered = [&](uint32_t key) { return key > LOWEST + tau_slack ? key - tau_slack : LOWEST; };
     float lmin = neg_inf();   // m_lane > 1: the lane's m-th best so far
     if (m_lane > 1u)
-        for (uint32_t i = 0; i < m_lane; ++i) lane_top[i * THREADS + tid] = neg_inf();
+        for (uint32_t i = 0; i < m_lane; ++i)
+            if (IN_BOUNDS(i * THREADS + tid, P.lane_top_words)) lane_top[i * THREADS + tid] = neg_inf();
     // the lane's m best, descending, in lane_top[i*THREADS + tid]; returns the new m-th best
     auto lane_insert = [&](float v) {
         for (uint32_t i = 0; i < m_lane; ++i) {
             const float cur = lane_top[i * THREADS + tid];
             if (v > cur) {
-                lane_top[i * THREADS + tid] = v;
+                if (IN_BOUNDS(i * THREADS + tid, P.lane_top_words)) lane_top[i * THREADS + tid] = v;
                 v = cur;
             }
         }
@@ -1320,7 +1323,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const unsigned gm = __ballot_sync(FULL_MASK, vm[u] >= tau_run);
-            if (lane == 0) grp_max[(t * U + u) * WARPS + warp] = gm;
+            if (lane == 0 && IN_BOUNDS((t * U + u) * WARPS + warp, P.groups)) grp_max[(t * U + u) * WARPS + warp] = gm;
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty_bar[stage]);  // this warp is done with the stage
@@ -1578,6 +1581,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
         uint32_t* si = P.sc_i + at * P.sc_stride;
         if (!overflow) {
             for (uint32_t i = tid; i < n; i += THREADS) {
+                if (!IN_BOUNDS(i, P.sc_stride)) continue;
                 __stcg(&sq[i], cand_q[i]);
                 __stcg(&si[i], cand_i[i]);
             }
@@ -1821,6 +1825,7 @@ void apply_plan(const LaunchPlan& plan, KParams* P) {
     P->limit = plan.limit;
     P->hash_slots = plan.hash_slots;
     P->bitmap_words = plan.bitmap_words;
+    P->groups = plan.groups;
     P->lane_top_words = plan.lane_top_words;
     P->cand_off = plan.cand_off;
     P->scratch_off = plan.scratch_off;

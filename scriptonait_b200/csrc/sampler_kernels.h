@@ -47,7 +47,7 @@ struct KParams {
     // launch geometry
     uint32_t split, shard_cols;
     uint32_t kcap, ccap, limit;     // kcap: exact-selection capacity; ccap: buffer entries; limit: compaction trigger
-    uint32_t hash_slots, bitmap_words;
+    uint32_t hash_slots, bitmap_words, groups;   // groups: flag words (one per 32 vectors) the layout holds
     uint32_t cand_off, scratch_off, tables_off;  // byte offsets into the kernel's dynamic shared memory
     uint32_t vlist_cap;             // flagged vectors the revisit list can hold
     uint32_t lane_top_words;        // floats of shared memory for the lanes' best values (rank cuts above 256), else 0

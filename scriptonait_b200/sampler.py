@@ -105,8 +105,9 @@ class Sampler:
     """Owns one llm_cuda_sampler handle (one GPU, one stream at a time)."""
 
     def __init__(self, device: int = 0, max_batch: int = 1024, max_vocab: int = 262144, max_history: int = 1024,
-                 max_top_k: int = 1024):
-        self._lib = N.load()
+                 max_top_k: int = 1024, checked: bool = False):
+        """`checked`: use the bounds-checked build of the library (slower; for tests)."""
+        self._lib = N.load(checked)
         self._h = C.c_void_p()
         self.device = device
         self.max_batch, self.max_vocab, self.max_history, self.max_top_k = max_batch, max_vocab, max_history, max_top_k
