@@ -228,6 +228,49 @@ int32_t llm_cuda_shard_select_packed(llm_cuda_sampler* s, const llm_cuda_sample_
 int32_t llm_cuda_merge_draw_packed(llm_cuda_sampler* s, const llm_cuda_sample_args* args, const void* packed_all,
                                    uint32_t n_shards, uint32_t cand_stride);
 
+/* Fused tied LM head -> sampler for a decode batch: final RMSNorm, the hidden x vocab contraction over the
+ * tied embedding on the tensor cores, and sampling, without ever writing the [batch, vocab] logits.
+ * Replaces the last three dispatches of GpuModel::decode_step (crates/llm-gpu/src/model.rs:481-490:
+ * dispatch_rmsnorm, dispatch_linear over self.embed, the vocab*4-byte copy + read_back), the linear kernel
+ * crates/llm-gpu/src/shaders/linear.wgsl and the sample_with call on the host that follows
+ * (crates/wasm-app/src/inference.rs:325-347). The hidden states are narrowed to bf16 after the norm and the
+ * products accumulate in f32 on the tensor cores, so the logits differ from the reference's f32 contraction
+ * by bf16 input rounding; given those logits every sampler stage is exact (logits_out exposes them).
+ * Limits: batch <= 256, hidden_dim a multiple of 8, 0 < top_k <= 256 or greedy; no repetition penalty and
+ * no allowed mask on this path (use llm_cuda_sample_batch on materialised logits for those). A row whose
+ * threshold estimate left fewer than top_k candidates, or more than the 2048 a list holds, is reported
+ * with LLM_CUDA_ROW_INVALID (token 0), not guessed. */
+typedef struct llm_cuda_lm_head_args {
+    uint32_t struct_size;        /* = sizeof(llm_cuda_lm_head_args) */
+    uint32_t batch;              /* rows of `hidden` (decode batch), <= 256 */
+    const float* hidden;         /* device [batch, hidden_dim] f32: the last layer's output, before the final norm */
+    const float* norm_gain;      /* device [hidden_dim] final RMSNorm gain, or NULL when `hidden` is already normalised */
+    float norm_eps;
+    uint32_t hidden_dim;
+    const void* embed;           /* device [vocab, hidden_dim] bf16, row-major: the tied embedding / LM head weight */
+    uint32_t vocab;
+    float temperature;           /* <= 0: greedy */
+    uint32_t top_k;
+    float top_p;
+    float min_p;
+    uint32_t reserved0;
+    const uint64_t* seeds;       /* as in llm_cuda_sample_args */
+    const uint64_t* draw_index;
+    uint64_t seed_base;
+    const float* uniforms;
+    uint32_t* tokens;            /* device [batch], out */
+    uint32_t* row_flags;         /* optional per-stage outputs, as in llm_cuda_sample_args */
+    uint32_t* kept_count;
+    uint32_t* kept_ids;
+    float* kept_probs;
+    uint32_t kept_capacity;
+    uint32_t reserved1;
+    float* row_stats;
+    float* logits_out;           /* optional device [batch, vocab] f32, testing aid: also write the logits themselves */
+    void* stream;
+} llm_cuda_lm_head_args;
+int32_t llm_cuda_lm_head_sample(llm_cuda_sampler* s, const llm_cuda_lm_head_args* args);
+
 /* Device-side decode-loop glue (Generator::step / recent_tokens,
  * crates/llm-core/src/generate.rs:157-182; the EOS test of
  * crates/wasm-app/src/inference.rs:326-333): for each row that is not finished,

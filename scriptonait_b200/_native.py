@@ -43,7 +43,7 @@ EXPORTS = [
     "llm_cuda_sample", "llm_cuda_shard_select", "llm_cuda_merge_draw", "llm_cuda_advance_rows",
     "llm_cuda_pack_allowed", "llm_cuda_last_launch_info", "llm_cuda_sample_batch_static", "llm_cuda_static_last_error",
     "llm_cuda_device_status", "llm_cuda_test_hold_full_sort_slots", "llm_cuda_packed_candidates_bytes",
-    "llm_cuda_shard_select_packed", "llm_cuda_merge_draw_packed",
+    "llm_cuda_shard_select_packed", "llm_cuda_merge_draw_packed", "llm_cuda_lm_head_sample",
 ]
 STATIC_MAX_BATCH, STATIC_MAX_TOP_K, STATIC_MAX_HISTORY = 64, 256, 512
 
@@ -74,6 +74,18 @@ class SampleArgs(C.Structure):
         ("column_offset", C.c_uint32), ("vocab_global", C.c_uint32),
         ("split", C.c_uint32), ("force_full_sort", C.c_uint32), ("stream", C.c_void_p),
         ("penalized_out", C.c_void_p),
+    ]
+
+
+class LmHeadArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32), ("batch", C.c_uint32), ("hidden", C.c_void_p), ("norm_gain", C.c_void_p),
+        ("norm_eps", C.c_float), ("hidden_dim", C.c_uint32), ("embed", C.c_void_p), ("vocab", C.c_uint32),
+        ("temperature", C.c_float), ("top_k", C.c_uint32), ("top_p", C.c_float), ("min_p", C.c_float),
+        ("reserved0", C.c_uint32), ("seeds", C.c_void_p), ("draw_index", C.c_void_p), ("seed_base", C.c_uint64),
+        ("uniforms", C.c_void_p), ("tokens", C.c_void_p), ("row_flags", C.c_void_p), ("kept_count", C.c_void_p),
+        ("kept_ids", C.c_void_p), ("kept_probs", C.c_void_p), ("kept_capacity", C.c_uint32), ("reserved1", C.c_uint32),
+        ("row_stats", C.c_void_p), ("logits_out", C.c_void_p), ("stream", C.c_void_p),
     ]
 
 
@@ -134,6 +146,8 @@ def load(checked: bool = False) -> C.CDLL:
     L.llm_cuda_shard_select_packed.argtypes = [vp, C.POINTER(SampleArgs), vp, u32]
     L.llm_cuda_merge_draw_packed.restype = i32
     L.llm_cuda_merge_draw_packed.argtypes = [vp, C.POINTER(SampleArgs), vp, u32, u32]
+    L.llm_cuda_lm_head_sample.restype = i32
+    L.llm_cuda_lm_head_sample.argtypes = [vp, C.POINTER(LmHeadArgs)]
     L.llm_cuda_device_status.restype = i32
     L.llm_cuda_device_status.argtypes = [vp, vp, C.POINTER(u32)]
     L.llm_cuda_test_hold_full_sort_slots.restype = i32

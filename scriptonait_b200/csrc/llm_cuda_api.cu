@@ -13,6 +13,7 @@
 
 #include "../../include/llm_cuda.h"
 #include "sampler_kernels.h"
+#include "lm_head.h"
 
 using namespace llmc;
 
@@ -21,6 +22,8 @@ namespace {
 constexpr uint32_t kMaxKcap = 2048;           // must match MAX_KCAP
 constexpr uint64_t kScratchEntries = 1u << 22;  // candidate entries shared by the CTAs of split rows (32 MiB)
 constexpr uint64_t kGamma = 0x9E3779B97F4A7C15ull;
+constexpr uint32_t kLmCandCap = 2048;   // candidates per row the fused LM head keeps
+constexpr uint32_t kLmProbeEvery = 8;   // one vocabulary tile in eight is probed for the thresholds
 constexpr uint32_t kSlotRounds = 1u << 16;  // a quarter of a second of polling: thousands of rows can queue for the slots of a launch
 
 char g_create_error[512] = "";
@@ -87,6 +90,15 @@ struct llm_cuda_sampler {
 #ifdef LLMC_DEV
     unsigned long long* phase_ns = nullptr;  // development builds only: per-CTA phase timestamps
 #endif
+    // scratch of the fused LM head path (allocated on its first use, grown on demand)
+    void* lm_xnorm = nullptr;       // [n_pad, hidden] bf16
+    float* lm_probe = nullptr;      // [batch, probe_cols]
+    float* lm_thr = nullptr;        // [256]
+    float* lm_cand_q = nullptr;     // [256, kLmCandCap]
+    uint32_t* lm_cand_i = nullptr;
+    uint32_t* lm_cand_count = nullptr;
+    size_t lm_xnorm_bytes = 0, lm_probe_bytes = 0;
+    bool lm_configured = false;
     // staging for the host-buffer entry points (grown on demand)
     unsigned char* arena = nullptr;
     size_t arena_bytes = 0;
@@ -120,6 +132,12 @@ void free_all(llm_cuda_sampler* s) {
     cudaFree(s->full_keys);
     cudaFree(s->full_vals);
     cudaFree(s->device_errors);
+    cudaFree(s->lm_xnorm);
+    cudaFree(s->lm_probe);
+    cudaFree(s->lm_thr);
+    cudaFree(s->lm_cand_q);
+    cudaFree(s->lm_cand_i);
+    cudaFree(s->lm_cand_count);
     cudaFree(s->arena);
 }
 
@@ -187,8 +205,8 @@ int32_t fill_params(llm_cuda_sampler* s, const llm_cuda_sample_args* a, bool nee
 
 bool scalar_greedy(const llm_cuda_sample_args* a) { return a->temperature_rows == nullptr && a->temperature <= 0.0f; }
 
-// Runs the streaming kernel (and the full-sort kernel behind it when a row may need it).
-int32_t run_select(llm_cuda_sampler* s, const llm_cuda_sample_args* a, KParams& P, bool lists_out) {
+// Plans and launches the streaming kernel (rows it cannot decide are ordered in full by their own CTA).
+int32_t run_select(llm_cuda_sampler* s, const llm_cuda_sample_args* a, KParams& P) {
     LaunchPlan plan{};
     const bool k_known = (a->top_k_rows == nullptr);
     const uint32_t k_hint = scalar_greedy(a) ? 1u : a->top_k;
@@ -224,7 +242,6 @@ int32_t run_select(llm_cuda_sampler* s, const llm_cuda_sample_args* a, KParams& 
     P.full_slots = s->full_slots;
     P.full_vpad = s->vpad;
     P.full_nslots = s->nslots;
-    (void)lists_out;
     CUDA_TRY(s, launch_stream_select(P, plan, stream, a->overlap_previous != 0u));
     s->last_kernels++;
     return LLM_CUDA_OK;
@@ -382,7 +399,7 @@ int32_t llm_cuda_sample_batch(llm_cuda_sampler* s, const llm_cuda_sample_args* a
     if (a->column_offset != 0 || (a->vocab_global != 0 && a->vocab_global != a->vocab))
         return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "column_offset/vocab_global are for llm_cuda_shard_select");
     CUDA_TRY(s, cudaSetDevice(s->device));
-    return run_select(s, a, P, false);
+    return run_select(s, a, P);
 }
 
 int32_t llm_cuda_shard_select(llm_cuda_sampler* s, const llm_cuda_sample_args* a, float* cand_values, uint32_t* cand_ids,
@@ -416,7 +433,7 @@ int32_t llm_cuda_shard_select(llm_cuda_sampler* s, const llm_cuda_sample_args* a
     P.out_stride = cand_stride;
     P.force_full = 0;
     CUDA_TRY(s, cudaSetDevice(s->device));
-    return run_select(s, a, P, true);
+    return run_select(s, a, P);
 }
 
 namespace {
@@ -424,7 +441,7 @@ namespace {
 // The merge step over lists laid out as the two public forms describe.
 int32_t run_merge(llm_cuda_sampler* s, const llm_cuda_sample_args* a, const float* cand_values, const uint32_t* cand_ids,
                   const uint32_t* cand_count, uint32_t n_shards, uint32_t cand_stride, uint64_t shard_words,
-                  uint64_t cnt_shard) {
+                  uint64_t cnt_shard, bool lists_sorted = true) {
     KParams P;
     int32_t rc = fill_params(s, a, false, &P);
     if (rc != LLM_CUDA_OK) return rc;
@@ -457,6 +474,7 @@ int32_t run_merge(llm_cuda_sampler* s, const llm_cuda_sample_args* a, const floa
     P.sc_rows = a->batch;
     P.sc_shard_words = (uint32_t)shard_words;
     P.sc_cnt_shard = (uint32_t)cnt_shard;
+    P.sc_sorted = lists_sorted ? 1u : 0u;
     P.force_full = 0;
     s->last_kernels = 0;
     s->last_split = n_shards;
@@ -498,6 +516,134 @@ int32_t llm_cuda_merge_draw_packed(llm_cuda_sampler* s, const llm_cuda_sample_ar
     const uint32_t* ids = reinterpret_cast<const uint32_t*>(values) + B * cand_stride;
     const uint32_t* counts = ids + B * cand_stride;
     return run_merge(s, a, values, ids, counts, n_shards, cand_stride, block, block);
+}
+
+int32_t llm_cuda_lm_head_sample(llm_cuda_sampler* s, const llm_cuda_lm_head_args* a) {
+    if (!s) return fail(nullptr, LLM_CUDA_ERR_BAD_ARGUMENT, "sampler handle is NULL");
+    if (!a) return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "args is NULL");
+    if (a->struct_size != sizeof(llm_cuda_lm_head_args))
+        return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "struct_size %u, expected %zu", a->struct_size, sizeof(llm_cuda_lm_head_args));
+    if (a->batch == 0) return LLM_CUDA_OK;
+    if (!a->hidden || !a->embed || !a->tokens) return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "hidden, embed or tokens is NULL");
+    if (a->batch > 256u || a->batch > s->max_batch)
+        return fail(s, LLM_CUDA_ERR_CAPACITY, "batch %u beyond 256 (one tensor-core tile) or the handle's max_batch", a->batch);
+    if (a->vocab == 0 || a->hidden_dim == 0 || a->hidden_dim % 8u)
+        return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "vocab and hidden_dim must be > 0 and hidden_dim a multiple of 8 (16-byte rows for TMA)");
+    if ((reinterpret_cast<uintptr_t>(a->embed) & 15u) || (reinterpret_cast<uintptr_t>(a->hidden) & 3u))
+        return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "embed must be 16-byte aligned and hidden 4-byte aligned");
+    if (a->temperature != a->temperature) return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "temperature is NaN");
+    const bool greedy = a->temperature <= 0.0f;
+    if (!greedy && (a->top_k == 0 || a->top_k > 256u))
+        return fail(s, LLM_CUDA_ERR_UNSUPPORTED, "the fused LM head samples rows with 0 < top_k <= 256 (or greedy); top_k %u needs the logits and llm_cuda_sample_batch", a->top_k);
+    if ((a->kept_ids || a->kept_probs) && a->kept_capacity == 0)
+        return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "kept_ids/kept_probs given with kept_capacity 0");
+    CUDA_TRY(s, cudaSetDevice(s->device));
+    cudaStream_t st = static_cast<cudaStream_t>(a->stream);
+    const uint32_t B = a->batch, V = a->vocab, H = a->hidden_dim;
+    const uint32_t n_pad = (B + 15u) & ~15u;
+    const uint32_t k = greedy ? 1u : a->top_k;
+    const uint32_t n_tiles = (V + 127u) / 128u;
+    // small vocabularies are probed whole: the thresholds are then exact and the main step has nothing to do
+    const uint32_t probe_every = n_tiles >= 64u ? kLmProbeEvery : 1u;
+    const uint32_t n_probe = (n_tiles + probe_every - 1u) / probe_every;
+    const uint32_t probe_cols = n_probe * 128u;
+    if (!s->lm_configured) {
+        CUDA_TRY(s, lm_head_configure(s->dev.max_dyn_smem));
+        CUDA_TRY(s, cudaMalloc(&s->lm_thr, 256u * 4u));
+        CUDA_TRY(s, cudaMalloc(&s->lm_cand_q, (size_t)256u * kLmCandCap * 4u));
+        CUDA_TRY(s, cudaMalloc(&s->lm_cand_i, (size_t)256u * kLmCandCap * 4u));
+        CUDA_TRY(s, cudaMalloc(&s->lm_cand_count, 256u * 4u));
+        s->lm_configured = true;
+    }
+    const size_t xnorm_bytes = (size_t)n_pad * H * 2u, probe_bytes = (size_t)B * probe_cols * 4u;
+    if (xnorm_bytes > s->lm_xnorm_bytes || probe_bytes > s->lm_probe_bytes) {
+        CUDA_TRY(s, cudaStreamSynchronize(st));  // nothing may still be using the old buffers
+        if (xnorm_bytes > s->lm_xnorm_bytes) {
+            cudaFree(s->lm_xnorm);
+            s->lm_xnorm = nullptr;
+            s->lm_xnorm_bytes = 0;
+            CUDA_TRY(s, cudaMalloc(&s->lm_xnorm, xnorm_bytes));
+            s->lm_xnorm_bytes = xnorm_bytes;
+        }
+        if (probe_bytes > s->lm_probe_bytes) {
+            cudaFree(s->lm_probe);
+            s->lm_probe = nullptr;
+            s->lm_probe_bytes = 0;
+            CUDA_TRY(s, cudaMalloc(&s->lm_probe, probe_bytes));
+            s->lm_probe_bytes = probe_bytes;
+        }
+    }
+    if (lm_head_smem_bytes(n_pad) > s->dev.max_dyn_smem)
+        return fail(s, LLM_CUDA_ERR_CAPACITY, "shared memory for batch %u does not fit", B);
+
+    LmParams P;
+    memset(&P, 0, sizeof(P));
+    P.vocab = V;
+    P.batch = B;
+    P.n_pad = n_pad;
+    P.k_chunks = (H + 63u) / 64u;
+    P.probe_every = probe_every;
+    P.temperature = greedy ? 1.0f : a->temperature;
+    P.thr = s->lm_thr;
+    P.probe_out = s->lm_probe;
+    P.probe_cols = probe_cols;
+    P.cand_q = s->lm_cand_q;
+    P.cand_i = s->lm_cand_i;
+    P.cand_count = s->lm_cand_count;
+    P.cand_cap = kLmCandCap;
+    P.logits_out = a->logits_out;
+    P.device_errors = s->device_errors;
+
+    s->last_kernels = 0;
+    CUDA_TRY(s, launch_rmsnorm_bf16(static_cast<const float*>(a->hidden), a->norm_gain, a->norm_eps, B, n_pad, H, s->lm_xnorm, st));
+    CUDA_TRY(s, cudaMemsetAsync(s->lm_cand_count, 0, 256u * 4u, st));
+    cudaError_t ce = cudaSuccess;
+    P.phase = LM_PHASE_PROBE;
+    P.n_items = n_probe;
+    int rc = launch_lm_head(P, a->embed, s->lm_xnorm, H, s->dev.sm_count, st, &ce);
+    if (rc == -1) return fail(s, LLM_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled is unavailable or rejected the matrices");
+    if (rc != 0) return fail(s, LLM_CUDA_ERR_CUDA, "lm_head_kernel (probe): %s", cudaGetErrorString(ce));
+    // the r-th largest of a row's probed logits stands at about rank r * probe_every in the whole row: r is chosen
+    // so that this is 2-3 times top_k plus a margin; the finalize step catches the rows where it still fell short
+    uint32_t rank = probe_every == 1u ? k : 2u * ((k + probe_every - 1u) / probe_every) + 8u;
+    if (rank > probe_cols) rank = probe_cols;
+    CUDA_TRY(s, launch_probe_threshold(P, rank, st));
+    P.phase = LM_PHASE_MAIN;
+    P.n_items = n_tiles - n_probe;
+    rc = launch_lm_head(P, a->embed, s->lm_xnorm, H, s->dev.sm_count, st, &ce);
+    if (rc != 0) return fail(s, LLM_CUDA_ERR_CUDA, "lm_head_kernel (main): %s", cudaGetErrorString(ce));
+    CUDA_TRY(s, launch_finalize_counts(s->lm_cand_count, B, kLmCandCap, k < V ? k : V, st));
+
+    // the sampler's own merge + ordered tail over one unordered candidate list per row
+    llm_cuda_sample_args m;
+    memset(&m, 0, sizeof(m));
+    m.struct_size = sizeof(m);
+    m.logits_dtype = LLM_CUDA_DTYPE_F32;
+    m.batch = B;
+    m.vocab_global = V;
+    m.temperature = a->temperature;
+    m.top_k = a->top_k;
+    m.top_p = a->top_p;
+    m.min_p = a->min_p;
+    m.repetition_penalty = 1.0f;
+    m.eos_id = LLM_CUDA_EOS_DEFAULT;
+    m.seeds = a->seeds;
+    m.draw_index = a->draw_index;
+    m.seed_base = a->seed_base;
+    m.uniforms = a->uniforms;
+    m.tokens = a->tokens;
+    m.row_flags = a->row_flags;
+    m.kept_count = a->kept_count;
+    m.kept_ids = a->kept_ids;
+    m.kept_probs = a->kept_probs;
+    m.kept_capacity = a->kept_capacity;
+    m.row_stats = a->row_stats;
+    m.stream = a->stream;
+    const int32_t mr = run_merge(s, &m, s->lm_cand_q, s->lm_cand_i, s->lm_cand_count, 1u, kLmCandCap, (uint64_t)B * kLmCandCap, B,
+                                 /*lists_sorted=*/false);
+    if (mr != LLM_CUDA_OK) return mr;
+    s->last_kernels = P.n_items ? 6u : 5u;
+    return LLM_CUDA_OK;
 }
 
 int32_t llm_cuda_advance_rows(llm_cuda_sampler* s, uint32_t batch, const uint32_t* tokens, const uint32_t* row_flags,

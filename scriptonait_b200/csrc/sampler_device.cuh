@@ -45,10 +45,10 @@ __device__ __forceinline__ unsigned long long global_ns() {
 
 constexpr int THREADS = 256;             // threads per CTA of the streaming kernel
 constexpr int WARPS = THREADS / 32;
-constexpr uint32_t STAGE_BYTES = 12288;  // one ring stage = one tile: the logits consumed between two capacity checks
+constexpr uint32_t STAGE_BYTES = 12288;  // the smaller of the two ring stage sizes (12 KB / 16 KB, chosen per launch)
 constexpr int RING_STAGES = 3;           // bulk copies in flight per CTA: up to RING_STAGES stages
 constexpr uint32_t WINDOW_CAP = 2048;    // candidate buffer of launches whose rows all run in window mode
-constexpr uint32_t MAX_SORT = 4096;      // most candidates the ordered tail takes (its scratch is the 32 KB ring)
+constexpr uint32_t MAX_SORT = 4096;      // most candidates the ordered tail takes (its scratch lives in the ring's memory after the sweep)
 constexpr uint32_t EPILOGUE_SCRATCH = (uint32_t)THREADS * 8u + MAX_SORT * 4u;  // sort keys of a rank sort + probabilities
 static_assert((size_t)THREADS * 8u + (size_t)MAX_SORT * 4u <= (size_t)RING_STAGES * STAGE_BYTES, "epilogue scratch");
 constexpr unsigned FULL_MASK = 0xffffffffu;
@@ -64,7 +64,7 @@ constexpr float WINDOW_EXACT = -17.4f;
 constexpr float WINDOW_STREAM = 17.5f;
 
 // Internal row flag: the candidate window could not decide the row; the
-// full-sort kernel resolves it. Never visible to the caller.
+// row is then ordered in full by its own CTA. Never visible to the caller.
 constexpr uint32_t ROW_NEEDS_FULL = 0x80000000u;
 
 

@@ -188,7 +188,7 @@ __device__ int finish_row(const KParams& P, uint32_t b, const RowCfg& rc, uint32
     }
     // ids blocked by the allowed mask are skipped by the stream. They only matter when the ordering
     // runs out of other values (fewer unmasked values than the rank cut, or nothing finite at all):
-    // then the -inf entries belong to the kept set, and the full-sort kernel produces them.
+    // then the -inf entries belong to the kept set, and the full ordering of the row produces them.
     if (P.allowed_bits && !P.out_q && !overflow) {
         if (!rc.windowed && n < rc.k_eff) return 2;
         if (rc.windowed && qmax == neg_inf()) return 2;
@@ -343,8 +343,8 @@ __device__ uint32_t merge_lists(const KParams& P, uint32_t b, const RowCfg& rc, 
 // ---------------------------------------------------------------------------
 // The hot kernel. Grid (split, batch); one CTA streams the columns
 // [shard*shard_cols, ...) of one row through a ring of RING_STAGES shared-memory
-// stages filled by bulk copies, so RING_STAGES-1 stages (8 KB each) are always in
-// flight per CTA whatever the occupancy.
+// stages (12 KB or 16 KB each, the launch plan's choice) filled by bulk copies, so up to
+// 36 or 48 KB are in flight per CTA whatever the occupancy.
 // MODE trims the code to what a launch can need (the hot loop must stay small enough for the
 // instruction cache): 0 = rows of either kind, 1 = every row runs in window mode, 2 = no row does.
 constexpr int STREAM_THREADS = THREADS + 32;  // THREADS consumers + one warp that only issues the bulk copies
@@ -1634,8 +1634,8 @@ __global__ void __launch_bounds__(THREADS) merge_draw_kernel(const __grid_consta
     }
     bool overflow;
     float qmax;
-    // the gathered lists were written in order by finish_row on their GPUs
-    const uint32_t n = merge_lists(P, b, rc, P.split, S, cand_q, cand_i, overflow, qmax, /*all_sorted=*/true);
+    // lists gathered from other GPUs were written in order by finish_row there; the fused LM head's are not ordered
+    const uint32_t n = merge_lists(P, b, rc, P.split, S, cand_q, cand_i, overflow, qmax, /*all_sorted=*/P.sc_sorted != 0u);
     // the logits of a gathered row live on other GPUs: a row its lists cannot decide is reported
     if (finish_row(P, b, rc, n, overflow, qmax, S, cand_q, cand_i, scratch) && threadIdx.x == 0) report_unresolved(P, b);
 }

@@ -62,6 +62,7 @@ struct KParams {
     // count at sc_cnt[s*sc_cnt_shard + b] (sc_rows*sc_stride and sc_rows for separate arrays; one packed block per
     // shard - values, ids, counts - has the block's length in both)
     uint32_t sc_shard_words, sc_cnt_shard;
+    uint32_t sc_sorted;             // merge_draw: every gathered list is in the reference order (best first)
     // candidate lists out (vocabulary sharding step 1); NULL = draw a token
     float* out_q;
     uint32_t* out_i;

@@ -76,6 +76,7 @@ class SampleResult:
     kept_probs: Optional["object"] = None
     row_stats: Optional["object"] = None
     penalized: Optional["object"] = None   # [B, H] post-mask, post-penalty, pre-temperature value at each history position
+    logits: Optional["object"] = None      # fused LM head only, on request: the logits the tensor cores produced
 
 
 class PreparedCall:
@@ -418,6 +419,76 @@ class Sampler:
                                                   cand_count.data_ptr(), G, S))
         res._keepalive = keep
         return res
+
+    # ------------------------------------------------------------------ fused LM head -> sampler
+    def lm_head_sample(self, hidden, embed, *, norm_gain=None, norm_eps: float = 1e-5, temperature: float = 1.0,
+                       top_k: int = 40, top_p: float = 1.0, min_p: float = 0.0, seeds=None, draw_index=None,
+                       seed_base: int = 0, uniforms=None, trace: bool = False, kept_capacity: int = 64,
+                       want_logits: bool = False, stream=None, prepare_only: bool = False):
+        """Final RMSNorm + tied LM head + sampling for a decode batch without materialising the logits
+        (llm_cuda_lm_head_sample; replaces crates/llm-gpu/src/model.rs:481-490 and the sample_with call that
+        follows). `hidden` [B, H] float32 CUDA tensor, `embed` [V, H] bfloat16 CUDA tensor (row-major),
+        `norm_gain` [H] float32 or None when `hidden` is already normalised. With `want_logits` the
+        logits the tensor cores produced are also written (testing aid) and returned as `.logits`."""
+        torch = _torch()
+        assert hidden.is_cuda and hidden.dtype == torch.float32 and hidden.dim() == 2 and hidden.is_contiguous()
+        assert embed.is_cuda and embed.dtype == torch.bfloat16 and embed.dim() == 2 and embed.is_contiguous()
+        B, H = int(hidden.shape[0]), int(hidden.shape[1])
+        V = int(embed.shape[0])
+        assert int(embed.shape[1]) == H
+        st = stream if stream is not None else torch.cuda.current_stream(hidden.device).cuda_stream
+        a = N.LmHeadArgs()
+        a.struct_size = C.sizeof(N.LmHeadArgs)
+        a.batch, a.hidden_dim, a.vocab = B, H, V
+        a.hidden, a.embed = hidden.data_ptr(), embed.data_ptr()
+        keep: list = [hidden, embed]
+        if norm_gain is not None:
+            g = norm_gain.to(device=hidden.device, dtype=torch.float32).contiguous()
+            keep.append(g)
+            a.norm_gain = g.data_ptr()
+        a.norm_eps = norm_eps
+        a.temperature, a.top_k, a.top_p, a.min_p = temperature, top_k, top_p, min_p
+
+        def dev64(value):
+            t = value if isinstance(value, torch.Tensor) else torch.as_tensor(_as_signed(np.asarray(value)))
+            t = t.to(device=hidden.device, dtype=torch.int64).contiguous()
+            keep.append(t)
+            return t.data_ptr()
+
+        if seeds is not None:
+            a.seeds = dev64(seeds)
+        if draw_index is not None:
+            a.draw_index = dev64(draw_index)
+        a.seed_base = seed_base & MASK64
+        if uniforms is not None:
+            un = torch.as_tensor(uniforms).to(device=hidden.device, dtype=torch.float32).contiguous()
+            keep.append(un)
+            a.uniforms = un.data_ptr()
+        a.stream = st
+        sa = N.SampleArgs()  # only to reuse the per-stage output allocation
+        res = self._outputs(sa, B, trace, kept_capacity, None, hidden.device)
+        a.tokens = res.tokens.data_ptr()
+        if trace:
+            a.row_flags, a.kept_count = res.row_flags.data_ptr(), res.kept_count.data_ptr()
+            a.kept_ids, a.kept_probs = res.kept_ids.data_ptr(), res.kept_probs.data_ptr()
+            a.kept_capacity, a.row_stats = kept_capacity, res.row_stats.data_ptr()
+        res.logits = None
+        if want_logits:
+            res.logits = torch.empty((B, V), dtype=torch.float32, device=hidden.device)
+            a.logits_out = res.logits.data_ptr()
+        res._keepalive = keep
+        fn, h, ref = self._lib.llm_cuda_lm_head_sample, self._h, C.byref(a)
+
+        def launch():
+            rc = fn(h, ref)
+            if rc != N.OK:
+                self._check(rc)
+            return res
+
+        launch._keepalive = (a, keep)
+        if prepare_only:
+            return launch
+        return launch()
 
     # ------------------------------------------------------------------ decode-loop glue
     def advance_rows(self, tokens, row_flags, *, history=None, window: int = 128, history_len=None, history_pos=None,
