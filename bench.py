@@ -366,7 +366,7 @@ def run_ours(args, rank, world, local_rank):
             entry["note"] = note
         others[name] = entry
 
-    if not args.skip_others:
+    if not args.skip_others and not args.only_lm_head:
         n_steps = max(20, min(args.steps * 5, 200))
         other("c1", workloads.c1(1000), n_steps,
               note="1000 sequential draws of ONE 32 KB row issued as one 1000-row call over the same row (row stride 0): "
@@ -386,7 +386,7 @@ def run_ours(args, rank, world, local_rank):
 
     # ------------------------------------------------------------------ c5, vocabulary sharded over the ranks (N > 1)
     c5_shard = None
-    if world > 1 and not args.skip_others:
+    if world > 1 and not args.skip_others and not args.only_lm_head:
         w5 = workloads.c5()
         K = 64
         clo, chi = sharding.vocab_shard_ranges(w5.vocab, world)[rank]
@@ -436,6 +436,54 @@ def run_ours(args, rank, world, local_rank):
                     "note": "select kernel streams one shard from HBM per step (a single 4-34 MB buffer: L2-resident between "
                             "steps at N >= 2, stated; the end-to-end figure is collective-latency-bound)"}
 
+    # ------------------------------------------------------------------ fused tied LM head -> sampler (the "next" row beside the path)
+    lm_head = None
+    if not args.skip_lm_head and (args.only_lm_head or not args.skip_others):
+        lm_head = {}
+        Hd, Vv = 4096, VOCAB
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(20270 + rank)
+        embed = (torch.randn((Vv, Hd), generator=gen, device=dev, dtype=torch.float32) * (2.0 / Hd ** 0.5)).to(torch.bfloat16)
+        gain = torch.rand(Hd, generator=gen, device=dev) + 0.5
+        bf16_peak = None
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                bf16_peak = float(json.load(f)["bf16_tflops_sustained"])
+        except Exception:
+            pass
+        for Bd in (64, 256):
+            hidden = torch.randn((Bd, Hd), generator=gen, device=dev, dtype=torch.float32)
+            sd = torch.arange(Bd, dtype=torch.int64, device=dev) + 4321
+            kw = dict(temperature=0.8, top_k=50, top_p=0.95, min_p=0.0)
+            fused = sampler.lm_head_sample(hidden, embed, norm_gain=gain, norm_eps=1e-5, seeds=sd, trace=True, prepare_only=True, **kw)
+            res = fused()
+            torch.cuda.synchronize()
+            undecided = int((res.row_flags == sb.native.ROW_INVALID).sum().item())
+            # the same work with a library contraction and the logits written out (bf16), then the sampler over them
+            def unfused():
+                ms = hidden.pow(2).mean(dim=1, keepdim=True)
+                y = (hidden * torch.rsqrt(ms + 1e-5) * gain).to(torch.bfloat16)
+                lg = torch.matmul(y, embed.t())
+                return sampler.sample_batch(lg, seeds=sd, repetition_penalty=1.0, **kw)
+            unfused()
+            n_lm = max(5, min(args.steps, 20))
+            ms_f = statistics.median(timed([fused], n_lm) for _ in range(3)) / n_lm
+            launches["n"] += 3 * n_lm * 5
+            ms_u = statistics.median(timed([unfused], n_lm) for _ in range(3)) / n_lm
+            w_bytes = Vv * Hd * 2
+            flops = 2.0 * Bd * Hd * Vv
+            entry = {"rows": Bd, "hidden_dim": Hd, "vocab": Vv, "us_per_step_fused": ms_f * 1e3,
+                     "us_per_step_library_gemm_then_sampler": ms_u * 1e3, "rows_per_s_fused": world * Bd / (ms_f * 1e-3),
+                     "embedding_gbs": w_bytes / (ms_f * 1e-3) / 1e9, "frac_of_measured_hbm_peak": w_bytes / (ms_f * 1e-3) / 1e9 / peak,
+                     "tflops": flops / (ms_f * 1e-3) / 1e12, "undecided_rows": undecided,
+                     "logits_bytes_never_written": Bd * Vv * 4}
+            if bf16_peak:
+                entry["frac_of_measured_bf16_peak_sustained"] = entry["tflops"] / bf16_peak
+            lm_head[f"batch{Bd}"] = entry
+        lm_head["note"] = ("final RMSNorm + tied LM head (tcgen05, TMA) + top-k/top-p sampling, logits never written; one read of the "
+                           "1.05 GB embedding per step bounds the small batch (HBM), the contraction the large one")
+        del embed
+
     if rank == 0:
         achieved = alg_bytes / (ms_per_step * 1e-3) / 1e9  # per GPU: one launch streams one 256-row batch
         achieved_single = alg_bytes / (ms_per_step_strict * 1e-3) / 1e9
@@ -463,7 +511,7 @@ def run_ours(args, rank, world, local_rank):
             "ms_per_step_strict_order": ms_per_step_strict,
             "overlapped_tokens_equal_strict_order": overlap_same,
             "region_ms_min_median_max": [min(regions), ms_region, max(regions)],
-            "strong_scaling": strong, "others": others, "c5_vocab_shard": c5_shard})
+            "strong_scaling": strong, "others": others, "c5_vocab_shard": c5_shard, "lm_head_fused": lm_head})
         line = {
             "metric": METRIC, "value": value, "unit": "rows/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
@@ -504,6 +552,8 @@ def main():
                     help="timed regions of K steps to run (0 = as many as keep the GPU loaded for about a second); "
                          "profiling runs use a small number")
     ap.add_argument("--skip-others", action="store_true", help="only the c3 headline (profiling runs)")
+    ap.add_argument("--skip-lm-head", action="store_true", help="leave the fused LM head section out")
+    ap.add_argument("--only-lm-head", action="store_true", help="profiling runs: the fused LM head section and little else")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

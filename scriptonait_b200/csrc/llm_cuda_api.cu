@@ -441,7 +441,7 @@ namespace {
 // The merge step over lists laid out as the two public forms describe.
 int32_t run_merge(llm_cuda_sampler* s, const llm_cuda_sample_args* a, const float* cand_values, const uint32_t* cand_ids,
                   const uint32_t* cand_count, uint32_t n_shards, uint32_t cand_stride, uint64_t shard_words,
-                  uint64_t cnt_shard, bool lists_sorted = true) {
+                  uint64_t cnt_shard, bool lists_sorted = true, uint32_t need = 0u) {
     KParams P;
     int32_t rc = fill_params(s, a, false, &P);
     if (rc != LLM_CUDA_OK) return rc;
@@ -475,6 +475,7 @@ int32_t run_merge(llm_cuda_sampler* s, const llm_cuda_sample_args* a, const floa
     P.sc_shard_words = (uint32_t)shard_words;
     P.sc_cnt_shard = (uint32_t)cnt_shard;
     P.sc_sorted = lists_sorted ? 1u : 0u;
+    P.sc_need = need;
     P.force_full = 0;
     s->last_kernels = 0;
     s->last_split = n_shards;
@@ -573,8 +574,8 @@ int32_t llm_cuda_lm_head_sample(llm_cuda_sampler* s, const llm_cuda_lm_head_args
             s->lm_probe_bytes = probe_bytes;
         }
     }
-    if (lm_head_smem_bytes(n_pad) > s->dev.max_dyn_smem)
-        return fail(s, LLM_CUDA_ERR_CAPACITY, "shared memory for batch %u does not fit", B);
+    const uint32_t stages = lm_head_stages(n_pad, s->dev.max_dyn_smem);
+    if (stages < 2u) return fail(s, LLM_CUDA_ERR_CAPACITY, "shared memory for batch %u does not fit", B);
 
     LmParams P;
     memset(&P, 0, sizeof(P));
@@ -583,6 +584,7 @@ int32_t llm_cuda_lm_head_sample(llm_cuda_sampler* s, const llm_cuda_lm_head_args
     P.n_pad = n_pad;
     P.k_chunks = (H + 63u) / 64u;
     P.probe_every = probe_every;
+    P.stages = stages;
     P.temperature = greedy ? 1.0f : a->temperature;
     P.thr = s->lm_thr;
     P.probe_out = s->lm_probe;
@@ -595,8 +597,8 @@ int32_t llm_cuda_lm_head_sample(llm_cuda_sampler* s, const llm_cuda_lm_head_args
     P.device_errors = s->device_errors;
 
     s->last_kernels = 0;
-    CUDA_TRY(s, launch_rmsnorm_bf16(static_cast<const float*>(a->hidden), a->norm_gain, a->norm_eps, B, n_pad, H, s->lm_xnorm, st));
-    CUDA_TRY(s, cudaMemsetAsync(s->lm_cand_count, 0, 256u * 4u, st));
+    CUDA_TRY(s, launch_rmsnorm_bf16(static_cast<const float*>(a->hidden), a->norm_gain, a->norm_eps, B, n_pad, H, s->lm_xnorm,
+                                    s->lm_cand_count, st));
     cudaError_t ce = cudaSuccess;
     P.phase = LM_PHASE_PROBE;
     P.n_items = n_probe;
@@ -604,15 +606,14 @@ int32_t llm_cuda_lm_head_sample(llm_cuda_sampler* s, const llm_cuda_lm_head_args
     if (rc == -1) return fail(s, LLM_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled is unavailable or rejected the matrices");
     if (rc != 0) return fail(s, LLM_CUDA_ERR_CUDA, "lm_head_kernel (probe): %s", cudaGetErrorString(ce));
     // the r-th largest of a row's probed logits stands at about rank r * probe_every in the whole row: r is chosen
-    // so that this is 2-3 times top_k plus a margin; the finalize step catches the rows where it still fell short
+    // so that this is 2-3 times top_k plus a margin; the merge step reports the rows where it still fell short
     uint32_t rank = probe_every == 1u ? k : 2u * ((k + probe_every - 1u) / probe_every) + 8u;
     if (rank > probe_cols) rank = probe_cols;
-    CUDA_TRY(s, launch_probe_threshold(P, rank, st));
+    CUDA_TRY(s, launch_probe_threshold(P, rank, probe_every == 1u, st));
     P.phase = LM_PHASE_MAIN;
     P.n_items = n_tiles - n_probe;
     rc = launch_lm_head(P, a->embed, s->lm_xnorm, H, s->dev.sm_count, st, &ce);
     if (rc != 0) return fail(s, LLM_CUDA_ERR_CUDA, "lm_head_kernel (main): %s", cudaGetErrorString(ce));
-    CUDA_TRY(s, launch_finalize_counts(s->lm_cand_count, B, kLmCandCap, k < V ? k : V, st));
 
     // the sampler's own merge + ordered tail over one unordered candidate list per row
     llm_cuda_sample_args m;
@@ -640,9 +641,9 @@ int32_t llm_cuda_lm_head_sample(llm_cuda_sampler* s, const llm_cuda_lm_head_args
     m.row_stats = a->row_stats;
     m.stream = a->stream;
     const int32_t mr = run_merge(s, &m, s->lm_cand_q, s->lm_cand_i, s->lm_cand_count, 1u, kLmCandCap, (uint64_t)B * kLmCandCap, B,
-                                 /*lists_sorted=*/false);
+                                 /*lists_sorted=*/false, /*need=*/k < V ? k : V);
     if (mr != LLM_CUDA_OK) return mr;
-    s->last_kernels = P.n_items ? 6u : 5u;
+    s->last_kernels = P.n_items ? 5u : 4u;
     return LLM_CUDA_OK;
 }
 

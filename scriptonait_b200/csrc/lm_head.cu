@@ -17,14 +17,14 @@
 //                             it become candidates
 //   lm_head_kernel, main      the other tiles: the epilogue reads the accumulators out of tensor memory and
 //                             appends (logit / T, vocabulary id) for every logit at or above the threshold
-//   finalize_counts_kernel    a row whose candidates number fewer than top_k (threshold too high) or more than
-//                             the list holds is marked undecided - it is reported, never guessed
-//   merge_draw_kernel         the sampler's own merge + ordered tail over the candidate lists
+//   merge_draw_kernel         the sampler's own merge + ordered tail over the candidate lists; a row whose
+//                             candidates number fewer than top_k (threshold too high) or more than the list
+//                             holds is undecided - it is reported, never guessed
 // Exact by construction: every logit >= threshold is captured, so when at least top_k were captured the
 // top_k largest are among them, whatever the threshold was.
 //
 // lm_head_kernel: 192 threads. Warp 0 issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of a
-// 128 x 64 tile of the embedding and the batch x 64 tile of the hidden states into a 4-stage ring; warp 1
+// 128 x 64 tile of the embedding and the batch x 64 tile of the hidden states into a ring of 4-8 stages; warp 1
 // issues tcgen05.mma (M = 128 vocabulary rows, N = padded batch, K = 16 per instruction) into one of two
 // accumulators in tensor memory and commits to mbarriers; warps 2-5 are the epilogue (tcgen05.ld). Every
 // wait is bounded: a wait that runs out sets LLM_CUDA_STATUS_COPY_TIMEOUT, all roles leave their loops,
@@ -44,7 +44,7 @@ namespace {
 constexpr int LM_THREADS = 192;
 constexpr int TILE_M = 128;            // vocabulary rows per tile = lanes of tensor memory
 constexpr int KCHUNK = 64;             // bf16 elements per 128-byte swizzled shared-memory row
-constexpr int LM_STAGES = 4;
+constexpr int LM_MAX_STAGES = 8;      // ring stages: as many as fit in shared memory, up to this
 constexpr uint32_t A_STAGE_BYTES = TILE_M * KCHUNK * 2;  // 16 KB
 constexpr uint32_t TMEM_COLS = 512;    // two accumulators of up to 256 columns
 constexpr uint32_t LM_WAIT_LIMIT = 1u << 16;
@@ -135,7 +135,7 @@ __device__ __forceinline__ uint32_t tile_of(uint32_t phase, uint32_t i, uint32_t
 __global__ void __launch_bounds__(LM_THREADS, 1)
 lm_head_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const LmParams P) {
     extern __shared__ unsigned char lm_dyn[];
-    __shared__ __align__(8) uint64_t full_bar[LM_STAGES], empty_bar[LM_STAGES], acc_full[2], acc_empty[2], drain_bar;
+    __shared__ __align__(8) uint64_t full_bar[LM_MAX_STAGES], empty_bar[LM_MAX_STAGES], acc_full[2], acc_empty[2], drain_bar;
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile uint32_t abort_flag;
     __shared__ float thr_s[256];
@@ -145,6 +145,7 @@ lm_head_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const uint32_t n_pad = P.n_pad;
     const uint32_t b_stage_bytes = n_pad * KCHUNK * 2u;
     unsigned char* a_tiles = base;
+    const uint32_t LM_STAGES = P.stages;
     unsigned char* b_tiles = base + (size_t)LM_STAGES * A_STAGE_BYTES;
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
@@ -152,7 +153,7 @@ lm_head_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const uint32_t k_chunks = P.k_chunks;
 
     if (tid == 0) {
-        for (int s = 0; s < LM_STAGES; ++s) {
+        for (uint32_t s = 0; s < LM_STAGES; ++s) {
             bar_init(&full_bar[s], 1u);
             bar_init(&empty_bar[s], 1u);
         }
@@ -183,7 +184,7 @@ lm_head_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const uint32_t tile = tile_of(P.phase, i, P.probe_every);
                 for (uint32_t kc = 0; kc < k_chunks; ++kc, ++g) {
                     const uint32_t s = g % LM_STAGES;
-                    if (g >= (uint32_t)LM_STAGES && !bar_wait(&empty_bar[s], ((g / LM_STAGES) - 1u) & 1u, &abort_flag)) break;
+                    if (g >= LM_STAGES && !bar_wait(&empty_bar[s], ((g / LM_STAGES) - 1u) & 1u, &abort_flag)) break;
                     bar_expect_tx(&full_bar[s], A_STAGE_BYTES + b_stage_bytes);
                     tma_load_2d(a_tiles + (size_t)s * A_STAGE_BYTES, &map_w, (int32_t)(kc * KCHUNK), (int32_t)(tile * TILE_M), &full_bar[s]);
                     tma_load_2d(b_tiles + (size_t)s * b_stage_bytes, &map_x, (int32_t)(kc * KCHUNK), 0, &full_bar[s]);
@@ -272,8 +273,10 @@ lm_head_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
 // y[b, :] = bf16(x[b, :] * rsqrt(mean(x[b, :]^2) + eps) * gain) (crates/llm-core/src/ops/activation.rs:5-19), or
 // bf16(x) when gain is NULL; rows batch .. n_pad - 1 of y are zero. One CTA per row of y.
-__global__ void rmsnorm_bf16_kernel(const float* x, const float* gain, float eps, uint32_t batch, uint32_t dim, __nv_bfloat16* y) {
+__global__ void rmsnorm_bf16_kernel(const float* x, const float* gain, float eps, uint32_t batch, uint32_t dim, __nv_bfloat16* y,
+                                    uint32_t* cand_count) {
     const uint32_t b = blockIdx.x;
+    if (threadIdx.x == 0 && cand_count) cand_count[b] = 0u;  // the step's candidate lists start empty
     __shared__ float part[32];
     __shared__ float inv_s;
     if (b >= batch) {
@@ -314,10 +317,15 @@ __device__ __forceinline__ float lm_okey_to_float(uint32_t k) {
 }
 }  // namespace
 
-// Per row: the `rank`-th largest of the row's probe logits (radix select over ordered keys, 8 bits a pass)
-// becomes the threshold - lowered by four floats when T != 1, since neighbouring floats can share a
-// quotient x / T - and the probe logits at or above it become the row's first candidates. One CTA per row.
-__global__ void __launch_bounds__(256) probe_threshold_kernel(const LmParams P, uint32_t rank) {
+// Per row: a threshold near the `rank`-th largest of the row's probe logits - lowered by four floats when
+// T != 1, since neighbouring floats can share a quotient x / T - and the probe logits at or above it become
+// the row's first candidates. Any threshold keeps the result exact (the merge step checks that enough
+// logits reached it); it only has to land where a few times top_k logits of the row pass. `exact` (small
+// vocabularies, probed whole): a radix select over ordered keys, 8 bits a pass. Otherwise every thread
+// takes the maximum of its share of the probe, and the rank-th largest of those 256 maxima is used: at
+// least `rank` probe logits reach it and, the top values nearly always sitting with different threads,
+// hardly more. One CTA per row.
+__global__ void __launch_bounds__(256) probe_threshold_kernel(const LmParams P, uint32_t rank, uint32_t exact) {
     const uint32_t b = blockIdx.x, tid = threadIdx.x;
     __shared__ uint32_t hist[256];
     __shared__ uint32_t sel_digit, sel_need;
@@ -325,6 +333,23 @@ __global__ void __launch_bounds__(256) probe_threshold_kernel(const LmParams P, 
     const uint32_t n = P.probe_cols;
     uint32_t need = rank < 1u ? 1u : rank;
     uint32_t prefix = 0u;
+    if (!exact) {
+        uint32_t best = 0u;  // below every ordered key of a float
+        for (uint32_t i = tid; i < n; i += 256u) {
+            const float x = row[i];
+            if (x == x) best = max(best, lm_okey(x));
+        }
+        hist[tid] = best;
+        __syncthreads();
+        uint32_t above = 0u;  // maxima that come before this thread's (ties broken by thread id)
+        for (uint32_t j = 0; j < 256u; ++j) {
+            const uint32_t o = hist[j];
+            above += (o > best || (o == best && j < tid)) ? 1u : 0u;
+        }
+        if (above == min(need, 256u) - 1u) sel_digit = best;
+        __syncthreads();
+        prefix = sel_digit;
+    } else
     for (int pass = 0; pass < 4; ++pass) {
         const int sh = 24 - 8 * pass;
         hist[tid] = 0u;
@@ -369,16 +394,6 @@ __global__ void __launch_bounds__(256) probe_threshold_kernel(const LmParams P, 
     }
 }
 
-// A row is decided by its candidates only if all logits at or above its threshold were captured (the list
-// did not overflow) and at least min(top_k, vocab) of them exist; otherwise its count becomes the marker
-// the merge step reads as "this list cannot decide the row".
-__global__ void finalize_counts_kernel(uint32_t* cand_count, uint32_t batch, uint32_t cand_cap, uint32_t need) {
-    const uint32_t b = blockIdx.x * blockDim.x + threadIdx.x;
-    if (b >= batch) return;
-    const uint32_t c = cand_count[b];
-    if (c > cand_cap || c < need) cand_count[b] = 0xffffffffu;
-}
-
 // ---------------------------------------------------------------------------
 // host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -412,15 +427,22 @@ static int make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t c
     return r == CUDA_SUCCESS ? 0 : -2;
 }
 
-size_t lm_head_smem_bytes(uint32_t n_pad) { return (size_t)LM_STAGES * (A_STAGE_BYTES + (size_t)n_pad * KCHUNK * 2u) + 1024u; }
+uint32_t lm_head_stages(uint32_t n_pad, size_t max_dyn_smem) {
+    const size_t per_stage = A_STAGE_BYTES + (size_t)n_pad * KCHUNK * 2u;
+    size_t n = (max_dyn_smem - 1024u) / per_stage;
+    if (n > (size_t)LM_MAX_STAGES) n = LM_MAX_STAGES;
+    return (uint32_t)n;
+}
+
+size_t lm_head_smem_bytes(uint32_t n_pad, uint32_t stages) { return (size_t)stages * (A_STAGE_BYTES + (size_t)n_pad * KCHUNK * 2u) + 1024u; }
 
 cudaError_t lm_head_configure(size_t max_dyn_smem) {
     return cudaFuncSetAttribute(lm_head_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)max_dyn_smem);
 }
 
 cudaError_t launch_rmsnorm_bf16(const float* x, const float* gain, float eps, uint32_t batch, uint32_t n_pad, uint32_t dim, void* y,
-                                cudaStream_t stream) {
-    rmsnorm_bf16_kernel<<<n_pad, 256, 0, stream>>>(x, gain, eps, batch, dim, static_cast<__nv_bfloat16*>(y));
+                                uint32_t* cand_count, cudaStream_t stream) {
+    rmsnorm_bf16_kernel<<<n_pad, 256, 0, stream>>>(x, gain, eps, batch, dim, static_cast<__nv_bfloat16*>(y), cand_count);
     return cudaGetLastError();
 }
 
@@ -432,18 +454,13 @@ int launch_lm_head(const LmParams& P, const void* embed, const void* x_norm, uin
     if (make_map(&map_w, embed, P.vocab, hidden, TILE_M) != 0) return -1;
     if (make_map(&map_x, x_norm, P.n_pad, hidden, P.n_pad) != 0) return -1;
     const uint32_t grid = P.n_items < sm_count ? P.n_items : sm_count;
-    lm_head_kernel<<<grid, LM_THREADS, lm_head_smem_bytes(P.n_pad), stream>>>(map_w, map_x, P);
+    lm_head_kernel<<<grid, LM_THREADS, lm_head_smem_bytes(P.n_pad, P.stages), stream>>>(map_w, map_x, P);
     *cuda_error = cudaGetLastError();
     return *cuda_error == cudaSuccess ? 0 : -3;
 }
 
-cudaError_t launch_probe_threshold(const LmParams& P, uint32_t rank, cudaStream_t stream) {
-    probe_threshold_kernel<<<P.batch, 256, 0, stream>>>(P, rank);
-    return cudaGetLastError();
-}
-
-cudaError_t launch_finalize_counts(uint32_t* cand_count, uint32_t batch, uint32_t cand_cap, uint32_t need, cudaStream_t stream) {
-    finalize_counts_kernel<<<(batch + 127u) / 128u, 128, 0, stream>>>(cand_count, batch, cand_cap, need);
+cudaError_t launch_probe_threshold(const LmParams& P, uint32_t rank, bool exact, cudaStream_t stream) {
+    probe_threshold_kernel<<<P.batch, 256, 0, stream>>>(P, rank, exact ? 1u : 0u);
     return cudaGetLastError();
 }
 

@@ -16,6 +16,7 @@ struct LmParams {
     uint32_t k_chunks;               // hidden_dim / 64, rounded up
     uint32_t phase, probe_every;
     uint32_t n_items;                // vocabulary tiles this launch works through
+    uint32_t stages;                 // ring stages (4-8: as many as shared memory holds)
     float temperature;
     float* thr;                      // [batch] per-row threshold (written by the probe step, read by the main step)
     float* probe_out;                // [batch, probe_cols]
@@ -28,14 +29,15 @@ struct LmParams {
     uint32_t* device_errors;
 };
 
-size_t lm_head_smem_bytes(uint32_t n_pad);
+uint32_t lm_head_stages(uint32_t n_pad, size_t max_dyn_smem);
+size_t lm_head_smem_bytes(uint32_t n_pad, uint32_t stages);
 cudaError_t lm_head_configure(size_t max_dyn_smem);
+// also zeroes cand_count[0 .. n_pad) (NULL to skip)
 cudaError_t launch_rmsnorm_bf16(const float* x, const float* gain, float eps, uint32_t batch, uint32_t n_pad, uint32_t dim, void* y,
-                                cudaStream_t stream);
+                                uint32_t* cand_count, cudaStream_t stream);
 // 0, -1 (no tensor-map encoder / encoding failed) or -3 (launch failed, *cuda_error says why)
 int launch_lm_head(const LmParams& P, const void* embed, const void* x_norm, uint32_t hidden, uint32_t sm_count, cudaStream_t stream,
                    cudaError_t* cuda_error);
-cudaError_t launch_probe_threshold(const LmParams& P, uint32_t rank, cudaStream_t stream);
-cudaError_t launch_finalize_counts(uint32_t* cand_count, uint32_t batch, uint32_t cand_cap, uint32_t need, cudaStream_t stream);
+cudaError_t launch_probe_threshold(const LmParams& P, uint32_t rank, bool exact, cudaStream_t stream);
 
 }  // namespace llmc

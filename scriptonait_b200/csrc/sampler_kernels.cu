@@ -264,7 +264,7 @@ __device__ uint32_t merge_lists(const KParams& P, uint32_t b, const RowCfg& rc, 
         const size_t at = (size_t)s * P.sc_cnt_shard + b;
         if (P.sc_maxkey) atomicMax(&S.max_key, __ldcg(&P.sc_maxkey[at]));
         const uint32_t raw = __ldcg(&P.sc_cnt[at]);
-        if (raw == 0xffffffffu) {
+        if (raw == 0xffffffffu || (P.sc_need && (raw > P.sc_stride || raw < P.sc_need))) {
             S.keep = 1u;
         } else {
             const uint32_t cnt = min(raw & LIST_COUNT, P.sc_stride);

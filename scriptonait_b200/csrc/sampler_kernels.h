@@ -63,6 +63,7 @@ struct KParams {
     // shard - values, ids, counts - has the block's length in both)
     uint32_t sc_shard_words, sc_cnt_shard;
     uint32_t sc_sorted;             // merge_draw: every gathered list is in the reference order (best first)
+    uint32_t sc_need;               // merge_draw: nonzero = a list with fewer entries than this, or more than sc_stride, cannot decide its row
     // candidate lists out (vocabulary sharding step 1); NULL = draw a token
     float* out_q;
     uint32_t* out_i;
