@@ -530,8 +530,9 @@ int32_t llm_cuda_lm_head_sample(llm_cuda_sampler* s, const llm_cuda_lm_head_args
         return fail(s, LLM_CUDA_ERR_CAPACITY, "batch %u beyond 256 (one tensor-core tile) or the handle's max_batch", a->batch);
     if (a->vocab == 0 || a->hidden_dim == 0 || a->hidden_dim % 8u)
         return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "vocab and hidden_dim must be > 0 and hidden_dim a multiple of 8 (16-byte rows for TMA)");
-    if ((reinterpret_cast<uintptr_t>(a->embed) & 15u) || (reinterpret_cast<uintptr_t>(a->hidden) & 3u))
-        return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "embed must be 16-byte aligned and hidden 4-byte aligned");
+    if ((reinterpret_cast<uintptr_t>(a->embed) & 15u) || (reinterpret_cast<uintptr_t>(a->hidden) & 15u) ||
+        (reinterpret_cast<uintptr_t>(a->norm_gain) & 15u))
+        return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "embed, hidden and norm_gain must be 16-byte aligned");
     if (a->temperature != a->temperature) return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "temperature is NaN");
     const bool greedy = a->temperature <= 0.0f;
     if (!greedy && (a->top_k == 0 || a->top_k > 256u))

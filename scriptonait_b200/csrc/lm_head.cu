@@ -284,10 +284,19 @@ __global__ void rmsnorm_bf16_kernel(const float* x, const float* gain, float eps
         return;
     }
     const float* row = x + (size_t)b * dim;
+    const uint32_t dim4 = dim / 4u;  // dim is a multiple of 8: whole 16-byte vectors
+    const float4* row4 = reinterpret_cast<const float4*>(row);
     float inv = 1.0f;
     if (gain) {
         float ss = 0.0f;
-        for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) ss = fmaf(row[i], row[i], ss);
+#pragma unroll 4
+        for (uint32_t i = threadIdx.x; i < dim4; i += blockDim.x) {
+            const float4 v = __ldg(&row4[i]);
+            ss = fmaf(v.x, v.x, ss);
+            ss = fmaf(v.y, v.y, ss);
+            ss = fmaf(v.z, v.z, ss);
+            ss = fmaf(v.w, v.w, ss);
+        }
         for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
         if ((threadIdx.x & 31u) == 0) part[threadIdx.x >> 5] = ss;
         __syncthreads();
@@ -299,9 +308,20 @@ __global__ void rmsnorm_bf16_kernel(const float* x, const float* gain, float eps
         __syncthreads();
         inv = inv_s;
     }
-    for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) {
-        const float v = gain ? row[i] * inv * gain[i] : row[i];
-        y[(size_t)b * dim + i] = __float2bfloat16_rn(v);
+    const float4* gain4 = reinterpret_cast<const float4*>(gain);
+    uint2* y2 = reinterpret_cast<uint2*>(y + (size_t)b * dim);
+#pragma unroll 4
+    for (uint32_t i = threadIdx.x; i < dim4; i += blockDim.x) {
+        float4 v = __ldg(&row4[i]);
+        if (gain) {
+            const float4 g = __ldg(&gain4[i]);
+            v.x = v.x * inv * g.x;
+            v.y = v.y * inv * g.y;
+            v.z = v.z * inv * g.z;
+            v.w = v.w * inv * g.w;
+        }
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+        y2[i] = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
     }
 }
 
@@ -335,9 +355,14 @@ __global__ void __launch_bounds__(256) probe_threshold_kernel(const LmParams P, 
     uint32_t prefix = 0u;
     if (!exact) {
         uint32_t best = 0u;  // below every ordered key of a float
-        for (uint32_t i = tid; i < n; i += 256u) {
-            const float x = row[i];
-            if (x == x) best = max(best, lm_okey(x));
+        const float4* row4 = reinterpret_cast<const float4*>(row);  // probe rows are whole tiles of 128 floats
+#pragma unroll 4
+        for (uint32_t i = tid; i < n / 4u; i += 256u) {
+            const float4 v = __ldg(&row4[i]);
+            if (v.x == v.x) best = max(best, lm_okey(v.x));
+            if (v.y == v.y) best = max(best, lm_okey(v.y));
+            if (v.z == v.z) best = max(best, lm_okey(v.z));
+            if (v.w == v.w) best = max(best, lm_okey(v.w));
         }
         hist[tid] = best;
         __syncthreads();
@@ -381,14 +406,21 @@ __global__ void __launch_bounds__(256) probe_threshold_kernel(const LmParams P, 
     if (key < lowest) key = lowest;
     const float thr = lm_okey_to_float(key);
     if (tid == 0) P.thr[b] = thr;
-    for (uint32_t i = tid; i < n; i += 256u) {
-        const float x = row[i];
-        const uint32_t v = (i / TILE_M) * P.probe_every * TILE_M + (i % TILE_M);
-        if (v < P.vocab && x >= thr) {
-            const uint32_t slot = atomicAdd(&P.cand_count[b], 1u);
-            if (slot < P.cand_cap) {
-                P.cand_q[(size_t)b * P.cand_cap + slot] = temper_lm(x, P.temperature);
-                P.cand_i[(size_t)b * P.cand_cap + slot] = v;
+    const float4* row4 = reinterpret_cast<const float4*>(row);
+#pragma unroll 4
+    for (uint32_t i4 = tid; i4 < n / 4u; i4 += 256u) {
+        const float4 q = __ldg(&row4[i4]);
+        const float xs[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const uint32_t i = i4 * 4u + (uint32_t)e;
+            const uint32_t v = (i / TILE_M) * P.probe_every * TILE_M + (i % TILE_M);
+            if (v < P.vocab && xs[e] >= thr) {
+                const uint32_t slot = atomicAdd(&P.cand_count[b], 1u);
+                if (slot < P.cand_cap) {
+                    P.cand_q[(size_t)b * P.cand_cap + slot] = temper_lm(xs[e], P.temperature);
+                    P.cand_i[(size_t)b * P.cand_cap + slot] = v;
+                }
             }
         }
     }
