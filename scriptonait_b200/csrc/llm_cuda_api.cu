@@ -575,7 +575,9 @@ int32_t llm_cuda_lm_head_sample(llm_cuda_sampler* s, const llm_cuda_lm_head_args
             s->lm_probe_bytes = probe_bytes;
         }
     }
-    const uint32_t stages = lm_head_stages(n_pad, s->dev.max_dyn_smem);
+    // up to 128 rows: two CTAs per SM, each with half of the SM's shared memory and tensor memory
+    const uint32_t ctas_per_sm = n_pad <= 128u ? 2u : 1u;
+    const uint32_t stages = lm_head_stages(n_pad, ctas_per_sm == 2u ? (s->dev.max_dyn_smem - 8192u) / 2u : s->dev.max_dyn_smem);
     if (stages < 2u) return fail(s, LLM_CUDA_ERR_CAPACITY, "shared memory for batch %u does not fit", B);
 
     LmParams P;
@@ -586,6 +588,8 @@ int32_t llm_cuda_lm_head_sample(llm_cuda_sampler* s, const llm_cuda_lm_head_args
     P.k_chunks = (H + 63u) / 64u;
     P.probe_every = probe_every;
     P.stages = stages;
+    P.tmem_cols = ctas_per_sm == 2u ? 256u : 512u;
+    P.ctas_per_sm = ctas_per_sm;
     P.temperature = greedy ? 1.0f : a->temperature;
     P.thr = s->lm_thr;
     P.probe_out = s->lm_probe;

@@ -46,7 +46,6 @@ constexpr int TILE_M = 128;            // vocabulary rows per tile = lanes of te
 constexpr int KCHUNK = 64;             // bf16 elements per 128-byte swizzled shared-memory row
 constexpr int LM_MAX_STAGES = 8;      // ring stages: as many as fit in shared memory, up to this
 constexpr uint32_t A_STAGE_BYTES = TILE_M * KCHUNK * 2;  // 16 KB
-constexpr uint32_t TMEM_COLS = 512;    // two accumulators of up to 256 columns
 constexpr uint32_t LM_WAIT_LIMIT = 1u << 16;
 
 __device__ __forceinline__ uint32_t saddr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -132,7 +131,7 @@ __device__ __forceinline__ uint32_t tile_of(uint32_t phase, uint32_t i, uint32_t
 
 }  // namespace
 
-__global__ void __launch_bounds__(LM_THREADS, 1)
+__global__ void __launch_bounds__(LM_THREADS, 2)
 lm_head_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const LmParams P) {
     extern __shared__ unsigned char lm_dyn[];
     __shared__ __align__(8) uint64_t full_bar[LM_MAX_STAGES], empty_bar[LM_MAX_STAGES], acc_full[2], acc_empty[2], drain_bar;
@@ -167,7 +166,7 @@ lm_head_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
     for (uint32_t i = tid; i < 256u; i += LM_THREADS) thr_s[i] = (P.thr && i < P.batch) ? P.thr[i] : __uint_as_float(0x7f800000u);
     if (warp == 1) {  // tensor memory: both accumulators, allocated by one whole warp, which also frees it
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(saddr(&tmem_base_slot)), "r"(TMEM_COLS)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(saddr(&tmem_base_slot)), "r"(P.tmem_cols)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -202,7 +201,7 @@ lm_head_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const uint32_t j = it & 1u;
                 if (it >= 2u && !bar_wait(&acc_empty[j], ((it >> 1) - 1u) & 1u, &abort_flag)) break;
                 tc_fence_after();
-                const uint32_t tmem_d = tmem_base + j * 256u;
+                const uint32_t tmem_d = tmem_base + j * (P.tmem_cols >> 1);
                 bool ok = true;
                 for (uint32_t kc = 0; kc < k_chunks; ++kc, ++g) {
                     const uint32_t s = g % LM_STAGES;
@@ -240,7 +239,7 @@ lm_head_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             const bool v_ok = v < P.vocab;
             for (uint32_t c0 = 0; c0 < n_pad; c0 += 32u) {
                 uint32_t r[32];
-                tmem_ld32(tmem_base + ((quarter * 32u) << 16) + j * 256u + c0, r);
+                tmem_ld32(tmem_base + ((quarter * 32u) << 16) + j * (P.tmem_cols >> 1) + c0, r);
 #pragma unroll
                 for (int c = 0; c < 32; ++c) {
                     const uint32_t b = c0 + (uint32_t)c;
@@ -267,7 +266,7 @@ lm_head_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     if (tid == 0 && abort_flag && P.device_errors) atomicOr(P.device_errors, LLM_CUDA_STATUS_COPY_TIMEOUT);
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(P.tmem_cols) : "memory");
     }
 }
 
@@ -485,7 +484,9 @@ int launch_lm_head(const LmParams& P, const void* embed, const void* x_norm, uin
     CUtensorMap map_w, map_x;
     if (make_map(&map_w, embed, P.vocab, hidden, TILE_M) != 0) return -1;
     if (make_map(&map_x, x_norm, P.n_pad, hidden, P.n_pad) != 0) return -1;
-    const uint32_t grid = P.n_items < sm_count ? P.n_items : sm_count;
+    // small batches leave room for two CTAs per SM (each with half of tensor memory): more loads in flight
+    const uint32_t slots = sm_count * P.ctas_per_sm;
+    const uint32_t grid = P.n_items < slots ? P.n_items : slots;
     lm_head_kernel<<<grid, LM_THREADS, lm_head_smem_bytes(P.n_pad, P.stages), stream>>>(map_w, map_x, P);
     *cuda_error = cudaGetLastError();
     return *cuda_error == cudaSuccess ? 0 : -3;

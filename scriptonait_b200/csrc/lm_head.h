@@ -16,7 +16,9 @@ struct LmParams {
     uint32_t k_chunks;               // hidden_dim / 64, rounded up
     uint32_t phase, probe_every;
     uint32_t n_items;                // vocabulary tiles this launch works through
-    uint32_t stages;                 // ring stages (4-8: as many as shared memory holds)
+    uint32_t stages;                 // ring stages (as many as shared memory holds, up to 8)
+    uint32_t tmem_cols;              // tensor-memory columns this CTA allocates: two accumulators of tmem_cols / 2
+    uint32_t ctas_per_sm;            // 2 when two CTAs' shared memory and tensor memory fit on an SM, else 1
     float temperature;
     float* thr;                      // [batch] per-row threshold (written by the probe step, read by the main step)
     float* probe_out;                // [batch, probe_cols]
