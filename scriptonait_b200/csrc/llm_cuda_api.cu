@@ -315,10 +315,12 @@ int32_t llm_cuda_sampler_create(int32_t device, uint32_t max_batch, uint32_t max
     if ((e = configure_kernels(s->dev.max_dyn_smem)) != cudaSuccess) return bail("cudaFuncSetAttribute", e);
     s->sc_lists = max_batch > 4096u ? max_batch : 4096u;
     s->vpad = (max_vocab + 1023u) & ~1023u;
-    // one slot per SM: 20 bytes per column (two key/index array pairs and the probabilities); rows that
-    // need the full ordering are rare, and a CTA that finds every slot taken waits for one (bounded)
-    s->nslots = s->dev.sm_count;
+    // two slots per SM (a batch of such rows then orders at two rows per SM instead of queueing for one): 20
+    // bytes per column (two key/index array pairs and the probabilities), at most 2 GiB in all; a CTA that
+    // finds every slot taken waits for one (bounded)
+    s->nslots = 2u * s->dev.sm_count;
     if (s->nslots > max_batch) s->nslots = max_batch;
+    while (s->nslots > s->dev.sm_count && (uint64_t)s->nslots * s->vpad * 20u > (2ull << 30)) s->nslots -= 1u;
     if ((e = cudaMalloc(&s->sc_q, kScratchEntries * 4u)) != cudaSuccess) return bail("cudaMalloc", e);
     if ((e = cudaMalloc(&s->sc_i, kScratchEntries * 4u)) != cudaSuccess) return bail("cudaMalloc", e);
     if ((e = cudaMalloc(&s->sc_cnt, (size_t)s->sc_lists * 4u)) != cudaSuccess) return bail("cudaMalloc", e);

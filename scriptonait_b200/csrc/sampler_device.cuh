@@ -195,6 +195,20 @@ __device__ __forceinline__ void hash_insert(uint32_t* hkeys, uint32_t* hcnt, uin
         h = (h + 1u) & mask;
     }
 }
+// Same insertion; returns the slot when this call created it (the first occurrence of the id), else EMPTY_KEY.
+__device__ __forceinline__ uint32_t hash_insert_owner(uint32_t* hkeys, uint32_t* hcnt, uint32_t slots, uint32_t id) {
+    const uint32_t mask = slots - 1u;
+    uint32_t h = hash_slot(id, mask);
+    for (uint32_t probe = 0; probe < slots; ++probe) {
+        uint32_t prev = atomicCAS(&hkeys[h], EMPTY_KEY, id);
+        if (prev == EMPTY_KEY || prev == id) {
+            atomicAdd(&hcnt[h], 1u);
+            return prev == EMPTY_KEY ? h : EMPTY_KEY;
+        }
+        h = (h + 1u) & mask;
+    }
+    return EMPTY_KEY;
+}
 __device__ __forceinline__ uint32_t hash_count(const uint32_t* hkeys, const uint32_t* hcnt, uint32_t slots, uint32_t id) {
     const uint32_t mask = slots - 1u;
     uint32_t h = hash_slot(id, mask);

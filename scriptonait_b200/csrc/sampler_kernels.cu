@@ -1077,6 +1077,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
     }
 
     // ---- mask / penalty side tables
+    float pre_x[2] = {0.0f, 0.0f};                       // logits of this thread's first two history ids ...
+    uint32_t pre_slot[2] = {EMPTY_KEY, EMPTY_KEY};       // ... and their table slots, where this thread created them
     if (BITS) {
         // the first 512 history ids are fetched while the tables are cleared
         const uint32_t* hist = P.history + (size_t)b * P.hist_stride;
@@ -1087,6 +1089,13 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
                 const uint32_t j = (uint32_t)k * THREADS + tid;
                 if (j < rc.hlen) pre_id[k] = __ldg(&hist[j]);
             }
+            // ... and so are their logits: the scattered loads travel while the tables are cleared and
+            // filled, instead of costing a trip to memory of their own afterwards
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                const uint32_t j = (uint32_t)k * THREADS + tid;
+                if (j < rc.hlen && pre_id[k] >= gid0 && pre_id[k] - gid0 < ncols) pre_x[k] = load_logit(row + (pre_id[k] - P.col_offset));
+            }
         }
         for (uint32_t w = tid; w < P.bitmap_words; w += THREADS) bitmap[w] = 0u;
         for (uint32_t i = tid; i < P.hash_slots; i += THREADS) {
@@ -1095,17 +1104,19 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
         }
         cta_sync();
         if (rc.has_pen) {
-            auto note = [&](uint32_t id) {
+            auto note = [&](uint32_t id) -> uint32_t {  // the table slot, if this occurrence of the id created it
+                uint32_t created = EMPTY_KEY;
                 if (id >= gid0 && id - gid0 < ncols) {  // ids outside the vocabulary are skipped (generate.rs:345)
-                    hash_insert(hkeys, hcnt, P.hash_slots, id);
+                    created = hash_insert_owner(hkeys, hcnt, P.hash_slots, id);
                     const uint32_t j2 = id - gid0 + lead;
                     if (IN_BOUNDS(j2 >> 5, P.bitmap_words)) atomicOr(&bitmap[j2 >> 5], 1u << (j2 & 31u));
                 }
+                return created;
             };
 #pragma unroll
             for (int k = 0; k < 2; ++k)
-                if ((uint32_t)k * THREADS + tid < rc.hlen) note(pre_id[k]);
-            for (uint32_t j = 2u * THREADS + tid; j < rc.hlen; j += THREADS) note(__ldg(&hist[j]));
+                if ((uint32_t)k * THREADS + tid < rc.hlen) pre_slot[k] = note(pre_id[k]);
+            for (uint32_t j = 2u * THREADS + tid; j < rc.hlen; j += THREADS) (void)note(__ldg(&hist[j]));
         }
         if (P.allowed_bits) {
             // bit jb of bitmap word w stands for global id gid0 - lead + 32*w + jb
@@ -1145,7 +1156,19 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
     //      CTA's columns is read once here, masked and penalised; the value replaces the id's count
     //      in the table and becomes a candidate after the sweep, if it can still matter then. The
     //      stream skips all flagged ids (penalised or blocked by the mask).
-    if (BITS) {
+    if (BITS && rc.has_pen && rc.hlen <= 2u * (uint32_t)THREADS) {
+        // every id's first occurrence was inserted by the thread that already holds its logit
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            if (pre_slot[k] != EMPTY_KEY) {
+                float x = pre_x[k];
+                if (id_blocked(P, hkeys[pre_slot[k]])) x = neg_inf();
+                x = penalize(x, rc.pen, hcnt[pre_slot[k]]);
+                tmax = fmaxf(tmax, x);
+                hcnt[pre_slot[k]] = __float_as_uint(x);  // only this thread touches the slot
+            }
+        }
+    } else if (BITS) {
         // four table slots per thread and round, so that the scattered loads of a round are in flight together
         for (uint32_t base = 0; base < P.hash_slots; base += 4u * THREADS) {
             uint32_t id[4], cnt[4];
