@@ -101,7 +101,11 @@ typedef struct llm_cuda_sample_args {
                                  * operation - e.g. consecutive llm_cuda_sample_batch calls over independent
                                  * batches. Not behind the kernel that produced the logits, and not behind
                                  * llm_cuda_advance_rows (it writes draw_index and history). 0 = strict stream
-                                 * order. llm_cuda_sample_batch_static ignores the flag (always strict). */
+                                 * order. 2 = early launch only: the grid is set up while the preceding kernel
+                                 * is finishing (if that kernel allows it, as this library's do) but reads and
+                                 * writes nothing before it has completed - data order is strict, safe behind any
+                                 * operation; it only takes the launch latency off the critical path.
+                                 * llm_cuda_sample_batch_static ignores the flag (always strict). */
     const float* temperature_rows;        /* device [batch] or NULL */
     const uint32_t* top_k_rows;           /* device [batch] or NULL */
     const float* top_p_rows;              /* device [batch] or NULL */

@@ -208,6 +208,7 @@ bool scalar_greedy(const llm_cuda_sample_args* a) { return a->temperature_rows =
 // Plans and launches the streaming kernel (rows it cannot decide are ordered in full by their own CTA).
 int32_t run_select(llm_cuda_sampler* s, const llm_cuda_sample_args* a, KParams& P) {
     LaunchPlan plan{};
+    P.full_keys_wanted = 1u;  // this handle owns full-ordering scratch: rows a sampled threshold cannot decide have somewhere to go
     const bool k_known = (a->top_k_rows == nullptr);
     const uint32_t k_hint = scalar_greedy(a) ? 1u : a->top_k;
     // lists the split scratch can hold at this launch's list length
@@ -242,6 +243,7 @@ int32_t run_select(llm_cuda_sampler* s, const llm_cuda_sample_args* a, KParams& 
     P.full_slots = s->full_slots;
     P.full_vpad = s->vpad;
     P.full_nslots = s->nslots;
+    P.wait_first = a->overlap_previous == 2u ? 1u : 0u;
     CUDA_TRY(s, launch_stream_select(P, plan, stream, a->overlap_previous != 0u));
     s->last_kernels++;
     return LLM_CUDA_OK;

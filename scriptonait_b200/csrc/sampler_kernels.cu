@@ -170,11 +170,14 @@ __device__ __forceinline__ uint32_t warp_rth_largest(uint32_t key, uint32_t r, u
 // After all candidates of a row are in cand[0..n): final selection, ordering
 // and either the ordered tail (token out) or the candidate list out. `scratch`
 // is EPILOGUE_SCRATCH bytes of shared memory nothing else uses any more.
+// `need_k`: the candidates came from a sampled threshold, and only decide the row if at least k_eff of them exist.
 __device__ int finish_row(const KParams& P, uint32_t b, const RowCfg& rc, uint32_t n, bool overflow, float qmax, Shared& S,
-                           float* cand_q, uint32_t* cand_i, unsigned char* scratch, bool window_filtered = false) {
+                           float* cand_q, uint32_t* cand_i, unsigned char* scratch, bool window_filtered = false,
+                           bool need_k = false) {
     uint64_t* keys64 = reinterpret_cast<uint64_t*>(scratch);                     // THREADS 64-bit words
     float* probs = reinterpret_cast<float*>(scratch + (size_t)THREADS * 8u);     // up to MAX_SORT floats
     if (!rc.windowed) {
+        if (need_k && !overflow && n < rc.k_eff) return 2;  // the sampled threshold was too high for this row
         // a set the rank sort below takes in one go needs no selection first: it is cut after sorting
         if (n > (uint32_t)THREADS) n = keep_top_k(n, rc.k_eff, S, cand_q, cand_i);
     } else if (!overflow) {
@@ -966,6 +969,9 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
     const uint32_t b = blockIdx.y, shard = blockIdx.x, tid = threadIdx.x;
     const unsigned lane = tid & 31u, warp = tid >> 5;
     const uint32_t LOWEST = 0x007fffffu;  // okey(-inf)
+    // overlap_previous = 2: the grid was set up while its predecessor was still running (its CTAs are resident,
+    // the launch latency is paid), but it touches no global memory before that kernel has completed
+    if (P.wait_first) grid_dependency_wait();
     // A launch that asked to overlap its predecessor is released by the producer lane of every CTA
     // once three eighths of the CTA's row have been requested (measured best: released at the very
     // start, three launches stream at once and then order at once). That launch reads its inputs and
@@ -1035,7 +1041,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
     __syncthreads();  // the one barrier all STREAM_THREADS threads share
     RowCfg rc = S.rc;
     if (MODE == 1) rc.windowed = 1u;  // lets the compiler drop the exact-selection code
-    if (MODE == 2) rc.windowed = 0u;  // ... or the window code
+    if (MODE >= 2) rc.windowed = 0u;  // ... or the window code
     PHASE(0);
     PHASE(12);
     if (rc.invalid || P.force_full) {
@@ -1244,8 +1250,20 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
     // than two or three values share a quotient); the exact selection afterwards works on the quotients.
     const uint32_t tau_slack = (T == 1.0f) ? 0u : 4u;
     auto lowered = [&](uint32_t key) { return key > LOWEST + tau_slack ? key - tau_slack : LOWEST; };
+    // Rank cuts above 64 on rows this CTA holds whole: the lanes' maxima bound the k-th largest value only
+    // loosely then (thousands of vectors get flagged), so the threshold is SAMPLED instead - the r-th
+    // largest of the 256 threads' maxima over the first stage, r chosen so that about 1.6 k values of the
+    // row are expected at or above it - and kept for the whole sweep. Exactness does not rest on the
+    // estimate: every value at or above the threshold is captured, so if at least k are, the k largest are
+    // among them; a row where fewer are is ordered in full instead (an order that rises along the row). r: with
+    // S values in the first stage, r0 = k S / V of the k largest are expected among them, and the r-th
+    // largest sampled value has about r (1 - 1/sqrt(r)) V/S ... r (1 + 1/sqrt(r)) V/S row values at or above
+    // it: r = (2.5 + sqrt(6.25 + r0))^2 leaves five standard deviations of room above k.
+    // MODE 3 (chosen by the launch plan: a scalar rank cut above 64 and at most an eighth of the row, rows
+    // not split, tokens wanted): every non-greedy row of the launch is sampled this way.
+    const bool sampled = (MODE == 3) && rc.k_eff > 1u;
     float lmin = neg_inf();   // m_lane > 1: the lane's m-th best so far
-    if (m_lane > 1u)
+    if (m_lane > 1u && !sampled)
         for (uint32_t i = 0; i < m_lane; ++i)
             if (IN_BOUNDS(i * THREADS + tid, P.lane_top_words)) lane_top[i * THREADS + tid] = neg_inf();
     // the lane's m best, descending, in lane_top[i*THREADS + tid]; returns the new m-th best
@@ -1279,7 +1297,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
             vm[u] = m;  // of the raw values; NaN elements are ignored by the maxima
             if (!BITS && m_lane == 1u) tmax = fmaxf(tmax, m);
         }
-        if (BITS || m_lane > 1u) {
+        if ((BITS || m_lane > 1u) && !sampled) {
             // A value of the edited row is wanted: flagged ids (penalised, blocked) must not count.
             // Only a vector that would change the lane's state is looked up in the bitmap (a lane's
             // best values change O(m log n) times over a row); vm[u] stays the raw maximum, which
@@ -1330,6 +1348,32 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
                 atomicMax(&S.tau_key, raw_threshold_key(window_stream_bound(qmax1), T));
             }
             tau_run = okey_to_float(vol_load(&S.tau_key));
+        } else if (sampled) {
+            if (tt == 0) {
+                const float n_sample = (float)min(nvi * (uint32_t)VEC, VPS * (uint32_t)VEC);
+                const float r0 = (float)rc.k_eff * n_sample / (float)max(ncols, 1u);
+                const float rr = 2.5f + sqrtf(6.25f + r0);
+                const float p_elem = fminf(1.0f, rr * rr / fmaxf(n_sample, 1.0f));
+                // a thread's maximum over its U * VEC sampled values reaches the threshold with probability q
+                const float q_thread = 1.0f - __powf(1.0f - p_elem, (float)(U * VEC));
+                const uint32_t sample_rank = min(250u, max(1u, (uint32_t)(q_thread * (float)THREADS + 0.5f)));
+                // the sample_rank-th largest of the threads' first-stage maxima (absent vectors rank last)
+                float m0 = neg_inf();
+#pragma unroll
+                for (int u = 0; u < U; ++u) m0 = fmaxf(m0, vm[u]);
+                const uint32_t mine = okey(m0);
+                S.hist[0][tid] = mine;
+                cta_sync();
+                uint32_t above = 0u;
+                for (uint32_t j = 0; j < (uint32_t)THREADS; ++j) {
+                    const uint32_t o = S.hist[0][j];
+                    above += (o > mine || (o == mine && j < tid)) ? 1u : 0u;
+                }
+                if (above == sample_rank - 1u) S.tau_key = max(mine, LOWEST);
+                cta_sync();
+                tau_k = S.tau_key;
+            }
+            tau_run = okey_to_float(lowered(tau_k));
         } else {
             const uint32_t h3 = tt / 3u;
             const bool refresh = tt < 4u || (tt & (tt - 1u)) == 0u || (tt == 3u * h3 && (h3 & (h3 - 1u)) == 0u);
@@ -1355,7 +1399,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
         // covers rows too short for a whole vector: only the leading / trailing elements exist
         const uint32_t wk = __reduce_max_sync(FULL_MASK, okey(tmax));
         if (lane == 0) atomicMax(&S.max_key, wk);
-    } else {
+    } else if (!sampled) {
         // every lane's final values go into its warp's bound (a warp still sweeping that reads it early
         // only sees a bound that is valid already)
         const uint32_t kth = warp_bound();
@@ -1375,7 +1419,9 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
         // as the minimum of the warps' bounds (a lower bound of the k-th largest value)
         const float qmaxf = temper(okey_to_float(S.max_key), T);
         float tau;
-        if (sweep_k) {
+        if (sampled) {
+            tau = okey_to_float(lowered(vtiles ? S.tau_key : LOWEST));  // a row too short for one vector was never sampled
+        } else if (sweep_k) {
             uint32_t lo = S.wkth[0];
 #pragma unroll
             for (int w = 1; w < WARPS; ++w) lo = min(lo, S.wkth[w]);
@@ -1562,7 +1608,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
     }
 
     if (P.split == 1u) {
-        const int undecided = finish_row(P, b, rc, n, overflow, qmax, S, cand_q, cand_i, scratch, window_filtered);
+        const int undecided = finish_row(P, b, rc, n, overflow, qmax, S, cand_q, cand_i, scratch, window_filtered, sampled);
 #ifdef LLMC_DEV_TWICE  // experiment: the same tail once more, now with its instructions cached
         if (!undecided) {
             cta_sync();
@@ -1738,6 +1784,7 @@ int plan_launch(const DeviceInfo& dev, const KParams& base, bool top_k_known, ui
     // 2: no row can; 0: decided per row in the kernel
     const bool may_be_greedy = base.t_rows != nullptr || base.temperature <= 0.0f;
     plan->mode = (window_only && !may_be_greedy) ? 1 : ((top_k_known && !window_only) ? 2 : 0);
+    plan->sample_threshold = false;  // decided below, once the split is known
     if (window_only) {
         // an append that falls off the buffer sends the row to the full ordering
         plan->ccap = WINDOW_CAP;
@@ -1775,6 +1822,13 @@ int plan_launch(const DeviceInfo& dev, const KParams& base, bool top_k_known, ui
     if (split < 1u) split = 1u;
     plan->split = split;
     plan->shard_cols = shard_cols;
+    // exact-selection launches with a scalar rank cut above 64 (and at most an eighth of the row) whose rows are
+    // not split and that draw tokens: the threshold is sampled from the first stage (kernel MODE 3)
+    if (plan->mode == 2 && split == 1u && base.out_q == nullptr && base.full_keys_wanted && top_k_hint > 64u &&
+        (uint64_t)top_k_hint * 8u <= base.vocab) {
+        plan->mode = 3;
+        plan->sample_threshold = true;
+    }
     if (plan->bits) {
         plan->bitmap_words = (shard_cols + 8u + 31u) / 32u + 1u;
         // sized for this launch's longest history (the handle's maximum when rows bring their own lengths)
@@ -1877,9 +1931,11 @@ static cudaError_t configure_stream(int v) {
     if ((e = configure_one<ElemT, BITS, 0, 3>(v)) != cudaSuccess) return e;
     if ((e = configure_one<ElemT, BITS, 1, 3>(v)) != cudaSuccess) return e;
     if ((e = configure_one<ElemT, BITS, 2, 3>(v)) != cudaSuccess) return e;
+    if ((e = configure_one<ElemT, BITS, 3, 3>(v)) != cudaSuccess) return e;
     if ((e = configure_one<ElemT, BITS, 0, 4>(v)) != cudaSuccess) return e;
     if ((e = configure_one<ElemT, BITS, 1, 4>(v)) != cudaSuccess) return e;
-    return configure_one<ElemT, BITS, 2, 4>(v);
+    if ((e = configure_one<ElemT, BITS, 2, 4>(v)) != cudaSuccess) return e;
+    return configure_one<ElemT, BITS, 3, 4>(v);
 }
 
 cudaError_t configure_kernels(size_t max_dyn_smem) {
@@ -1927,6 +1983,7 @@ template <typename ElemT, bool BITS>
 static cudaError_t launch_stream_m(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap) {
     if (plan.mode == 1) return launch_stream_u<ElemT, BITS, 1>(P, plan, stream, overlap);
     if (plan.mode == 2) return launch_stream_u<ElemT, BITS, 2>(P, plan, stream, overlap);
+    if (plan.mode == 3) return launch_stream_u<ElemT, BITS, 3>(P, plan, stream, overlap);
     return launch_stream_u<ElemT, BITS, 0>(P, plan, stream, overlap);
 }
 

@@ -70,6 +70,8 @@ struct KParams {
     uint32_t* out_cnt;
     uint32_t out_stride;
     uint32_t force_full;
+    uint32_t full_keys_wanted;      // host only: the launch will have full-ordering scratch (the plan may pick variants that need it)
+    uint32_t wait_first;            // launched early (programmatic dependent launch) but must read nothing before the preceding kernel has completed
     // full ordering of the rare rows the stream cannot decide: scratch slots claimed by the row's own CTA
     unsigned long long* full_keys;  // [full_nslots][4][full_vpad] 32-bit words (keys in/out, column indices in/out), or NULL = no such stage
     float* full_vals;               // [full_nslots][full_vpad]
@@ -93,7 +95,9 @@ struct LaunchPlan {
         cand_off, scratch_off, tables_off, vlist_cap, stage_u;  // stage_u: 16-byte vectors per consumer thread and ring stage (3 or 4)
     size_t smem;
     bool bits;  // mask or penalty tables needed
-    int mode;   // kernel variant: 0 rows of either kind, 1 window-mode rows only, 2 exact-selection rows only
+    bool sample_threshold;
+    int mode;   // kernel variant: 0 rows of either kind, 1 window-mode rows only, 2 exact-selection rows only,
+                // 3 exact-selection rows whose threshold is sampled from the first stage (rank cuts above 64)
 };
 
 // Raises the dynamic shared-memory limit of every kernel; once per device.

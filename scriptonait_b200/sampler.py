@@ -264,7 +264,7 @@ class Sampler:
                             allowed_bits=allowed_bits, allowed_len=allowed_len, eos_id=eos_id, seeds=seeds,
                             draw_index=draw_index, seed_base=seed_base, uniforms=uniforms, split=split,
                             force_full_sort=force_full_sort, stream=st, keep=keep)
-        a.overlap_previous = 1 if overlap_previous else 0
+        a.overlap_previous = int(overlap_previous)  # False/True, or 2 = early launch with strict data order
         res = self._outputs(a, B, trace, kept_capacity, out_tokens, logits.device)
         if want_penalized and a.history:
             res.penalized = torch.full((B, int(a.history_stride)), float("nan"), dtype=torch.float32, device=logits.device)
