@@ -455,6 +455,38 @@ __device__ __forceinline__ void sort_small(uint32_t n, Shared& S, float* cand_q,
     cta_sync();
 }
 
+// Sorts cand[0..n), THREADS < n <= 2048, into the reference ordering: a bitonic network over the 64-bit
+// composite keys alone (one 8-byte word per entry in `keys`, room for the next power of two; padding keys
+// are 0 and sort last), from which values and ids are read back afterwards (a value's ordered key is
+// exact except that -0.0 comes back as +0.0, which no later stage can tell apart).
+__device__ __forceinline__ void sort_keys64(uint32_t n, float* cand_q, uint32_t* cand_i, uint64_t* keys) {
+    uint32_t m = 1u;
+    while (m < n) m <<= 1;
+    for (uint32_t i = threadIdx.x; i < m; i += THREADS) keys[i] = i < n ? composite(cand_q[i], cand_i[i]) : 0ull;
+    cta_sync();
+    for (uint32_t size = 2u; size <= m; size <<= 1) {
+        for (uint32_t stride = size >> 1; stride > 0u; stride >>= 1) {
+            for (uint32_t t = threadIdx.x; t < (m >> 1); t += THREADS) {
+                const uint32_t lo = ((t & ~(stride - 1u)) << 1) | (t & (stride - 1u));
+                const uint32_t hi = lo + stride;
+                const bool descending_block = ((lo & size) == 0u);  // first-in-order (largest key) at the low slot
+                const uint64_t kl = keys[lo], kh = keys[hi];
+                if ((kh > kl) == descending_block) {
+                    keys[lo] = kh;
+                    keys[hi] = kl;
+                }
+            }
+            cta_sync();
+        }
+    }
+    for (uint32_t i = threadIdx.x; i < n; i += THREADS) {
+        const uint64_t k = keys[i];
+        cand_q[i] = okey_to_float((uint32_t)(k >> 32));
+        cand_i[i] = ~(uint32_t)k;
+    }
+    cta_sync();
+}
+
 // Sorts cand[0..n), n > THREADS, into the reference ordering with a bitonic network; slots [n, m)
 // (m the next power of two) are filled with entries that sort last.
 __device__ __forceinline__ void sort_candidates(uint32_t n, float* cand_q, uint32_t* cand_i) {

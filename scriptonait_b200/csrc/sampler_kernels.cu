@@ -203,6 +203,8 @@ __device__ int finish_row(const KParams& P, uint32_t b, const RowCfg& rc, uint32
     const bool small_tail = small && !P.out_q && !rc.greedy;
     if (small)
         sort_small(n, S, cand_q, cand_i, keys64, S.hist[0], probs, small_tail);
+    else if (n <= 2048u)
+        sort_keys64(n, cand_q, cand_i, keys64);  // 2048 keys take the sort-key words and the (not yet used) probabilities' space
     else
         sort_candidates(n, cand_q, cand_i);
     PHASE(4);
