@@ -340,45 +340,51 @@ __device__ __forceinline__ float lm_okey_to_float(uint32_t k) {
 // T != 1, since neighbouring floats can share a quotient x / T - and the probe logits at or above it become
 // the row's first candidates. Any threshold keeps the result exact (the merge step checks that enough
 // logits reached it); it only has to land where a few times top_k logits of the row pass. `exact` (small
-// vocabularies, probed whole): a radix select over ordered keys, 8 bits a pass. Otherwise every thread
-// takes the maximum of its share of the probe, and the rank-th largest of those 256 maxima is used: at
-// least `rank` probe logits reach it and, the top values nearly always sitting with different threads,
-// hardly more. One CTA per row.
-__global__ void __launch_bounds__(256) probe_threshold_kernel(const LmParams P, uint32_t rank, uint32_t exact) {
-    const uint32_t b = blockIdx.x, tid = threadIdx.x;
+// vocabularies, probed whole): a radix select over ordered keys, 8 bits a pass. Otherwise 256 groups of
+// four threads each take the maximum of their share of the probe, and the rank-th largest of those 256
+// maxima is used: at least `rank` probe logits reach it and, the top values nearly always sitting with
+// different groups, hardly more. One CTA of 1024 threads per row.
+__global__ void __launch_bounds__(1024) probe_threshold_kernel(const LmParams P, uint32_t rank, uint32_t exact) {
+    const uint32_t b = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;  // 1024 threads: a row's probe is one round of 16-byte loads
     __shared__ uint32_t hist[256];
     __shared__ uint32_t sel_digit, sel_need;
     const float* row = P.probe_out + (size_t)b * P.probe_cols;
+    const float4* row4 = reinterpret_cast<const float4*>(row);  // probe rows are whole tiles of 128 floats
     const uint32_t n = P.probe_cols;
     uint32_t need = rank < 1u ? 1u : rank;
     uint32_t prefix = 0u;
     if (!exact) {
+        // 256 groups of four threads: the rank-th largest of the groups' maxima
         uint32_t best = 0u;  // below every ordered key of a float
-        const float4* row4 = reinterpret_cast<const float4*>(row);  // probe rows are whole tiles of 128 floats
 #pragma unroll 4
-        for (uint32_t i = tid; i < n / 4u; i += 256u) {
+        for (uint32_t i = tid; i < n / 4u; i += nt) {
             const float4 v = __ldg(&row4[i]);
             if (v.x == v.x) best = max(best, lm_okey(v.x));
             if (v.y == v.y) best = max(best, lm_okey(v.y));
             if (v.z == v.z) best = max(best, lm_okey(v.z));
             if (v.w == v.w) best = max(best, lm_okey(v.w));
         }
-        hist[tid] = best;
+        best = max(best, __shfl_xor_sync(0xffffffffu, best, 1));
+        best = max(best, __shfl_xor_sync(0xffffffffu, best, 2));
+        if ((tid & 3u) == 0u) hist[tid >> 2] = best;
         __syncthreads();
-        uint32_t above = 0u;  // maxima that come before this thread's (ties broken by thread id)
-        for (uint32_t j = 0; j < 256u; ++j) {
-            const uint32_t o = hist[j];
-            above += (o > best || (o == best && j < tid)) ? 1u : 0u;
+        if (tid < 256u) {
+            const uint32_t mine = hist[tid];
+            uint32_t above = 0u;  // maxima that come before this group's (ties broken by group number)
+            for (uint32_t j = 0; j < 256u; ++j) {
+                const uint32_t o = hist[j];
+                above += (o > mine || (o == mine && j < tid)) ? 1u : 0u;
+            }
+            if (above == min(need, 256u) - 1u) sel_digit = mine;
         }
-        if (above == min(need, 256u) - 1u) sel_digit = best;
         __syncthreads();
         prefix = sel_digit;
     } else
     for (int pass = 0; pass < 4; ++pass) {
         const int sh = 24 - 8 * pass;
-        hist[tid] = 0u;
+        if (tid < 256u) hist[tid] = 0u;
         __syncthreads();
-        for (uint32_t i = tid; i < n; i += 256u) {
+        for (uint32_t i = tid; i < n; i += nt) {
             const float x = row[i];
             if (x != x) continue;
             const uint32_t key = lm_okey(x);
@@ -399,15 +405,14 @@ __global__ void __launch_bounds__(256) probe_threshold_kernel(const LmParams P, 
         need = sel_need;
         __syncthreads();
     }
-    uint32_t key = prefix;  // ordered key of the rank-th largest probe logit (or of the smallest, if the row has fewer)
+    uint32_t key = prefix;  // ordered key of (about) the rank-th largest probe logit
     const uint32_t lowest = 0x007fffffu;  // ordered key of -inf
     if (P.temperature != 1.0f) key = key > lowest + 4u ? key - 4u : lowest;
     if (key < lowest) key = lowest;
     const float thr = lm_okey_to_float(key);
     if (tid == 0) P.thr[b] = thr;
-    const float4* row4 = reinterpret_cast<const float4*>(row);
 #pragma unroll 4
-    for (uint32_t i4 = tid; i4 < n / 4u; i4 += 256u) {
+    for (uint32_t i4 = tid; i4 < n / 4u; i4 += nt) {
         const float4 q = __ldg(&row4[i4]);
         const float xs[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
@@ -493,7 +498,7 @@ int launch_lm_head(const LmParams& P, const void* embed, const void* x_norm, uin
 }
 
 cudaError_t launch_probe_threshold(const LmParams& P, uint32_t rank, bool exact, cudaStream_t stream) {
-    probe_threshold_kernel<<<P.batch, 256, 0, stream>>>(P, rank, exact ? 1u : 0u);
+    probe_threshold_kernel<<<P.batch, 1024, 0, stream>>>(P, rank, exact ? 1u : 0u);
     return cudaGetLastError();
 }
 

@@ -10,7 +10,11 @@ import oracle
 pytestmark = pytest.mark.gpu
 
 
-def test_batched_decode_loop_matches_a_host_loop_of_sample_with(sampler):
+@pytest.mark.parametrize("early_launch", [0, 2])
+def test_batched_decode_loop_matches_a_host_loop_of_sample_with(sampler, early_launch):
+    """`early_launch` = 2 launches every sampling step with overlap_previous = 2 right behind
+    llm_cuda_advance_rows, which writes the step's history and draw counters: the grid may be set up
+    early but reads nothing before that kernel has completed, so the results must not change."""
     import torch
     g = np.random.default_rng(21)
     B, V, steps, window = 12, 600, 40, 16
@@ -46,7 +50,8 @@ def test_batched_decode_loop_matches_a_host_loop_of_sample_with(sampler):
     tbl = torch.from_numpy(table).to(dev)
     for t in range(steps):
         res = sampler.sample_batch(tbl[t], temperature=0.9, top_k=20, top_p=0.95, repetition_penalty=1.3, history=hist,
-                                   history_len=hlen, seeds=seeds, draw_index=draws, trace=True)
+                                   history_len=hlen, seeds=seeds, draw_index=draws, trace=True,
+                                   overlap_previous=early_launch)
         was_finished = finished.clone()
         sampler.advance_rows(res.tokens, res.row_flags, history=hist, window=window, history_len=hlen, history_pos=hpos,
                              draw_index=draws, finished=finished)
