@@ -316,7 +316,10 @@ int32_t llm_cuda_sampler_create(int32_t device, uint32_t max_batch, uint32_t max
     if ((e = cudaSetDevice(device)) != cudaSuccess) return bail("cudaSetDevice", e);
     if ((e = configure_kernels(s->dev.max_dyn_smem)) != cudaSuccess) return bail("cudaFuncSetAttribute", e);
     s->sc_lists = max_batch > 4096u ? max_batch : 4096u;
-    s->vpad = (max_vocab + 1023u) & ~1023u;
+    // the arrays of a slot, and the slots, start an odd number of 256-byte lines apart: rows that are ordered
+    // side by side step through their arrays together, and a power-of-two spacing would send all of their
+    // traffic to the same few memory channels
+    s->vpad = ((max_vocab + 1023u) & ~1023u) + 1088u;
     // two slots per SM (a batch of such rows then orders at two rows per SM instead of queueing for one): 20
     // bytes per column (two key/index array pairs and the probabilities), at most 2 GiB in all; a CTA that
     // finds every slot taken waits for one (bounded)

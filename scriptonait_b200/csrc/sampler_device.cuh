@@ -49,7 +49,12 @@ constexpr uint32_t STAGE_BYTES = 12288;  // the smaller of the two ring stage si
 constexpr int RING_STAGES = 3;           // bulk copies in flight per CTA: up to RING_STAGES stages
 constexpr uint32_t WINDOW_CAP = 2048;    // candidate buffer of launches whose rows all run in window mode
 constexpr uint32_t MAX_SORT = 4096;      // most candidates the ordered tail takes (its scratch lives in the ring's memory after the sweep)
-constexpr uint32_t EPILOGUE_SCRATCH = (uint32_t)THREADS * 8u + MAX_SORT * 4u;  // sort keys of a rank sort + probabilities
+constexpr uint32_t WINDOW_CAP_WIDE = 4096; // the same, where the ring leaves room for it without costing a resident CTA
+// Probabilities of up to MAX_SORT candidates. The sort keys share it: a rank sort (at most THREADS entries)
+// keeps its keys in the last THREADS * 8 bytes, which its own probabilities never reach; the key-only
+// network (at most 2048 entries) takes the whole block before any probability exists.
+constexpr uint32_t EPILOGUE_SCRATCH = MAX_SORT * 4u;
+constexpr uint32_t RANK_KEYS_OFF = EPILOGUE_SCRATCH - (uint32_t)THREADS * 8u;
 static_assert((size_t)THREADS * 8u + (size_t)MAX_SORT * 4u <= (size_t)RING_STAGES * STAGE_BYTES, "epilogue scratch");
 constexpr unsigned FULL_MASK = 0xffffffffu;
 constexpr uint32_t EMPTY_KEY = 0xffffffffu;
@@ -247,6 +252,7 @@ struct Shared {
     uint32_t hist[2][256];  // radix-select histograms, alternated between passes
     float f_sum, f_total, f_u, f_r, f_thr;
     uint32_t token, out_flags, kept_n, walk_end;
+    uint32_t ex_done, ex_all;  // rounds of the flagged-vector examination that ran / that the list holds
 };
 
 // Warp-collective append of passing lanes to the candidate buffer. `end` tracks
@@ -320,10 +326,12 @@ __device__ __forceinline__ uint32_t compact_inplace(uint32_t n, Pred keep, Share
 // Radix select over the 64-bit composite keys of cand[0..n): finds (shift, thr)
 // such that exactly k entries satisfy (composite >> shift) >= thr. Requires
 // 1 <= k < n. Eight bits per pass from the top; stops as soon as the bucket that
-// holds the k-th entry is wanted whole. Lanes that hit the same bin are combined
-// with match_any before the shared-memory atomic (the top bytes of float keys are
-// nearly constant, so a plain histogram would serialise on one address); the
-// 256-bin scan is done redundantly by every warp, so a pass costs two barriers.
+// holds the k-th entry is wanted whole. A warp whose active lanes all hit the same
+// bin adds once (the top bytes of float keys are nearly constant, and a plain
+// histogram would serialise on one address); otherwise every lane adds for itself
+// (`match_any` takes a step per distinct digit, far more than the few conflicts of
+// mixed digits cost). The 256-bin scan is done redundantly by every warp, so a pass
+// costs two barriers.
 __device__ __forceinline__ void radix_select(uint32_t n, uint32_t k, Shared& S, const float* cand_q, const uint32_t* cand_i,
                                              uint64_t& thr, int& shift) {
     uint64_t prefix = 0ull;
@@ -344,9 +352,14 @@ __device__ __forceinline__ void radix_select(uint32_t n, uint32_t k, Shared& S, 
                 digit = (uint32_t)(c >> sh) & 255u;
             }
             const unsigned am = __ballot_sync(FULL_MASK, act);
-            if (act) {
-                const unsigned peers = __match_any_sync(am, digit);
-                if ((int)lane == __ffs(peers) - 1) atomicAdd(&H[digit], (uint32_t)__popc(peers));
+            if (am) {
+                const int src = __ffs(am) - 1;
+                const uint32_t d0 = __shfl_sync(FULL_MASK, digit, src);
+                if (__all_sync(FULL_MASK, !act || digit == d0)) {
+                    if ((int)lane == src) atomicAdd(&H[d0], (uint32_t)__popc(am));
+                } else if (act) {
+                    atomicAdd(&H[digit], 1u);
+                }
             }
         }
         S.hist[(p + 1) & 1][threadIdx.x] = 0u;  // last read two barriers ago

@@ -174,8 +174,9 @@ __device__ __forceinline__ uint32_t warp_rth_largest(uint32_t key, uint32_t r, u
 __device__ int finish_row(const KParams& P, uint32_t b, const RowCfg& rc, uint32_t n, bool overflow, float qmax, Shared& S,
                            float* cand_q, uint32_t* cand_i, unsigned char* scratch, bool window_filtered = false,
                            bool need_k = false) {
-    uint64_t* keys64 = reinterpret_cast<uint64_t*>(scratch);                     // THREADS 64-bit words
-    float* probs = reinterpret_cast<float*>(scratch + (size_t)THREADS * 8u);     // up to MAX_SORT floats
+    float* probs = reinterpret_cast<float*>(scratch);                               // up to MAX_SORT floats
+    uint64_t* rank_keys = reinterpret_cast<uint64_t*>(scratch + RANK_KEYS_OFF);     // THREADS 64-bit words, past probs[THREADS)
+    uint64_t* net_keys = reinterpret_cast<uint64_t*>(scratch);                      // 2048 keys, before any probability exists
     if (!rc.windowed) {
         if (need_k && !overflow && n < rc.k_eff) return 2;  // the sampled threshold was too high for this row
         // a set the rank sort below takes in one go needs no selection first: it is cut after sorting
@@ -202,9 +203,9 @@ __device__ int finish_row(const KParams& P, uint32_t b, const RowCfg& rc, uint32
     const bool small = n <= (uint32_t)THREADS;
     const bool small_tail = small && !P.out_q && !rc.greedy;
     if (small)
-        sort_small(n, S, cand_q, cand_i, keys64, S.hist[0], probs, small_tail);
+        sort_small(n, S, cand_q, cand_i, rank_keys, S.hist[0], probs, small_tail);
     else if (n <= 2048u)
-        sort_keys64(n, cand_q, cand_i, keys64);  // 2048 keys take the sort-key words and the (not yet used) probabilities' space
+        sort_keys64(n, cand_q, cand_i, net_keys);
     else
         sort_candidates(n, cand_q, cand_i);
     PHASE(4);
@@ -384,20 +385,38 @@ __device__ uint32_t acquire_full_slot(const KParams& P) {
     return 0xffffffffu;
 }
 
+// Shared-memory words of the full ordering's working area (`work`): the radix sort's tables, then the
+// chains' staging ring.
+constexpr uint32_t WORK_HIST = 0u;      // [2][256] digit histograms: this pass's, and the next pass's while keys are moved
+constexpr uint32_t WORK_BASE = 512u;    // [256] where the next key of every digit goes
+constexpr uint32_t WORK_WTOT = 768u;    // [2][32] per-warp totals (two sets)
+constexpr uint32_t WORK_DELTA = 832u;   // [256] per digit: position in the output minus position in the reordered tile
+constexpr uint32_t WORK_WRUN = 1088u;   // [2][WARPS][256] per-warp digit counts of a tile (two sets, used alternately)
+constexpr uint32_t WORK_TILE = WORK_WRUN + 2u * (uint32_t)WARPS * 256u;  // [2][1024] a tile's keys and columns, ordered by digit
+constexpr uint32_t WORK_CHAIN = WORK_TILE + 2048u;                        // [2][CHAIN_CHUNK] floats + 16
+constexpr uint32_t CHAIN_CHUNK = 256u;
+constexpr uint32_t WORK_WORDS = WORK_CHAIN + 2u * CHAIN_CHUNK + 16u;  // + the pad a walk reads past the second buffer
+static_assert(512u + WORK_WORDS * 4u <= RING_STAGES * STAGE_BYTES, "the full ordering's working area lives in the ring");
+
 // A chain of dependent rounded f32 operations acc = op(acc, vals[i]) over vals[0..n), in order, run by
-// the calling warp: all lanes fetch 128 values at a time with one coalesced 16-byte load each (the
-// next chunk already requested) into a double-buffered shared-memory stage, and lane 0 walks the
-// stage with 16-byte shared loads, so the chain costs about its own dependent latency and not one
-// memory round trip per term. Every lane returns the same result.
-//   hit(before, after, v)  evaluated for every element; the chain stops at the first element where it
-//                          holds: its index is returned and acc is left as it was after that element.
+// the calling warp: all lanes fetch CHAIN_CHUNK values at a time with coalesced 16-byte loads (two
+// chunks ahead of the one being walked) into a double-buffered shared-memory stage, and lane 0 walks
+// the stage eight values at a time, the next eight already in registers, with no test or branch inside 64, so the chain costs about
+// its own dependent latency (under five cycles a term) and not one memory round trip per term. Every
+// lane returns the same result.
+//   hit(before, after, v)  the chain stops at the first element where it holds: its index is returned
+//                          and acc is left as it was after that element.
+//   any_hit(after)         asked after every 64 elements with the value acc has then: true iff
+//                          hit held for one of them (the caller's chains are monotone, so the last
+//                          value tells); only then are the 64 walked again one by one. A test and a
+//                          branch cost about fifty cycles, ten additions' worth.
 //   rest_is_noop(v0, acc)  asked once per chunk with the chunk's first value: true means no later
 //                          element can change acc or hit (values are in descending order), so stop.
 // Returns n when nothing hit. Elements past n read as 0.0f, which op must leave acc unchanged for.
-// `vals` is 16-byte aligned; `stage` holds 256 floats.
-template <class Op, class Hit, class Noop>
-__device__ __forceinline__ uint32_t warp_chain(const float* vals, uint32_t n, float& acc, Op op, Hit hit, Noop rest_is_noop,
-                                               float* stage) {
+// `vals` is 16-byte aligned; `stage` holds 2 * CHAIN_CHUNK + 16 floats.
+template <class Op, class Hit, class AnyHit, class Noop>
+__device__ __forceinline__ uint32_t warp_chain(const float* vals, uint32_t n, float& acc_io, Op op, Hit hit, AnyHit any_hit,
+                                               Noop rest_is_noop, float* stage) {
     const unsigned lane = threadIdx.x & 31u;
     auto fetch = [&](uint32_t i) {  // four consecutive values starting at i (a multiple of 4), zero past n
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -410,94 +429,222 @@ __device__ __forceinline__ uint32_t warp_chain(const float* vals, uint32_t n, fl
         }
         return v;
     };
-    float4 next = fetch(lane * 4u);
+    // a chunk: lane l holds values [4 l, 4 l + 4) and [128 + 4 l, 128 + 4 l + 4)
+    float4 a0 = fetch(lane * 4u), a1 = fetch(128u + lane * 4u);
+    float4 b0 = fetch(CHAIN_CHUNK + lane * 4u), b1 = fetch(CHAIN_CHUNK + 128u + lane * 4u);
     uint32_t result = n;
-    for (uint32_t i0 = 0; i0 < n; i0 += 128u) {
-        float* buf = stage + ((i0 >> 7) & 1u) * 128u;
-        *reinterpret_cast<float4*>(buf + lane * 4u) = next;
+    float acc = acc_io;
+    for (uint32_t i0 = 0; i0 < n; i0 += CHAIN_CHUNK) {
+        float* buf = stage + ((i0 / CHAIN_CHUNK) & 1u) * CHAIN_CHUNK;
+        *reinterpret_cast<float4*>(buf + lane * 4u) = a0;
+        *reinterpret_cast<float4*>(buf + 128u + lane * 4u) = a1;
         __syncwarp();
-        next = fetch(i0 + 128u + lane * 4u);
+        a0 = b0;
+        a1 = b1;
+        b0 = fetch(i0 + 2u * CHAIN_CHUNK + lane * 4u);
+        b1 = fetch(i0 + 2u * CHAIN_CHUNK + 128u + lane * 4u);
         int stop = 0;
         if (lane == 0) {
             if (rest_is_noop(buf[0], acc)) {
                 stop = 1;
             } else {
-                const uint32_t m = min(128u, n - i0);
-                uint32_t first = 0xffffffffu;
-                float acc_at = acc;
-#pragma unroll 4
-                for (uint32_t j = 0; j < 128u; j += 4u) {
-                    const float4 v = *reinterpret_cast<const float4*>(buf + j);
-                    const float e[4] = {v.x, v.y, v.z, v.w};
+                const uint32_t m = min(CHAIN_CHUNK, n - i0);
+                const float4* b4 = reinterpret_cast<const float4*>(buf);
+                float4 p = b4[0], q = b4[1];
+#pragma unroll 1
+                for (uint32_t j = 0; j < CHAIN_CHUNK; j += 64u) {
+                    const float before = acc;
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        const float before = acc;
-                        acc = op(acc, e[c]);
-                        if (first == 0xffffffffu && j + (uint32_t)c < m && hit(before, acc, e[c])) {
-                            first = j + (uint32_t)c;
-                            acc_at = acc;
-                        }
+                    for (uint32_t s8 = 0; s8 < 8u; ++s8) {
+                        // the next eight (past the chunk's end: the other buffer or the pad, never used)
+                        const float4 p2 = b4[(j >> 2) + 2u * s8 + 2u], q2 = b4[(j >> 2) + 2u * s8 + 3u];
+                        acc = op(acc, p.x); acc = op(acc, p.y); acc = op(acc, p.z); acc = op(acc, p.w);
+                        acc = op(acc, q.x); acc = op(acc, q.y); acc = op(acc, q.z); acc = op(acc, q.w);
+                        p = p2;
+                        q = q2;
                     }
-                }
-                if (first != 0xffffffffu) {
-                    stop = 2;
-                    acc = acc_at;
-                    result = i0 + first;
+                    if (any_hit(acc)) {
+                        float again = before;
+                        for (uint32_t e = 0; e < 64u && j + e < m; ++e) {
+                            const float was = again;
+                            again = op(again, buf[j + e]);
+                            if (hit(was, again, buf[j + e])) {
+                                acc = again;
+                                result = i0 + j + e;
+                                stop = 2;
+                                break;
+                            }
+                        }
+                        if (stop) break;
+                    }
                 }
             }
         }
         stop = __shfl_sync(FULL_MASK, stop, 0);
         if (stop) break;
     }
-    acc = __shfl_sync(FULL_MASK, acc, 0);
+    acc_io = __shfl_sync(FULL_MASK, acc, 0);
     return __shfl_sync(FULL_MASK, result, 0);
 }
 
+// The full ordering's four chains, each a function of its own: inlined into their caller they would
+// share its registers, and a spilled value of the walking lane costs a trip to L2 per step.
+//   sum of the exponentials (generate.rs:386-389): once the sum is >= 1 a term below 2^-24 is under half
+//   an ulp and leaves it unchanged, and the terms only get smaller: adding them and stopping are the same
+__device__ __noinline__ float chain_sum(const float* vals, uint32_t n, float* stage) {
+    float s = 0.0f;
+    warp_chain(
+        vals, n, s, [](float acc, float e) { return __fadd_rn(acc, e); }, [](float, float, float) { return false; },
+        [](float) { return false; }, [](float e0, float acc) { return e0 < 5.9604644775390625e-08f && acc >= 1.0f; }, stage);
+    return s;
+}
+//   cumulative probability up to the first entry that reaches top_p (generate.rs:396-403), or over all n
+//   entries when top_p is 1; a term below `tiny` (2^-26 of the leader) is under half an ulp of any running
+//   sum, which is at least the leader's share: it changes nothing, and neither does anything after it.
+//   The running sum never falls: it has reached top_p inside a block iff it is there at the block's end.
+__device__ __noinline__ uint32_t chain_cumulative(const float* vals, uint32_t n, float top_p, float tiny, float* total_io, float* stage) {
+    float total = *total_io;
+    auto add = [](float acc, float p) { return __fadd_rn(acc, p); };
+    auto below_tiny = [=](float p_first, float) { return p_first < tiny; };
+    uint32_t at;
+    if (top_p < 1.0f)
+        at = warp_chain(vals, n, total, add, [=](float, float after, float) { return after >= top_p; },
+                        [=](float after) { return after >= top_p; }, below_tiny, stage);
+    else
+        at = warp_chain(vals, n, total, add, [](float, float, float) { return false; }, [](float) { return false; }, below_tiny, stage);
+    *total_io = total;
+    return at;
+}
+//   the draw's walk (generate.rs:411-417) stops at the first entry with r < p. r starts at u * total >= 0,
+//   and r - p rounds to a negative number exactly when r < p; from there on it only falls: a block holds
+//   that entry iff r is negative at the block's end
+__device__ __noinline__ uint32_t chain_walk(const float* vals, uint32_t n, float r, float* stage) {
+    return warp_chain(
+        vals, n, r, [](float acc, float p) { return __fsub_rn(acc, p); }, [](float before, float, float p) { return before < p; },
+        [](float after) { return after < 0.0f; }, [](float, float) { return false; }, stage);
+}
+
+// What the full ordering needs to read one row the way the reference edits it. Held by value in the
+// functions that stream the row: fields of the launch parameters, reached through a reference, would
+// have to be read again after every store to scratch.
+struct RowSource {
+    const void* row;               // first logit of the row
+    const uint32_t* allowed_bits;  // or NULL
+    const uint32_t* hkeys;         // id -> occurrences table of the row's history
+    const uint32_t* hcnt;
+    uint32_t bf16, vocab, col_offset, eos_id, allowed_len, hash_slots, has_pen;
+    float pen, T;
+};
+
+__device__ __forceinline__ RowSource row_source(const KParams& P, uint32_t b, const RowCfg& rc, const uint32_t* hkeys, const uint32_t* hcnt) {
+    RowSource R;
+    R.bf16 = P.dtype == LLM_CUDA_DTYPE_BF16 ? 1u : 0u;
+    R.row = R.bf16 ? static_cast<const void*>(reinterpret_cast<const uint16_t*>(P.logits) + (size_t)b * P.row_stride)
+                   : static_cast<const void*>(reinterpret_cast<const float*>(P.logits) + (size_t)b * P.row_stride);
+    R.allowed_bits = P.allowed_bits;
+    R.hkeys = hkeys;
+    R.hcnt = hcnt;
+    R.vocab = P.vocab;
+    R.col_offset = P.col_offset;
+    R.eos_id = P.eos_id;
+    R.allowed_len = P.allowed_len;
+    R.hash_slots = P.hash_slots;
+    R.has_pen = rc.has_pen;
+    R.pen = rc.pen;
+    R.T = rc.T;
+    return R;
+}
+
+__device__ __forceinline__ float source_load(const RowSource& R, uint32_t c) {
+    if (R.bf16) return load_logit(reinterpret_cast<const uint16_t*>(R.row) + c);
+    return load_logit(reinterpret_cast<const float*>(R.row) + c);
+}
+
+// One logit as the reference orders it: allowed mask (generate.rs:333-341), penalty, temperature.
+__device__ __forceinline__ float source_edit(const RowSource& R, uint32_t c, float x) {
+    const uint32_t gid = R.col_offset + c;
+    if (R.allowed_bits && gid != R.eos_id && gid < R.allowed_len && ((__ldg(&R.allowed_bits[gid >> 5]) >> (gid & 31u)) & 1u) == 0u)
+        x = neg_inf();
+    if (R.has_pen) x = penalize(x, R.pen, hash_count(R.hkeys, R.hcnt, R.hash_slots, gid));
+    return temper(x, R.T);
+}
+
+// Every column of the row as a (key, column) pair in column order; returns this thread's count of
+// values that are not NaN. ~(ordered bits) ascending == value descending; a stable sort from column
+// order gives index ascending among equal values, which is the reference's order. Eight columns per
+// thread and round, their loads travelling together; the loop is kept small enough to need no spill
+// (the streaming kernel runs with almost no L1, and a spilled value costs a trip to L2).
+template <bool EDITS>
+__device__ __forceinline__ uint32_t build_all_keys_t(const RowSource& R, uint32_t* __restrict__ sk, uint32_t* __restrict__ si) {
+    const uint32_t V = R.vocab;
+    const float T = R.T;
+    uint32_t valid = 0u;
+    for (uint32_t c0 = threadIdx.x; c0 < V; c0 += 8u * THREADS) {
+        float x[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const uint32_t c = c0 + (uint32_t)u * THREADS;
+            x[u] = c < V ? source_load(R, c) : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const uint32_t c = c0 + (uint32_t)u * THREADS;
+            if (c >= V) continue;
+            const float q = EDITS ? source_edit(R, c, x[u]) : temper(x[u], T);
+            uint32_t key = 0xffffffffu;  // NaN: behind everything (no value maps here: ~okey(-inf) is 0xff800000)
+            if (q == q) {
+                key = ~okey(q);
+                ++valid;
+            }
+            __stcg(&sk[c], key);
+            __stcg(&si[c], c);
+        }
+    }
+    return valid;
+}
+
+__device__ __noinline__ uint32_t build_all_keys(const RowSource R, uint32_t* __restrict__ sk, uint32_t* __restrict__ si) {
+    if (R.allowed_bits || R.has_pen) return build_all_keys_t<true>(R, sk, si);
+    return build_all_keys_t<false>(R, sk, si);
+}
+
 // The members of a row's significance window, as (key, column) pairs compacted in column order into
-// sk / si; returns their number (the same in every thread). Chunks of 1024 columns in the radix
-// sort's own (warp, step, lane) order, ballots inside a warp, warp totals across the CTA.
-__device__ __noinline__ uint32_t build_window_keys(const KParams& P, uint32_t b, const RowCfg& rc, float win_qmax, uint32_t* sk,
-                                                   uint32_t* si, const uint32_t* hkeys, const uint32_t* hcnt, uint32_t* work) {
+// sk / si (`cap` entries each); returns their number (the same in every thread). Rounds of 2048
+// columns: warp w takes columns [256 w, 256 w + 256) of the round, 32 consecutive columns per step, so
+// (warp, step, lane) order is column order; ballots place a member inside its warp, warp totals (one
+// barrier per round, two sets of totals used alternately) place the warp.
+template <bool EDITS>
+__device__ __forceinline__ uint32_t build_window_keys_t(const KParams& P, const RowSource& R, float win_qmax, uint32_t* __restrict__ sk,
+                                                        uint32_t* __restrict__ si, uint32_t cap, uint32_t* work) {
     const uint32_t tid = threadIdx.x;
     const unsigned lane = tid & 31u, warp = tid >> 5;
-    const uint32_t V = P.vocab;
-    // the window's members, compacted in column order: chunks of 1024 columns in the sort's own
-    // (warp, step, lane) order, ballots inside a warp, warp totals across the CTA
-    uint32_t* wtot = work + 512;
+    const unsigned below = (1u << lane) - 1u;
+    const uint32_t V = R.vocab;
+    constexpr int STEPS = 8;
+    const float T = R.T;
     uint32_t run_base = 0u;  // the same in every thread
-    for (uint32_t chunk = 0; chunk < V; chunk += 1024u) {
-        float x[4];
+    uint32_t it = 0u;
+    for (uint32_t chunk = 0; chunk < V; chunk += (uint32_t)STEPS * THREADS, ++it) {
+        const uint32_t c0 = chunk + warp * (uint32_t)STEPS * 32u + lane;
+        float q[STEPS];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const uint32_t c = chunk + warp * 128u + (uint32_t)e * 32u + lane;
-            x[e] = 0.0f;
-            if (c < V) {
-                if (P.dtype == LLM_CUDA_DTYPE_BF16)
-                    x[e] = load_logit(reinterpret_cast<const uint16_t*>(P.logits) + (size_t)b * P.row_stride + c);
-                else
-                    x[e] = load_logit(reinterpret_cast<const float*>(P.logits) + (size_t)b * P.row_stride + c);
-            }
+        for (int e = 0; e < STEPS; ++e) {
+            const uint32_t c = c0 + (uint32_t)e * 32u;
+            q[e] = c < V ? source_load(R, c) : 0.0f;
         }
-        uint32_t key[4], pos[4], wcount = 0u;
-        bool in[4];
+        uint32_t mine = 0u, wcount = 0u;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const uint32_t c = chunk + warp * 128u + (uint32_t)e * 32u + lane;
-            in[e] = false;
-            key[e] = 0u;
+        for (int e = 0; e < STEPS; ++e) {
+            const uint32_t c = c0 + (uint32_t)e * 32u;
+            bool in = false;
             if (c < V) {
-                const uint32_t gid = P.col_offset + c;
-                float xe = x[e];
-                if (id_blocked(P, gid)) xe = neg_inf();
-                if (rc.has_pen) xe = penalize(xe, rc.pen, hash_count(hkeys, hcnt, P.hash_slots, gid));
-                const float q = temper(xe, rc.T);
-                in[e] = (__fsub_rn(q, win_qmax) >= WINDOW_EXACT) || (q == win_qmax);  // false for NaN
-                key[e] = ~okey(q);
+                q[e] = EDITS ? source_edit(R, c, q[e]) : temper(q[e], T);
+                in = (__fsub_rn(q[e], win_qmax) >= WINDOW_EXACT) || (q[e] == win_qmax);  // false for NaN
             }
-            const unsigned m = __ballot_sync(FULL_MASK, in[e]);
-            pos[e] = wcount + (uint32_t)__popc(m & ((1u << lane) - 1u));
-            wcount += (uint32_t)__popc(m);
+            if (in) mine |= 1u << e;
+            wcount += (uint32_t)__popc(__ballot_sync(FULL_MASK, in));
         }
+        uint32_t* wtot = work + WORK_WTOT + (it & 1u) * 32u;
         if (lane == 0) wtot[warp] = wcount;
         cta_sync();
         uint32_t off = run_base, total = 0u;
@@ -508,56 +655,105 @@ __device__ __noinline__ uint32_t build_window_keys(const KParams& P, uint32_t b,
             total += t;
         }
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            if (in[e]) {
-                if (!IN_BOUNDS(off + pos[e], P.full_vpad)) continue;
-                __stcg(&sk[off + pos[e]], key[e]);
-                __stcg(&si[off + pos[e]], chunk + warp * 128u + (uint32_t)e * 32u + lane);
+        for (int e = 0; e < STEPS; ++e) {
+            const bool in = (mine >> e) & 1u;
+            const unsigned m = __ballot_sync(FULL_MASK, in);
+            const uint32_t at = off + (uint32_t)__popc(m & below);
+            off += (uint32_t)__popc(m);
+            if (in && IN_BOUNDS(at, cap)) {
+                __stcg(&sk[at], ~okey(q[e]));
+                __stcg(&si[at], c0 + (uint32_t)e * 32u);
             }
         }
         run_base += total;
-        cta_sync();
     }
+    cta_sync();
     return run_base;
 }
 
-//  least-significant-digit radix sort, 8 bits per pass, by this CTA alone. Per pass: digit
-// histogram, exclusive scan, then a stable scatter in tiles of 1024 keys - warp w takes keys
-// [128 w, 128 w + 128) of the tile, 32 consecutive keys per step, so (warp, step, lane) order is
-// column order; a key's place is its digit's base + the same-digit keys of earlier warps + those
-// earlier in its own warp (`match_any` finds the lanes that share a digit).
+__device__ __noinline__ uint32_t build_window_keys(const KParams& P, const RowSource R, float win_qmax, uint32_t* __restrict__ sk,
+                                                   uint32_t* __restrict__ si, uint32_t cap, uint32_t* work) {
+    if (R.allowed_bits || R.has_pen) return build_window_keys_t<true>(P, R, win_qmax, sk, si, cap, work);
+    return build_window_keys_t<false>(P, R, win_qmax, sk, si, cap, work);
+}
+
+// The lanes of the warp that hold the same 8-bit digit as this one, from one vote per bit (`match_any`
+// takes a step per distinct value, about a thousand cycles for 32 different digits). Lanes without a
+// key (`have` false) match nobody and are matched by nobody.
+__device__ __forceinline__ unsigned digit_peers(uint32_t d, bool have) {
+    unsigned peers = __ballot_sync(FULL_MASK, have);
+#pragma unroll
+    for (int bit = 0; bit < 8; ++bit) {
+        const bool set = (d >> bit) & 1u;
+        const unsigned m = __ballot_sync(FULL_MASK, set);
+        peers &= set ? m : ~m;
+    }
+    return peers;
+}
+
+// One key's digit into a shared-memory histogram: plain additions, except that a digit common to the
+// whole warp (equal keys, key bits that are zero in every value) is added once.
+__device__ __forceinline__ void count_digit(uint32_t* hist, uint32_t d, bool have) {
+    const uint32_t d0 = __shfl_sync(FULL_MASK, d, 0);
+    if (__all_sync(FULL_MASK, have && d == d0)) {
+        if ((threadIdx.x & 31u) == 0u) atomicAdd(&hist[d0], 32u);
+    } else if (have) {
+        atomicAdd(&hist[d], 1u);
+    }
+}
+
+// Least-significant-digit radix sort, 8 bits per pass, by this CTA alone. Per pass: the digit
+// histogram (counted while the previous pass moved the keys, or by a pass of its own), an exclusive
+// scan, then a stable scatter in tiles of 1024 keys - warp w takes keys [128 w, 128 w + 128) of the
+// tile, 32 consecutive keys per step, so (warp, step, lane) order is the order the keys are in. A key's
+// place inside its tile is the tile's keys of smaller digits + the same-digit keys of earlier warps +
+// those earlier in its own warp (one vote per digit bit finds the lanes that share a digit, a returning
+// shared-memory addition counts the earlier steps). The tile is put in that order in shared memory
+// first and written out from there, so that consecutive threads store to consecutive addresses within
+// a digit: scattered 4-byte stores, one memory transaction each, cost more than everything else in
+// the pass together. The next tile's keys are already on their way while this tile is placed.
 // Sorts n_all (key, column) pairs; the pointers are exchanged so that sk / si hold the result.
 __device__ __noinline__ void radix_sort_row(const KParams& P, uint32_t n_all, uint32_t*& sk_io, uint32_t*& si_io, uint32_t*& dk_io, uint32_t*& di_io,
                                             uint32_t* work) {
     const uint32_t tid = threadIdx.x;
     const unsigned lane = tid & 31u, warp = tid >> 5;
+    const unsigned below = (1u << lane) - 1u;
     // local copies: the stores below must not be taken for stores to the caller's pointer variables
     uint32_t* __restrict__ sk = sk_io;
     uint32_t* __restrict__ si = si_io;
     uint32_t* __restrict__ dk = dk_io;
     uint32_t* __restrict__ di = di_io;
-    uint32_t* hist = work;                  // [256]
-    uint32_t* base = work + 256;            // [256]
-    uint32_t* wtot = work + 512;            // [WARPS]
-    uint32_t* wrun = work + 512 + 32;       // [WARPS][256]
+    constexpr int KEYS = 4;
+    constexpr uint32_t TILE = KEYS * (uint32_t)THREADS, WSPAN = KEYS * 32u;
+    uint32_t* gbase = work + WORK_BASE;
+    uint32_t* wtot = work + WORK_WTOT;
+    uint32_t* wtot_tile = work + WORK_WTOT + 32u;
+    uint32_t* delta = work + WORK_DELTA;
+    uint32_t* tk = work + WORK_TILE;
+    uint32_t* ti = tk + TILE;
+    uint32_t cur = 0u;        // which histogram belongs to this pass
+    bool counted = false;     // ... and whether the previous pass filled it
     for (uint32_t shift = 0; shift < 32u; shift += 8u) {
-        hist[tid] = 0u;
-        cta_sync();
-        for (uint32_t i0 = 0; i0 < n_all; i0 += 4u * THREADS) {
-            uint32_t d[4];
+        uint32_t* hist = work + WORK_HIST + cur * 256u;
+        uint32_t* hist_next = work + WORK_HIST + (cur ^ 1u) * 256u;
+        if (!counted) {
+            hist[tid] = 0u;
+            cta_sync();
+            for (uint32_t i0 = 0; i0 < n_all; i0 += 8u * THREADS) {
+                uint32_t kk[8];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const uint32_t i = i0 + (uint32_t)u * THREADS + tid;
-                d[u] = i < n_all ? ((__ldcg(&sk[i]) >> shift) & 255u) : 256u + lane;  // absent: a digit nobody shares
-            }
+                for (int u = 0; u < 8; ++u) {
+                    const uint32_t i = i0 + (uint32_t)u * THREADS + tid;
+                    kk[u] = i < n_all ? __ldcg(&sk[i]) : 0u;
+                }
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const unsigned peers = __match_any_sync(FULL_MASK, d[u]);
-                if (d[u] < 256u && (peers & ((1u << lane) - 1u)) == 0u) atomicAdd(&hist[d[u]], (uint32_t)__popc(peers));
+                for (int u = 0; u < 8; ++u) count_digit(hist, (kk[u] >> shift) & 255u, i0 + (uint32_t)u * THREADS + tid < n_all);
             }
+            cta_sync();
         }
-        cta_sync();
         const uint32_t mine = hist[tid];
+        hist_next[tid] = 0u;
+        counted = false;
         if (cta_sync_or(mine == n_all ? 1 : 0)) continue;  // every key has the same digit: nothing moves
         uint32_t incl = mine;
 #pragma unroll
@@ -566,54 +762,114 @@ __device__ __noinline__ void radix_sort_row(const KParams& P, uint32_t n_all, ui
             if (lane >= (unsigned)o) incl += y;
         }
         if (lane == 31) wtot[warp] = incl;
+        {   // the first tile's per-warp counts start from zero
+            uint32_t* w0 = work + WORK_WRUN;
+#pragma unroll
+            for (uint32_t w = 0; w < (uint32_t)WARPS; ++w) w0[w * 256u + tid] = 0u;
+        }
         cta_sync();
         uint32_t pre = 0u;
         for (uint32_t w = 0; w < warp; ++w) pre += wtot[w];
-        base[tid] = pre + incl - mine;
+        gbase[tid] = pre + incl - mine;
+        const bool count_next = shift < 24u;
+        uint32_t kn[KEYS];
+#pragma unroll
+        for (int e = 0; e < KEYS; ++e) {
+            const uint32_t i = warp * WSPAN + (uint32_t)e * 32u + lane;
+            kn[e] = i < n_all ? __ldcg(&sk[i]) : 0u;
+        }
         cta_sync();
-        for (uint32_t tile = 0; tile < n_all; tile += 1024u) {
-            for (uint32_t j = lane; j < 256u; j += 32u) wrun[warp * 256u + j] = 0u;
-            uint32_t k[4], id[4], d[4], rank[4];
+        uint32_t t = 0u;
+        for (uint32_t tile = 0; tile < n_all; tile += TILE, ++t) {
+            uint32_t* wr = work + WORK_WRUN + (t & 1u) * (uint32_t)WARPS * 256u;
+            uint32_t* wr_other = work + WORK_WRUN + ((t + 1u) & 1u) * (uint32_t)WARPS * 256u;
+            uint32_t k[KEYS], id[KEYS], pos[KEYS];
+            const uint32_t i_first = tile + warp * WSPAN + lane;
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const uint32_t i = tile + warp * 128u + (uint32_t)e * 32u + lane;
-                const bool have = i < n_all;
-                k[e] = have ? __ldcg(&sk[i]) : 0u;
-                id[e] = have ? __ldcg(&si[i]) : 0u;
-                d[e] = have ? ((k[e] >> shift) & 255u) : 256u + lane;
+            for (int e = 0; e < KEYS; ++e) k[e] = kn[e];
+#pragma unroll
+            for (int e = 0; e < KEYS; ++e) {
+                const uint32_t i = i_first + TILE + (uint32_t)e * 32u;
+                kn[e] = i < n_all ? __ldcg(&sk[i]) : 0u;
             }
-            __syncwarp();
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const unsigned peers = __match_any_sync(FULL_MASK, d[e]);
-                const uint32_t lower = (uint32_t)__popc(peers & ((1u << lane) - 1u));
-                rank[e] = d[e] < 256u ? wrun[warp * 256u + d[e]] + lower : 0u;
-                __syncwarp();
-                if (d[e] < 256u && lower == 0u) wrun[warp * 256u + d[e]] += (uint32_t)__popc(peers);
-                __syncwarp();
+            for (int e = 0; e < KEYS; ++e) {  // place among the warp's keys of the same digit
+                const bool have = i_first + (uint32_t)e * 32u < n_all;
+                const uint32_t d = (k[e] >> shift) & 255u;
+                const unsigned peers = digit_peers(d, have);
+                const uint32_t lower = (uint32_t)__popc(peers & below);
+                uint32_t old = 0u;
+                if (have && lower == 0u) old = atomicAdd(&wr[warp * 256u + d], (uint32_t)__popc(peers));  // the earlier steps' count
+                old = __shfl_sync(FULL_MASK, old, have ? __ffs(peers) - 1 : (int)lane);
+                pos[e] = old + lower;
+            }
+            if (count_next) {
+#pragma unroll
+                for (int e = 0; e < KEYS; ++e) count_digit(hist_next, (k[e] >> (shift + 8u)) & 255u, i_first + (uint32_t)e * 32u < n_all);
             }
             cta_sync();
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                if (d[e] < 256u) {
-                    uint32_t off = base[d[e]] + rank[e];
-                    for (uint32_t w = 0; w < warp; ++w) off += wrun[w * 256u + d[e]];
-                    if (!IN_BOUNDS(off, n_all)) continue;
-                    __stcg(&dk[off], k[e]);
-                    __stcg(&di[off], id[e]);
+            for (int e = 0; e < KEYS; ++e) {  // the columns: needed two barriers from here
+                const uint32_t i = i_first + (uint32_t)e * 32u;
+                id[e] = i < n_all ? __ldcg(&si[i]) : 0u;
+            }
+            // digit `tid`: its keys in this tile; the other table is cleared for the next tile
+            uint32_t c = 0u;
+#pragma unroll
+            for (uint32_t w = 0; w < (uint32_t)WARPS; ++w) {
+                c += wr[w * 256u + tid];
+                wr_other[w * 256u + tid] = 0u;
+            }
+            uint32_t before = c;  // becomes the tile's keys of digits up to this one
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t y = __shfl_up_sync(FULL_MASK, before, o);
+                if (lane >= (unsigned)o) before += y;
+            }
+            if (lane == 31) wtot_tile[warp] = before;
+            cta_sync();
+            {
+                uint32_t start = before - c;  // where the digit begins in the reordered tile
+                for (uint32_t w = 0; w < warp; ++w) start += wtot_tile[w];
+                const uint32_t g = gbase[tid];
+                delta[tid] = g - start;
+                gbase[tid] = g + c;
+#pragma unroll
+                for (uint32_t w = 0; w < (uint32_t)WARPS; ++w) {  // the warps' counts become the warps' first positions
+                    const uint32_t cw = wr[w * 256u + tid];
+                    wr[w * 256u + tid] = start;
+                    start += cw;
                 }
             }
             cta_sync();
-            {
-                uint32_t add = 0u;
 #pragma unroll
-                for (uint32_t w = 0; w < (uint32_t)WARPS; ++w) add += wrun[w * 256u + tid];
-                base[tid] += add;
+            for (int e = 0; e < KEYS; ++e) {
+                if (i_first + (uint32_t)e * 32u < n_all) {
+                    const uint32_t at = wr[warp * 256u + ((k[e] >> shift) & 255u)] + pos[e];
+                    if (!IN_BOUNDS(at, TILE)) continue;
+                    tk[at] = k[e];
+                    ti[at] = id[e];
+                }
             }
             cta_sync();
+            const uint32_t m = min(TILE, n_all - tile);
+#pragma unroll
+            for (int e = 0; e < KEYS; ++e) {
+                const uint32_t j = (uint32_t)e * THREADS + tid;
+                if (j < m) {
+                    const uint32_t kk = tk[j];
+                    const uint32_t out = delta[(kk >> shift) & 255u] + j;
+                    if (!IN_BOUNDS(out, n_all)) continue;
+                    __stcg(&dk[out], kk);
+                    __stcg(&di[out], ti[j]);
+                }
+            }
         }
-        uint32_t* t = sk; sk = dk; dk = t;
-        t = si; si = di; di = t;
+        cta_sync();  // the moved keys and the next pass's histogram are complete
+        counted = count_next;
+        cur ^= 1u;
+        uint32_t* tmp = sk; sk = dk; dk = tmp;
+        tmp = si; si = di; di = tmp;
     }
     sk_io = sk;
     si_io = si;
@@ -665,7 +921,7 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
     uint32_t* dk = slot_base + 2u * P.full_vpad;   // keys out
     uint32_t* di = slot_base + 3u * P.full_vpad;   // column indices out
     float* vals = P.full_vals + (size_t)F.slot * P.full_vpad;
-    float* chain_stage = reinterpret_cast<float*>(work + 4096);  // 256 floats, clear of the sort's tables
+    float* chain_stage = reinterpret_cast<float*>(work + WORK_CHAIN);  // clear of the sort's tables
     if (rc.has_pen) {
         const uint32_t* hist = P.history + (size_t)b * P.hist_stride;
         for (uint32_t j = tid; j < rc.hlen; j += THREADS) {
@@ -675,49 +931,24 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
     }
     cta_sync();
     bool filter = try_window;  // this attempt orders the significance window only
+    PHASE(14);
     for (;;) {
     uint32_t n_all = V;        // keys to sort
     // ---- keys: ~(ordered bits) ascending == value descending; a stable sort from column order gives
     //      index ascending among equal values, which is the reference's order
     uint32_t myvalid = 0u;
+    const RowSource R = row_source(P, b, rc, hkeys, hcnt);
     if (filter) {
-        n_all = build_window_keys(P, b, rc, win_qmax, sk, si, hkeys, hcnt, work);
+        n_all = build_window_keys(P, R, win_qmax, sk, si, P.full_vpad, work);
         if (tid == 0) myvalid = n_all;
-    } else
-    for (uint32_t c0 = tid; c0 < V; c0 += 4u * THREADS) {  // four columns per thread and round: their loads travel together
-        float x[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const uint32_t c = c0 + (uint32_t)u * THREADS;
-            x[u] = 0.0f;
-            if (c < V) {
-                if (P.dtype == LLM_CUDA_DTYPE_BF16)
-                    x[u] = load_logit(reinterpret_cast<const uint16_t*>(P.logits) + (size_t)b * P.row_stride + c);
-                else
-                    x[u] = load_logit(reinterpret_cast<const float*>(P.logits) + (size_t)b * P.row_stride + c);
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const uint32_t c = c0 + (uint32_t)u * THREADS;
-            if (c >= V) continue;
-            const uint32_t gid = P.col_offset + c;
-            float xe = x[u];
-            if (id_blocked(P, gid)) xe = neg_inf();
-            if (rc.has_pen) xe = penalize(xe, rc.pen, hash_count(hkeys, hcnt, P.hash_slots, gid));
-            const float q = temper(xe, rc.T);
-            uint32_t key = 0xffffffffu;  // NaN: behind everything (no value maps here: ~okey(-inf) is 0xff800000)
-            if (q == q) {
-                key = ~okey(q);
-                ++myvalid;
-            }
-            __stcg(&sk[c], key);
-            __stcg(&si[c], c);
-        }
+    } else {
+        myvalid = build_all_keys(R, sk, si);
     }
     if (myvalid) atomicAdd(&F.nvalid, myvalid);
     cta_sync();
+    PHASE(3);
     radix_sort_row(P, n_all, sk, si, dk, di, work);
+    PHASE(4);
     const uint32_t n = min(F.nvalid, rc.k_eff);
     // window attempt: the reference's ordering continues past these n entries with values outside the
     // significance window; what that leaves undecided is handled as in the shared-memory path
@@ -737,33 +968,30 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
     if (!done) {
         mx = q_at(0);
         if (tid == 0) F.mx = mx;
-        for (uint32_t i0 = tid; i0 < n; i0 += 4u * THREADS) {
-            float q4[4];
+        for (uint32_t i0 = tid; i0 < n; i0 += 8u * THREADS) {
+            float q8[8];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < 8; ++u) {
                 const uint32_t i = i0 + (uint32_t)u * THREADS;
-                q4[u] = i < n ? q_at(i) : 0.0f;
+                q8[u] = i < n ? q_at(i) : 0.0f;
             }
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < 8; ++u) {
                 const uint32_t i = i0 + (uint32_t)u * THREADS;
-                if (i < n) __stcg(&vals[i], exp_f32(__fsub_rn(q4[u], mx)));
+                if (i < n) __stcg(&vals[i], exp_f32(__fsub_rn(q8[u], mx)));
             }
         }
         cta_sync();
+        PHASE(8);
         if (tid < 32u) {  // warp 0 runs the sequential chains, every lane alike
-            // Once the sum is >= 1 a term below 2^-24 is under half an ulp and leaves it unchanged, and
-            // the terms only get smaller: adding such terms and stopping before them are the same thing.
-            float s = 0.0f;
-            warp_chain(
-                vals, n, s, [](float acc, float e) { return __fadd_rn(acc, e); }, [](float, float, float) { return false; },
-                [](float e0, float acc) { return e0 < 5.9604644775390625e-08f && acc >= 1.0f; }, chain_stage);
+            const float s = chain_sum(vals, n, chain_stage);
             if (tid == 0) {
                 F.sum = s;
                 F.keep = n;
             }
         }
         cta_sync();
+        PHASE(9);
         const float sum = F.sum;
         if ((sum <= 0.0f) || !(fabsf(sum) <= 3.402823466e38f)) {
             if (tid == 0) {
@@ -773,17 +1001,17 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
             done = true;
         }
         if (!done) {
-            for (uint32_t i0 = tid; i0 < n; i0 += 4u * THREADS) {
-                float e4[4];
+            for (uint32_t i0 = tid; i0 < n; i0 += 8u * THREADS) {
+                float e8[8];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
+                for (int u = 0; u < 8; ++u) {
                     const uint32_t i = i0 + (uint32_t)u * THREADS;
-                    e4[u] = i < n ? __ldcg(&vals[i]) : 0.0f;
+                    e8[u] = i < n ? __ldcg(&vals[i]) : 0.0f;
                 }
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
+                for (int u = 0; u < 8; ++u) {
                     const uint32_t i = i0 + (uint32_t)u * THREADS;
-                    if (i < n) __stcg(&vals[i], __fdiv_rn(e4[u], sum));
+                    if (i < n) __stcg(&vals[i], __fdiv_rn(e8[u], sum));
                 }
             }
             cta_sync();
@@ -808,6 +1036,7 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
             // certain when the threshold is at least 2^-24 of the leader
             const bool unknown_tail = truncated && rc.min_p > 0.0f && F.keep == n && rc.min_p < 5.9604644775390625e-08f;
             const bool open_tail = truncated && F.keep == n && !(rc.min_p > 0.0f);  // the kept set continues past the window
+            PHASE(10);
             if (tid < 32u) {
                 const uint32_t keep_minp = F.keep;
                 uint32_t keep = keep_minp;
@@ -815,28 +1044,18 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
                 bool reached = false;
                 const float p0 = __ldcg(&vals[0]);
                 const float tiny = __fmul_rn(p0, 1.4901161193847656e-08f);  // 2^-26 of the leader: below half an ulp of any running sum
-                // a term below `tiny` is under half an ulp of any running sum (which is at least the
-                // leader's share): it changes nothing, and neither does anything after it
-                auto add = [](float acc, float p) { return __fadd_rn(acc, p); };
-                auto below_tiny = [=](float p_first, float) { return p_first < tiny; };
-                if (rc.top_p < 1.0f) {
-                    const float top_p = rc.top_p;
-                    const uint32_t at = warp_chain(vals, keep_minp, total, add,
-                                                   [=](float, float after, float) { return after >= top_p; }, below_tiny, chain_stage);
-                    if (at < keep_minp) {
+                {
+                    const uint32_t at = chain_cumulative(vals, keep_minp, rc.top_p, tiny, &total, chain_stage);
+                    if (rc.top_p < 1.0f && at < keep_minp) {
                         keep = at + 1u;  // the first index whose running sum reaches top_p
                         reached = true;
                     }
-                } else {
-                    warp_chain(vals, keep_minp, total, add, [](float, float, float) { return false; }, below_tiny, chain_stage);
                 }
                 const float u = row_uniform(P, b);
                 float rr = __fmul_rn(u, total);
                 const float r0 = rr;
                 uint32_t flags = LLM_CUDA_ROW_DRAW_CONSUMED;
-                const uint32_t at = warp_chain(
-                    vals, keep, rr, [](float acc, float p) { return __fsub_rn(acc, p); },
-                    [](float before, float, float p) { return before < p; }, [](float, float) { return false; }, chain_stage);
+                const uint32_t at = chain_walk(vals, keep, rr, chain_stage);
                 const bool found = at < keep;
                 // entries past the window add less than half an ulp to the running sums, so `total` is final
                 const bool tail_kept = open_tail && !reached;
@@ -863,6 +1082,7 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
         }
     }
     cta_sync();
+    PHASE(5);
     if (filter && (F.flags & ROW_NEEDS_FULL)) {
         // the window could not settle the row: once more over the whole row
         cta_sync();  // everyone has seen the flags
@@ -905,6 +1125,8 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
         }
     }
     cta_sync();
+    PHASE(6);
+    PHASE(11);
     if (tid == 0) {
         __threadfence();
         atomicExch(&P.full_slots[F.slot], 0u);
@@ -1584,6 +1806,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
         };
         uint32_t v_next;
         uint4 d_next;
+        uint32_t r_done = rounds;
         fetch(0u, v_next, d_next);
 #pragma unroll 1
         for (uint32_t r = 0; r < rounds; ++r) {
@@ -1592,6 +1815,15 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
             fetch(r + 1u, v_next, d_next);
             examine(v < nvi, v, d);
             settle();
+            // a window that has already outgrown the buffer is ordered in global scratch: stop collecting it
+            if (!sweep_k && __any_sync(FULL_MASK, (vol_load(&S.error) & 1u) != 0u)) {
+                r_done = r + 1u;
+                break;
+            }
+        }
+        if (tid == 0) {
+            S.ex_done = r_done;
+            S.ex_all = rounds;
         }
         cta_sync();
         window_filtered = rc.windowed && P.split == 1u;
@@ -1600,7 +1832,10 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
     if (wait_failed) atomicOr(&S.error, 4u);
     cta_sync();
 
-    const uint32_t found_total = S.count;  // every value that passed the exact test was counted, whether or not it still fitted
+    // every value that passed the exact test was counted, whether or not it still fitted; where the collection
+    // stopped early, the count is scaled to the whole list (it only chooses which ordering is tried first)
+    uint32_t found_total = S.count;
+    if (S.ex_done < S.ex_all) found_total = (uint32_t)min((uint64_t)found_total * S.ex_all / max(S.ex_done, 1u), (uint64_t)ncols);
     uint32_t n = min(S.count, P.ccap);
     bool overflow = (S.error & 3u) != 0u;  // window too large, or an append fell off the buffer
     float qmax = temper(okey_to_float(S.max_key), T);
@@ -1882,10 +2117,17 @@ int plan_launch(const DeviceInfo& dev, const KParams& base, bool top_k_known, ui
     const size_t smem_total = ring_bytes + tables_bytes + (aliased ? 0u : cand_bytes);
     if (smem_total > dev.max_dyn_smem) return -1;
     if (aliased) {
+        size_t cb = cand_bytes;
+        // window launches: twice the candidates where the ring has the room anyway (16 KB stages), so that rows
+        // with 2049..4096 significant values are still ordered in shared memory
+        if (window_only && (size_t)WINDOW_CAP_WIDE * 8u + EPILOGUE_SCRATCH <= ring_bytes) {
+            plan->ccap = WINDOW_CAP_WIDE;
+            cb = (size_t)WINDOW_CAP_WIDE * 8u;
+        }
         plan->cand_off = 0u;
-        plan->scratch_off = (uint32_t)cand_bytes;
+        plan->scratch_off = (uint32_t)cb;
         plan->tables_off = (uint32_t)ring_bytes;
-        plan->vlist_cap = (uint32_t)((ring_bytes - cand_bytes) / 4u);
+        plan->vlist_cap = (uint32_t)((ring_bytes - cb) / 4u);
     } else {
         plan->cand_off = (uint32_t)ring_bytes;
         plan->scratch_off = 0u;
