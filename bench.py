@@ -177,7 +177,7 @@ def run_ours(args, rank, world, local_rank):
     import torch
     import torch.distributed as dist
     import scriptonait_b200 as sb
-    from scriptonait_b200 import sharding, workloads
+    from scriptonait_b200 import native, sharding, workloads
 
     torch.cuda.set_device(local_rank)
     dev = torch.device(f"cuda:{local_rank}")
@@ -384,6 +384,30 @@ def run_ours(args, rank, world, local_rank):
         del w4
         other("c5", workloads.c5(), n_steps, note="whole vocabulary on each GPU (the vocabulary-sharded form is c5_vocab_shard)")
 
+    # ------------------------------------------------------------------ rows the streaming selection cannot decide (top_k = 0)
+    # sample() on rows whose significance window holds thousands of values (N(0, 5^2): ~23k of 128k) or the
+    # whole row (N(0, 1)): ordered in global scratch by the same kernel, 256 rows per GPU
+    full_ordering = None
+    if not args.skip_others and not args.only_lm_head:
+        full_ordering = {}
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(1234 + rank)
+        for name, sd in (("window_23k_of_128k", 5.0), ("whole_row", 1.0)):
+            x = torch.randn((BATCH, VOCAB), generator=gen, device=dev, dtype=torch.float32) * sd
+            tk = torch.empty(BATCH, dtype=torch.int32, device=dev)
+            call = sampler.sample_batch(x, temperature=1.0, top_k=0, top_p=0.9, seeds=seeds, out_tokens=tk, trace=True,
+                                        prepare_only=True)
+            for _ in range(3):
+                call.launch()
+            sync_all()
+            ms = statistics.median(timed([call.launch], 1) for _ in range(5))
+            ms = max_over_ranks(ms)
+            flags = call.result.row_flags.cpu().numpy()
+            full_ordering[name] = {"rows_per_gpu": BATCH, "vocab": VOCAB, "logits": f"f32 N(0, {sd:g}^2), top_k 0, top_p 0.9",
+                                   "ms_per_batch": ms, "rows_per_s": world * BATCH / (ms * 1e-3),
+                                   "rows_ordered_in_global_scratch": int(((flags & native.ROW_FULL_SORT) != 0).sum())}
+            del x, call
+
     # ------------------------------------------------------------------ c5, vocabulary sharded over the ranks (N > 1)
     c5_shard = None
     if world > 1 and not args.skip_others and not args.only_lm_head:
@@ -511,7 +535,8 @@ def run_ours(args, rank, world, local_rank):
             "ms_per_step_strict_order": ms_per_step_strict,
             "overlapped_tokens_equal_strict_order": overlap_same,
             "region_ms_min_median_max": [min(regions), ms_region, max(regions)],
-            "strong_scaling": strong, "others": others, "c5_vocab_shard": c5_shard, "lm_head_fused": lm_head})
+            "strong_scaling": strong, "others": others, "full_ordering": full_ordering, "c5_vocab_shard": c5_shard,
+            "lm_head_fused": lm_head})
         line = {
             "metric": METRIC, "value": value, "unit": "rows/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",

@@ -472,32 +472,81 @@ __device__ __forceinline__ void sort_small(uint32_t n, Shared& S, float* cand_q,
 // composite keys alone (one 8-byte word per entry in `keys`, room for the next power of two; padding keys
 // are 0 and sort last), from which values and ids are read back afterwards (a value's ordered key is
 // exact except that -0.0 comes back as +0.0, which no later stage can tell apart).
-__device__ __forceinline__ void sort_keys64(uint32_t n, float* cand_q, uint32_t* cand_i, uint64_t* keys) {
-    uint32_t m = 1u;
-    while (m < n) m <<= 1;
-    for (uint32_t i = threadIdx.x; i < m; i += THREADS) keys[i] = i < n ? composite(cand_q[i], cand_i[i]) : 0ull;
-    cta_sync();
-    for (uint32_t size = 2u; size <= m; size <<= 1) {
+// Every thread holds E consecutive keys in registers: compare-exchange steps whose partners lie in the same
+// thread need nothing, those inside a warp take one shuffle per key, and only the strides that cross warps
+// (six steps of the whole network) go through shared memory and a barrier.
+template <int E>
+__device__ __forceinline__ void sort_keys64_regs(uint32_t n, float* cand_q, uint32_t* cand_i, uint64_t* keys) {
+    const uint32_t t = threadIdx.x;
+    constexpr uint32_t M = (uint32_t)E * (uint32_t)THREADS;
+    uint64_t k[E];
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+        const uint32_t i = t * E + e;
+        k[e] = i < n ? composite(cand_q[i], cand_i[i]) : 0ull;
+    }
+#pragma unroll
+    for (uint32_t size = 2u; size <= M; size <<= 1) {
+#pragma unroll
         for (uint32_t stride = size >> 1; stride > 0u; stride >>= 1) {
-            for (uint32_t t = threadIdx.x; t < (m >> 1); t += THREADS) {
-                const uint32_t lo = ((t & ~(stride - 1u)) << 1) | (t & (stride - 1u));
-                const uint32_t hi = lo + stride;
-                const bool descending_block = ((lo & size) == 0u);  // first-in-order (largest key) at the low slot
-                const uint64_t kl = keys[lo], kh = keys[hi];
-                if ((kh > kl) == descending_block) {
-                    keys[lo] = kh;
-                    keys[hi] = kl;
+            if (stride < (uint32_t)E) {
+#pragma unroll
+                for (int e = 0; e < E; ++e) {
+                    if ((e & stride) == 0u) {
+                        const bool larger_first = (((t * E + e) & size) == 0u);  // first-in-order (largest key) at the low slot
+                        const uint64_t lo = k[e], hi = k[e + stride];
+                        if ((hi > lo) == larger_first) {
+                            k[e] = hi;
+                            k[e + stride] = lo;
+                        }
+                    }
+                }
+            } else if (stride < 32u * (uint32_t)E) {
+                const uint32_t d = stride / (uint32_t)E;
+                const bool am_low = (t & d) == 0u;
+#pragma unroll
+                for (int e = 0; e < E; ++e) {
+                    const uint64_t other = __shfl_xor_sync(FULL_MASK, k[e], (int)d);
+                    const bool larger_first = (((t * E + e) & size) == 0u);
+                    const bool keep_larger = (am_low == larger_first);
+                    k[e] = keep_larger ? (other > k[e] ? other : k[e]) : (other < k[e] ? other : k[e]);
+                }
+            } else {
+                cta_sync();  // the previous exchange's reads are done
+#pragma unroll
+                for (int e = 0; e < E; ++e) keys[t * E + e] = k[e];
+                cta_sync();
+#pragma unroll
+                for (int e = 0; e < E; ++e) {
+                    const uint32_t i = t * E + e;
+                    const uint64_t other = keys[i ^ stride];
+                    const bool larger_first = ((i & size) == 0u);
+                    const bool keep_larger = (((i & stride) == 0u) == larger_first);
+                    k[e] = keep_larger ? (other > k[e] ? other : k[e]) : (other < k[e] ? other : k[e]);
                 }
             }
-            cta_sync();
         }
     }
-    for (uint32_t i = threadIdx.x; i < n; i += THREADS) {
-        const uint64_t k = keys[i];
-        cand_q[i] = okey_to_float((uint32_t)(k >> 32));
-        cand_i[i] = ~(uint32_t)k;
+    cta_sync();  // cand_q / cand_i were read by everyone long ago; the keys' last exchange is read
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+        const uint32_t i = t * E + e;
+        if (i < n) {
+            cand_q[i] = okey_to_float((uint32_t)(k[e] >> 32));
+            cand_i[i] = ~(uint32_t)k[e];
+        }
     }
     cta_sync();
+}
+
+// Not inlined: the network's registers stay out of the streaming kernel's own allocation.
+__device__ __noinline__ void sort_keys64(uint32_t n, float* cand_q, uint32_t* cand_i, uint64_t* keys) {
+    if (n <= 2u * THREADS)
+        sort_keys64_regs<2>(n, cand_q, cand_i, keys);
+    else if (n <= 4u * THREADS)
+        sort_keys64_regs<4>(n, cand_q, cand_i, keys);
+    else
+        sort_keys64_regs<8>(n, cand_q, cand_i, keys);
 }
 
 // Sorts cand[0..n), n > THREADS, into the reference ordering with a bitonic network; slots [n, m)
@@ -538,18 +587,123 @@ __device__ __forceinline__ void sort_candidates(uint32_t n, float* cand_q, uint3
 // the significance window (window mode only). Thread 0 owns the sequential
 // chains; everything else is data parallel. Returns through S: token, flags,
 // kept_n and the stage statistics.
-// Eight consecutive values of a 16-byte aligned shared-memory array starting at i0 (a multiple of 8),
-// 0.0f past n: two 16-byte loads for a whole batch.
-__device__ __forceinline__ void load_batch8(const float* vals, uint32_t i0, uint32_t n, float (&e)[8]) {
-    if (i0 + 8u <= n) {
-        const float4 a = *reinterpret_cast<const float4*>(vals + i0);
-        const float4 b = *reinterpret_cast<const float4*>(vals + i0 + 4u);
-        e[0] = a.x; e[1] = a.y; e[2] = a.z; e[3] = a.w;
-        e[4] = b.x; e[5] = b.y; e[6] = b.z; e[7] = b.w;
-    } else {
+// A chain of dependent rounded f32 operations acc = op(acc, v[i]) over v[0..n) in shared memory (16-byte
+// aligned), strictly in order, run by the calling thread alone. Whole blocks of 64 are walked eight values
+// at a time, the next eight already loaded, with no test or branch inside the block (a test and a branch on
+// the running value cost about fifty cycles, ten additions' worth); what is left is walked in groups of
+// eight with values past n read as 0.0f, which op must leave acc unchanged for.
+//   hit(before, after, x)  the chain stops at the first element where it holds: its index is returned and
+//                          acc is left as it was after that element.
+//   any_hit(after)         asked after a block with the value acc has then: true iff hit held for one of its
+//                          elements (the callers' chains are monotone, so the last value tells); only then
+//                          is the block walked again one element at a time.
+//   rest_is_noop(x0, acc)  asked before a block with its first value: true means no later element can change
+//                          acc or hit (values are in descending order), so stop.
+// Returns n when nothing hit.
+template <class Op, class Hit, class AnyHit, class Noop>
+__device__ __forceinline__ uint32_t thread_chain(const float* v, uint32_t n, float& acc_io, Op op, Hit hit, AnyHit any_hit,
+                                                 Noop rest_is_noop) {
+    float acc = acc_io;
+    uint32_t j = 0u;
+    uint32_t result = n;
+    const float4* v4 = reinterpret_cast<const float4*>(v);
+    auto again = [&](uint32_t from, uint32_t to, float start) {  // one by one over [from, to): the first hit
+        float a = start;
+        for (uint32_t i = from; i < to; ++i) {
+            const float was = a;
+            a = op(a, v[i]);
+            if (hit(was, a, v[i])) {
+                acc = a;
+                result = i;
+                return true;
+            }
+        }
+        return false;
+    };
+    bool done = false;
+#pragma unroll 1
+    for (; j + 64u <= n; j += 64u) {
+        if (rest_is_noop(v[j], acc)) {
+            done = true;
+            break;
+        }
+        const float before = acc;
+        float4 p = v4[j >> 2], q = v4[(j >> 2) + 1u];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) e[j] = (i0 + j < n) ? vals[i0 + j] : 0.0f;
+        for (uint32_t s8 = 0; s8 < 8u; ++s8) {
+            float4 p2 = p, q2 = q;
+            if (s8 < 7u) {
+                p2 = v4[(j >> 2) + 2u * s8 + 2u];
+                q2 = v4[(j >> 2) + 2u * s8 + 3u];
+            }
+            acc = op(acc, p.x); acc = op(acc, p.y); acc = op(acc, p.z); acc = op(acc, p.w);
+            acc = op(acc, q.x); acc = op(acc, q.y); acc = op(acc, q.z); acc = op(acc, q.w);
+            p = p2;
+            q = q2;
+        }
+        if (any_hit(acc) && again(j, j + 64u, before)) {
+            done = true;
+            break;
+        }
     }
+    if (!done && j < n && !rest_is_noop(v[j], acc)) {
+        const float before = acc;
+        const uint32_t from = j;
+#pragma unroll 1
+        for (; j < n; j += 8u) {
+            float x[8];
+            if (j + 8u <= n) {
+                const float4 a = v4[j >> 2], b = v4[(j >> 2) + 1u];
+                x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
+                x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) x[e] = (j + (uint32_t)e < n) ? v[j + e] : 0.0f;
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc = op(acc, x[e]);
+        }
+        if (any_hit(acc)) (void)again(from, n, before);
+    }
+    acc_io = acc;
+    return result;
+}
+
+// The ordered tail's three chains as functions of their own: inlined, their registers would be taken out of
+// the streaming kernel's allocation, and whatever that spills costs a trip to L2 (the kernel runs with
+// almost no L1).
+//   generate.rs:374, the left-to-right f32 sum. Once the sum is >= 1 a term below 2^-24 is under half an
+//   ulp and leaves it unchanged, and the terms only get smaller.
+__device__ __noinline__ float tail_sum(const float* probs, uint32_t n) {
+    float s = 0.0f;
+    thread_chain(
+        probs, n, s, [](float acc, float e) { return __fadd_rn(acc, e); }, [](float, float, float) { return false; },
+        [](float) { return false; }, [](float e0, float acc) { return e0 < 5.9604644775390625e-08f && acc >= 1.0f; });
+    return s;
+}
+//   generate.rs:397-409; the later re-summation of the kept prefix (:411) repeats the same additions. The
+//   running sum never falls: it has reached top_p inside a block iff it is there at the block's end.
+//   Returns the first index that reaches top_p (n if none, or if top_p is 1); the sum so far in *total.
+__device__ __noinline__ uint32_t tail_cumulative(const float* probs, uint32_t n, float top_p, float* total) {
+    float acc = 0.0f;
+    auto add = [](float a, float p) { return __fadd_rn(a, p); };
+    auto never = [](float, float) { return false; };
+    uint32_t at;
+    if (top_p < 1.0f)
+        at = thread_chain(probs, n, acc, add, [=](float, float after, float) { return after >= top_p; },
+                          [=](float after) { return after >= top_p; }, never);
+    else
+        at = thread_chain(probs, n, acc, add, [](float, float, float) { return false; }, [](float) { return false; }, never);
+    *total = acc;
+    return at;
+}
+//   generate.rs:413-418 stops at the first entry with r < p. r starts at u * total >= 0, and r - p rounds to
+//   a negative number exactly when r < p; from there on it only falls: a block holds that entry iff r is
+//   negative at the block's end. Returns that entry's index (n if there is none).
+__device__ __noinline__ uint32_t tail_walk(const float* probs, uint32_t n, float r) {
+    return thread_chain(
+        probs, n, r, [](float acc, float p) { return __fsub_rn(acc, p); }, [](float before, float, float p) { return before < p; },
+        [](float after) { return after < 0.0f; }, [](float, float) { return false; });
 }
 
 // The uniform the row's draw consumes: output `draw_index + 1` of its SplitMix64 stream
@@ -562,8 +716,8 @@ __device__ __forceinline__ float row_uniform(const KParams& P, uint32_t b) {
 }
 
 // `probs_ready`: probs[i] already holds exp(q_i - max) (the small sort computes it alongside the ranks).
-// The chains of thread 0 run in batches of 8 with the next batch's loads already in flight: the
-// additions stay strictly sequential, only loads and comparisons leave the dependent chain.
+// The chains of thread 0 run through thread_chain: the additions stay strictly sequential, only loads
+// and comparisons leave the dependent chain.
 __device__ __forceinline__ void ordered_tail(const KParams& P, uint32_t b, const RowCfg& rc, uint32_t n, bool truncated,
                                              uint32_t k_total, Shared& S, const float* cand_q, const uint32_t* cand_i,
                                              float* probs, bool probs_ready = false) {
@@ -582,20 +736,7 @@ __device__ __forceinline__ void ordered_tail(const KParams& P, uint32_t b, const
     cta_sync();
     PHASE(8);
     if (threadIdx.x == 0) {
-        // :374 left-to-right f32 sum. Once the sum is >= 1 a term below 2^-24 is under
-        // half an ulp and leaves it unchanged, and the terms only get smaller.
-        float s = 0.0f;
-        float e[8], nx[8];
-        load_batch8(probs, 0u, n, e);
-        for (uint32_t i0 = 0; i0 < n; i0 += 8u) {
-            if (i0 + 8u < n) load_batch8(probs, i0 + 8u, n, nx);
-            if (e[0] < 5.9604644775390625e-08f && s >= 1.0f) break;  // this and every later term is a no-op
-#pragma unroll
-            for (int j = 0; j < 8; ++j) s = __fadd_rn(s, e[j]);       // adding 0.0f past the end changes nothing
-#pragma unroll
-            for (int j = 0; j < 8; ++j) e[j] = nx[j];
-        }
-        S.f_sum = s;
+        S.f_sum = tail_sum(probs, n);
     }
     const float e_first = probs[0];  // read before anyone normalises it (the barrier below comes first)
     cta_sync();
@@ -634,38 +775,11 @@ __device__ __forceinline__ void ordered_tail(const KParams& P, uint32_t b, const
         uint32_t keep = keep_minp;
         float total = 0.0f;
         bool reached = false;
-        float p[8], nx[8];
-        load_batch8(probs, 0u, keep_minp, p);
-        if (rc.top_p < 1.0f) {
-            // :397-409; the later re-summation of the kept prefix (:411) repeats the same additions
-            float cum = 0.0f;
-            for (uint32_t i0 = 0; i0 < keep_minp && !reached; i0 += 8u) {
-                if (i0 + 8u < keep_minp) load_batch8(probs, i0 + 8u, keep_minp, nx);
-                float c[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    cum = __fadd_rn(cum, p[j]);
-                    c[j] = cum;
-                }
-#pragma unroll
-                for (int j = 7; j >= 0; --j) {
-                    if (i0 + j < keep_minp && c[j] >= rc.top_p) {
-                        keep = i0 + j + 1u;  // ends as the first index that reaches top_p
-                        total = c[j];
-                        reached = true;
-                    }
-                }
-                if (!reached) total = cum;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) p[j] = nx[j];
-            }
-        } else {
-            for (uint32_t i0 = 0; i0 < keep_minp; i0 += 8u) {
-                if (i0 + 8u < keep_minp) load_batch8(probs, i0 + 8u, keep_minp, nx);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) total = __fadd_rn(total, p[j]);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) p[j] = nx[j];
+        {
+            const uint32_t at = tail_cumulative(probs, keep_minp, rc.top_p, &total);
+            if (rc.top_p < 1.0f && at < keep_minp) {
+                keep = at + 1u;  // the first index that reaches top_p
+                reached = true;
             }
         }
         // entries past the window add less than half an ulp to `cum`/`total`, so both are final
@@ -677,26 +791,9 @@ __device__ __forceinline__ void ordered_tail(const KParams& P, uint32_t b, const
         S.f_r = r;
         uint32_t flags = LLM_CUDA_ROW_DRAW_CONSUMED;
         uint32_t token = 0u;
-        bool found = false;
-        load_batch8(probs, 0u, keep, p);
-        for (uint32_t i0 = 0; i0 < keep && !found; i0 += 8u) {  // :413-418, in batches of 8
-            if (i0 + 8u < keep) load_batch8(probs, i0 + 8u, keep, nx);
-            float rr[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                rr[j] = r;                 // r before entry i0+j is examined
-                r = __fsub_rn(r, p[j]);    // subtracting 0.0f past the end changes nothing
-            }
-#pragma unroll
-            for (int j = 7; j >= 0; --j) {
-                if (i0 + j < keep && rr[j] < p[j]) {  // ends as the first entry with r < p
-                    token = cand_i[i0 + j];
-                    found = true;
-                }
-            }
-#pragma unroll
-            for (int j = 0; j < 8; ++j) p[j] = nx[j];
-        }
+        const uint32_t at = tail_walk(probs, keep, r);
+        const bool found = at < keep;
+        if (found) token = cand_i[at];
         if (!found) {
             if (tail_kept || unknown_tail) {
                 flags = ROW_NEEDS_FULL;  // the walk continues into entries the window dropped
