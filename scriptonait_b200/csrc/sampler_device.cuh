@@ -590,39 +590,65 @@ __device__ __forceinline__ void sort_candidates(uint32_t n, float* cand_q, uint3
 // A chain of dependent rounded f32 operations acc = op(acc, v[i]) over v[0..n) in shared memory (16-byte
 // aligned), strictly in order, run by the calling thread alone. Whole blocks of 64 are walked eight values
 // at a time, the next eight already loaded, with no test or branch inside the block (a test and a branch on
-// the running value cost about fifty cycles, ten additions' worth); what is left is walked in groups of
-// eight with values past n read as 0.0f, which op must leave acc unchanged for.
+// the running value cost about fifty cycles, ten additions' worth); what is left, and a block that holds
+// a hit, is walked in groups of eight with the test per element and one branch per group (keeping the
+// first hit by selects instead makes a second, longer dependent chain: measured slower).
 //   hit(before, after, x)  the chain stops at the first element where it holds: its index is returned and
 //                          acc is left as it was after that element.
 //   any_hit(after)         asked after a block with the value acc has then: true iff hit held for one of its
 //                          elements (the callers' chains are monotone, so the last value tells); only then
-//                          is the block walked again one element at a time.
+//                          is the block walked again.
 //   rest_is_noop(x0, acc)  asked before a block with its first value: true means no later element can change
 //                          acc or hit (values are in descending order), so stop.
+// MIN_BLOCKS: the block walk is used while that many blocks are left; a chain that can hit passes 2 (a rest
+// of under 128 values is cheaper walked once, with the tests, than twice), one that cannot passes 1.
 // Returns n when nothing hit.
-template <class Op, class Hit, class AnyHit, class Noop>
+template <uint32_t MIN_BLOCKS, class Op, class Hit, class AnyHit, class Noop>
 __device__ __forceinline__ uint32_t thread_chain(const float* v, uint32_t n, float& acc_io, Op op, Hit hit, AnyHit any_hit,
                                                  Noop rest_is_noop) {
     float acc = acc_io;
     uint32_t j = 0u;
     uint32_t result = n;
     const float4* v4 = reinterpret_cast<const float4*>(v);
-    auto again = [&](uint32_t from, uint32_t to, float start) {  // one by one over [from, to): the first hit
+    // [from, to) in groups of eight with the hit test per element but one branch per group: the first hit, if any
+    // (acc and result set, true returned); otherwise acc is the value after element to - 1
+    auto walk = [&](uint32_t from, uint32_t to, float start) {
         float a = start;
-        for (uint32_t i = from; i < to; ++i) {
-            const float was = a;
-            a = op(a, v[i]);
-            if (hit(was, a, v[i])) {
-                acc = a;
-                result = i;
+#pragma unroll 1
+        for (uint32_t i = from; i < to; i += 8u) {
+            float x[8], c[8];
+            if (i + 8u <= to) {
+                const float4 lo = v4[i >> 2], hi = v4[(i >> 2) + 1u];
+                x[0] = lo.x; x[1] = lo.y; x[2] = lo.z; x[3] = lo.w;
+                x[4] = hi.x; x[5] = hi.y; x[6] = hi.z; x[7] = hi.w;
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) x[e] = (i + (uint32_t)e < to) ? v[i + e] : 0.0f;
+            }
+            uint32_t h = 0u;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float was = a;
+                a = op(a, x[e]);
+                c[e] = a;
+                if (i + (uint32_t)e < to && hit(was, a, x[e])) h |= 1u << e;
+            }
+            if (h) {
+                const uint32_t e0 = (uint32_t)__ffs(h) - 1u;
+                float at = c[0];
+#pragma unroll
+                for (int e = 1; e < 8; ++e) at = (e0 == (uint32_t)e) ? c[e] : at;
+                acc = at;
+                result = i + e0;
                 return true;
             }
         }
+        acc = a;
         return false;
     };
     bool done = false;
 #pragma unroll 1
-    for (; j + 64u <= n; j += 64u) {
+    for (; j + MIN_BLOCKS * 64u <= n; j += 64u) {
         if (rest_is_noop(v[j], acc)) {
             done = true;
             break;
@@ -641,30 +667,12 @@ __device__ __forceinline__ uint32_t thread_chain(const float* v, uint32_t n, flo
             p = p2;
             q = q2;
         }
-        if (any_hit(acc) && again(j, j + 64u, before)) {
+        if (any_hit(acc) && walk(j, j + 64u, before)) {
             done = true;
             break;
         }
     }
-    if (!done && j < n && !rest_is_noop(v[j], acc)) {
-        const float before = acc;
-        const uint32_t from = j;
-#pragma unroll 1
-        for (; j < n; j += 8u) {
-            float x[8];
-            if (j + 8u <= n) {
-                const float4 a = v4[j >> 2], b = v4[(j >> 2) + 1u];
-                x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
-                x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
-            } else {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) x[e] = (j + (uint32_t)e < n) ? v[j + e] : 0.0f;
-            }
-#pragma unroll
-            for (int e = 0; e < 8; ++e) acc = op(acc, x[e]);
-        }
-        if (any_hit(acc)) (void)again(from, n, before);
-    }
+    if (!done && j < n && !rest_is_noop(v[j], acc)) (void)walk(j, n, acc);
     acc_io = acc;
     return result;
 }
@@ -676,7 +684,7 @@ __device__ __forceinline__ uint32_t thread_chain(const float* v, uint32_t n, flo
 //   ulp and leaves it unchanged, and the terms only get smaller.
 __device__ __noinline__ float tail_sum(const float* probs, uint32_t n) {
     float s = 0.0f;
-    thread_chain(
+    thread_chain<1>(
         probs, n, s, [](float acc, float e) { return __fadd_rn(acc, e); }, [](float, float, float) { return false; },
         [](float) { return false; }, [](float e0, float acc) { return e0 < 5.9604644775390625e-08f && acc >= 1.0f; });
     return s;
@@ -690,10 +698,10 @@ __device__ __noinline__ uint32_t tail_cumulative(const float* probs, uint32_t n,
     auto never = [](float, float) { return false; };
     uint32_t at;
     if (top_p < 1.0f)
-        at = thread_chain(probs, n, acc, add, [=](float, float after, float) { return after >= top_p; },
+        at = thread_chain<2>(probs, n, acc, add, [=](float, float after, float) { return after >= top_p; },
                           [=](float after) { return after >= top_p; }, never);
     else
-        at = thread_chain(probs, n, acc, add, [](float, float, float) { return false; }, [](float) { return false; }, never);
+        at = thread_chain<1>(probs, n, acc, add, [](float, float, float) { return false; }, [](float) { return false; }, never);
     *total = acc;
     return at;
 }
@@ -701,7 +709,7 @@ __device__ __noinline__ uint32_t tail_cumulative(const float* probs, uint32_t n,
 //   a negative number exactly when r < p; from there on it only falls: a block holds that entry iff r is
 //   negative at the block's end. Returns that entry's index (n if there is none).
 __device__ __noinline__ uint32_t tail_walk(const float* probs, uint32_t n, float r) {
-    return thread_chain(
+    return thread_chain<2>(
         probs, n, r, [](float acc, float p) { return __fsub_rn(acc, p); }, [](float before, float, float p) { return before < p; },
         [](float after) { return after < 0.0f; }, [](float, float) { return false; });
 }
