@@ -677,6 +677,256 @@ __device__ __forceinline__ uint32_t thread_chain(const float* v, uint32_t n, flo
     return result;
 }
 
+// ---------------------------------------------------------------------------
+// Long chains, exactly, by the whole CTA. The reference's sums are sequences of dependent rounded f32
+// additions (or subtractions); a thread can only walk them one term after the other. But while the
+// running value s stays inside one binade, s = A * u with u = ulp(s) and A an integer in
+// [2^23, 2^24), and round-to-nearest-even of s + x is A + floor(x/u) + c, where c depends on the
+// fraction of x/u alone (above / below one half) except for an exact half, where it depends on the
+// parity of A. So every term is a little machine with two states (the parity of A before it) that
+// adds an integer and leaves a parity, machines compose associatively, and a chunk of 2048 terms is
+// evaluated with a prefix scan over the CTA instead of 2048 dependent additions. Whatever the
+// integers cannot express is an "event", found as the first term where A would cross a bound: the
+// value leaving its binade (the next binade rounds on a different grid), a term larger than the
+// value, the cumulative sum reaching top_p, the walk's r falling below its term. The term of an
+// event is evaluated with real f32 arithmetic from the exact value before it, so are a few terms
+// after it (events come in clusters where value and terms are of similar size), and the scan starts
+// again behind them. The result is bit for bit that of the sequential chain
+// (tests/test_gpu_full_ordering.py and the flat-row parity tests run through it).
+constexpr uint32_t CHAIN_SAT = 1u << 30;
+struct ChainMachine {
+    uint32_t inc0, inc1;  // what the terms add to A for parity 0 / 1 of A before them (saturating)
+    uint32_t par;         // bit p: the parity they leave for parity p before them
+};
+__device__ __forceinline__ ChainMachine chain_then(const ChainMachine& f, const ChainMachine& g) {  // f's terms, then g's
+    ChainMachine h;
+    const uint32_t f0 = f.par & 1u, f1 = (f.par >> 1) & 1u;
+    h.inc0 = min(f.inc0 + (f0 ? g.inc1 : g.inc0), CHAIN_SAT);
+    h.inc1 = min(f.inc1 + (f1 ? g.inc1 : g.inc0), CHAIN_SAT);
+    h.par = ((g.par >> f0) & 1u) | (((g.par >> f1) & 1u) << 1);
+    return h;
+}
+// One term against a value whose unbiased exponent is es: floor(x/u), whether the fraction is above one
+// half / exactly one half / not zero, and whether the term lies above the value's binade.
+struct ChainTerm {
+    uint32_t fl;
+    uint32_t bits;  // 1: fraction > 1/2, 2: fraction == 1/2, 4: fraction != 0, 8: term above the binade
+};
+__device__ __forceinline__ ChainTerm chain_term(float x, int es) {
+    const uint32_t b = __float_as_uint(x);
+    const uint32_t ex = (b >> 23) & 0xffu;
+    const uint32_t m = b & 0x7fffffu;
+    const uint32_t M = ex ? (m | 0x800000u) : m;
+    const int E = ex ? (int)ex - 127 : -126;
+    const int shift = es - E;
+    ChainTerm t;
+    if (shift < 0) {
+        t.fl = 0u;
+        t.bits = 8u;
+    } else if (shift >= 32) {
+        t.fl = 0u;
+        t.bits = M ? 4u : 0u;
+    } else {
+        t.fl = M >> shift;
+        const uint32_t rem = M & ((1u << shift) - 1u);
+        const uint32_t half = shift ? (1u << (shift - 1)) : 0xffffffffu;
+        t.bits = (rem > half ? 1u : 0u) | (rem == half ? 2u : 0u) | (rem ? 4u : 0u);
+    }
+    return t;
+}
+__device__ __forceinline__ uint32_t chain_step(const ChainTerm& t, uint32_t parity) {  // what the term adds to / takes from A
+    return t.fl + ((t.bits & 2u) ? ((parity + t.fl) & 1u) : (t.bits & 1u));
+}
+
+enum { CHAIN_SUM = 0, CHAIN_CUMULATIVE = 1, CHAIN_WALK = 2 };
+constexpr uint32_t CHAIN_EPT = 8;                                  // terms per thread and chunk
+constexpr uint32_t CHAIN_SPAN = CHAIN_EPT * (uint32_t)THREADS;     // terms per chunk
+constexpr uint32_t CHAIN_WORDS = 3u * WARPS + 2u;                  // shared words the function needs
+
+// Called by all THREADS threads of the CTA with the same arguments; v[0..n) in global (GLOBAL: read past L1,
+// other threads of the CTA have just written it) or shared memory, descending (that is only used to stop
+// early), finite, not negative. `sh`: CHAIN_WORDS words of shared memory.
+//   CHAIN_SUM         acc = fl(acc + v[i]) over all i; returns n
+//   CHAIN_CUMULATIVE  the same, stopping at the first i with acc >= bound (returned, acc as after it); n if none
+//   CHAIN_WALK        stops at the first i with acc < v[i] (returned, acc as before it), else acc = fl(acc - v[i]); n if none
+// Every thread returns the same result.
+template <bool GLOBAL>
+__device__ __noinline__ uint32_t cta_chain(const float* v, uint32_t n, int kind, float bound, float* acc_io, uint32_t* sh) {
+    const uint32_t tid = threadIdx.x;
+    const unsigned lane = tid & 31u, warp = tid >> 5;
+    uint32_t* w_inc0 = sh;
+    uint32_t* w_inc1 = sh + WARPS;
+    uint32_t* w_par = sh + 2 * WARPS;
+    uint32_t* sh_event = sh + 3 * WARPS;
+    uint32_t* sh_before = sh + 3 * WARPS + 1;
+    float s = *acc_io;
+    uint32_t pos = 0u;
+    uint32_t result = n;
+    const bool sub = kind == CHAIN_WALK;
+    auto at = [&](uint32_t i) { return GLOBAL ? __ldcg(v + i) : v[i]; };
+    // one term with real arithmetic, by every thread alike; true when the chain ends at it
+    auto real_step = [&](uint32_t i) {
+        const float x = at(i);
+        if (sub) {
+            if (s < x) {
+                result = i;
+                return true;
+            }
+            s = __fsub_rn(s, x);
+            return false;
+        }
+        s = __fadd_rn(s, x);
+        if (kind == CHAIN_CUMULATIVE && s >= bound) {
+            result = i;
+            return true;
+        }
+        return false;
+    };
+    while (pos < n) {
+        const uint32_t sb = __float_as_uint(s);
+        const uint32_t sex = (sb >> 23) & 0xffu;
+        if (sex == 0u || sex == 0xffu || (sb >> 31) || (pos & 7u)) {  // zero, subnormal, not finite or negative: no integer form
+            if (real_step(pos)) break;
+            ++pos;
+            continue;
+        }
+        const int es = (int)sex - 127;
+        const uint32_t A0 = (sb & 0x7fffffu) | 0x800000u;
+        if (!sub) {
+            // a term under half an ulp changes nothing, and the terms only get smaller
+            const ChainTerm t0 = chain_term(at(pos), es);
+            if (t0.fl == 0u && (t0.bits & 11u) == 0u) break;
+        }
+        // the bound on A that ends the scan: the binade's end, or where the value reaches `bound`
+        uint32_t B = 1u << 24;
+        if (kind == CHAIN_CUMULATIVE) {
+            const uint32_t bb = __float_as_uint(bound);
+            const uint32_t bex = (bb >> 23) & 0xffu;
+            const int eb = bex ? (int)bex - 127 : -126;
+            if ((bb >> 31) || bb == 0u || eb < es)
+                B = 0u;  // every value qualifies
+            else if (eb == es)
+                B = min(B, (bb & 0x7fffffu) | 0x800000u);
+        }
+        if (tid == 0) *sh_event = 0xffffffffu;
+        // this thread's terms (chunks start at multiples of eight: two 16-byte loads), and their machine
+        float x[CHAIN_EPT];
+        const uint32_t first = pos + tid * CHAIN_EPT;
+        if (first + CHAIN_EPT <= n) {
+            const float4* v4 = reinterpret_cast<const float4*>(v + first);
+            const float4 lo = GLOBAL ? __ldcg(v4) : v4[0];
+            const float4 hi = GLOBAL ? __ldcg(v4 + 1) : v4[1];
+            x[0] = lo.x; x[1] = lo.y; x[2] = lo.z; x[3] = lo.w;
+            x[4] = hi.x; x[5] = hi.y; x[6] = hi.z; x[7] = hi.w;
+        } else {
+#pragma unroll
+            for (uint32_t k = 0; k < CHAIN_EPT; ++k) x[k] = first + k < n ? at(first + k) : 0.0f;
+        }
+        ChainMachine mine;
+        mine.inc0 = mine.inc1 = 0u;
+        mine.par = 2u;
+        {
+            uint32_t p0 = 0u, p1 = 1u;
+#pragma unroll
+            for (uint32_t k = 0; k < CHAIN_EPT; ++k) {
+                const ChainTerm t = chain_term(x[k], es);
+                const uint32_t d0 = chain_step(t, p0), d1 = chain_step(t, p1);
+                mine.inc0 = min(mine.inc0 + d0, CHAIN_SAT);
+                mine.inc1 = min(mine.inc1 + d1, CHAIN_SAT);
+                p0 = (p0 + d0) & 1u;
+                p1 = (p1 + d1) & 1u;
+            }
+            mine.par = p0 | (p1 << 1);
+        }
+        // inclusive scan over the warp, then over the warps
+        ChainMachine incl = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            ChainMachine prev;
+            prev.inc0 = __shfl_up_sync(FULL_MASK, incl.inc0, o);
+            prev.inc1 = __shfl_up_sync(FULL_MASK, incl.inc1, o);
+            prev.par = __shfl_up_sync(FULL_MASK, incl.par, o);
+            if (lane >= (unsigned)o) incl = chain_then(prev, incl);
+        }
+        if (lane == 31) {
+            w_inc0[warp] = incl.inc0;
+            w_inc1[warp] = incl.inc1;
+            w_par[warp] = incl.par;
+        }
+        ChainMachine excl;  // the terms of this warp before this thread's
+        excl.inc0 = __shfl_up_sync(FULL_MASK, incl.inc0, 1);
+        excl.inc1 = __shfl_up_sync(FULL_MASK, incl.inc1, 1);
+        excl.par = __shfl_up_sync(FULL_MASK, incl.par, 1);
+        if (lane == 0) {
+            excl.inc0 = excl.inc1 = 0u;
+            excl.par = 2u;
+        }
+        cta_sync();
+        ChainMachine before;  // everything before this thread's terms
+        before.inc0 = before.inc1 = 0u;
+        before.par = 2u;
+        ChainMachine whole = before;  // the whole chunk
+#pragma unroll
+        for (uint32_t w = 0; w < (uint32_t)WARPS; ++w) {
+            ChainMachine m;
+            m.inc0 = w_inc0[w];
+            m.inc1 = w_inc1[w];
+            m.par = w_par[w];
+            if (w < warp) before = chain_then(before, m);
+            whole = chain_then(whole, m);
+        }
+        before = chain_then(before, excl);
+        const uint32_t par0 = A0 & 1u;
+        const uint32_t moved = par0 ? before.inc1 : before.inc0;
+        uint32_t A = sub ? A0 - min(moved, A0) : A0 + moved;
+        uint32_t my_event = 0xffffffffu, my_before = 0u;
+#pragma unroll
+        for (uint32_t k = 0; k < CHAIN_EPT; ++k) {
+            const ChainTerm t = chain_term(x[k], es);
+            const uint32_t d = chain_step(t, A & 1u);
+            bool ev;
+            if (sub)
+                ev = (t.bits & 8u) || A < t.fl + ((t.bits >> 2) & 1u) + (1u << 23);
+            else
+                ev = (t.bits & 8u) || A + d >= B;
+            if (ev && my_event == 0xffffffffu && first + k < n) {
+                my_event = first + k;
+                my_before = A;
+            }
+            A = sub ? A - d : A + d;
+        }
+        if (my_event != 0xffffffffu) atomicMin(sh_event, my_event);
+        cta_sync();
+        const uint32_t ev = *sh_event;
+        if (ev == 0xffffffffu) {
+            const uint32_t all = par0 ? whole.inc1 : whole.inc0;
+            const uint32_t A_end = sub ? A0 - all : A0 + all;
+            s = __uint_as_float((sb & 0xff800000u) | (A_end & 0x7fffffu));  // same binade: A_end in [2^23, 2^24)
+            pos = min(pos + CHAIN_SPAN, n);
+            cta_sync();  // everyone has read the event word before the next chunk resets it
+            continue;
+        }
+        if (my_event == ev) *sh_before = my_before;
+        cta_sync();
+        const uint32_t A_before = *sh_before;
+        s = __uint_as_float((sb & 0xff800000u) | (A_before & 0x7fffffu));
+        // the event's term and the terms up to the next multiple of eight (at least eight of them), one by one
+        bool ended = false;
+        uint32_t i = ev;
+        const uint32_t until = min(n, (ev + 16u) & ~7u);
+        for (; i < until; ++i) {
+            if (real_step(i)) {
+                ended = true;
+                break;
+            }
+        }
+        if (ended) break;
+        pos = i;
+    }
+    *acc_io = s;
+    return result;
+}
+
 // The ordered tail's three chains as functions of their own: inlined, their registers would be taken out of
 // the streaming kernel's allocation, and whatever that spills costs a trip to L2 (the kernel runs with
 // almost no L1).

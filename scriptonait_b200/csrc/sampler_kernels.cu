@@ -385,144 +385,17 @@ __device__ uint32_t acquire_full_slot(const KParams& P) {
     return 0xffffffffu;
 }
 
-// Shared-memory words of the full ordering's working area (`work`): the radix sort's tables, then the
-// chains' staging ring.
+// Shared-memory words of the full ordering's working area (`work`): the radix sort's tables (the chains
+// use the per-warp totals' words).
 constexpr uint32_t WORK_HIST = 0u;      // [2][256] digit histograms: this pass's, and the next pass's while keys are moved
 constexpr uint32_t WORK_BASE = 512u;    // [256] where the next key of every digit goes
 constexpr uint32_t WORK_WTOT = 768u;    // [2][32] per-warp totals (two sets)
 constexpr uint32_t WORK_DELTA = 832u;   // [256] per digit: position in the output minus position in the reordered tile
 constexpr uint32_t WORK_WRUN = 1088u;   // [2][WARPS][256] per-warp digit counts of a tile (two sets, used alternately)
 constexpr uint32_t WORK_TILE = WORK_WRUN + 2u * (uint32_t)WARPS * 256u;  // [2][1024] a tile's keys and columns, ordered by digit
-constexpr uint32_t WORK_CHAIN = WORK_TILE + 2048u;                        // [2][CHAIN_CHUNK] floats + 16
-constexpr uint32_t CHAIN_CHUNK = 256u;
-constexpr uint32_t WORK_WORDS = WORK_CHAIN + 2u * CHAIN_CHUNK + 16u;  // + the pad a walk reads past the second buffer
+constexpr uint32_t WORK_WORDS = WORK_TILE + 2048u;
+static_assert(2u * 32u >= CHAIN_WORDS, "the chains' shared words are the per-warp totals' two sets");
 static_assert(512u + WORK_WORDS * 4u <= RING_STAGES * STAGE_BYTES, "the full ordering's working area lives in the ring");
-
-// A chain of dependent rounded f32 operations acc = op(acc, vals[i]) over vals[0..n), in order, run by
-// the calling warp: all lanes fetch CHAIN_CHUNK values at a time with coalesced 16-byte loads (two
-// chunks ahead of the one being walked) into a double-buffered shared-memory stage, and lane 0 walks
-// the stage eight values at a time, the next eight already in registers, with no test or branch inside 64, so the chain costs about
-// its own dependent latency (under five cycles a term) and not one memory round trip per term. Every
-// lane returns the same result.
-//   hit(before, after, v)  the chain stops at the first element where it holds: its index is returned
-//                          and acc is left as it was after that element.
-//   any_hit(after)         asked after every 64 elements with the value acc has then: true iff
-//                          hit held for one of them (the caller's chains are monotone, so the last
-//                          value tells); only then are the 64 walked again one by one. A test and a
-//                          branch cost about fifty cycles, ten additions' worth.
-//   rest_is_noop(v0, acc)  asked once per chunk with the chunk's first value: true means no later
-//                          element can change acc or hit (values are in descending order), so stop.
-// Returns n when nothing hit. Elements past n read as 0.0f, which op must leave acc unchanged for.
-// `vals` is 16-byte aligned; `stage` holds 2 * CHAIN_CHUNK + 16 floats.
-template <class Op, class Hit, class AnyHit, class Noop>
-__device__ __forceinline__ uint32_t warp_chain(const float* vals, uint32_t n, float& acc_io, Op op, Hit hit, AnyHit any_hit,
-                                               Noop rest_is_noop, float* stage) {
-    const unsigned lane = threadIdx.x & 31u;
-    auto fetch = [&](uint32_t i) {  // four consecutive values starting at i (a multiple of 4), zero past n
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (i + 3u < n) {
-            v = __ldcg(reinterpret_cast<const float4*>(vals + i));
-        } else {
-            if (i < n) v.x = __ldcg(&vals[i]);
-            if (i + 1u < n) v.y = __ldcg(&vals[i + 1u]);
-            if (i + 2u < n) v.z = __ldcg(&vals[i + 2u]);
-        }
-        return v;
-    };
-    // a chunk: lane l holds values [4 l, 4 l + 4) and [128 + 4 l, 128 + 4 l + 4)
-    float4 a0 = fetch(lane * 4u), a1 = fetch(128u + lane * 4u);
-    float4 b0 = fetch(CHAIN_CHUNK + lane * 4u), b1 = fetch(CHAIN_CHUNK + 128u + lane * 4u);
-    uint32_t result = n;
-    float acc = acc_io;
-    for (uint32_t i0 = 0; i0 < n; i0 += CHAIN_CHUNK) {
-        float* buf = stage + ((i0 / CHAIN_CHUNK) & 1u) * CHAIN_CHUNK;
-        *reinterpret_cast<float4*>(buf + lane * 4u) = a0;
-        *reinterpret_cast<float4*>(buf + 128u + lane * 4u) = a1;
-        __syncwarp();
-        a0 = b0;
-        a1 = b1;
-        b0 = fetch(i0 + 2u * CHAIN_CHUNK + lane * 4u);
-        b1 = fetch(i0 + 2u * CHAIN_CHUNK + 128u + lane * 4u);
-        int stop = 0;
-        if (lane == 0) {
-            if (rest_is_noop(buf[0], acc)) {
-                stop = 1;
-            } else {
-                const uint32_t m = min(CHAIN_CHUNK, n - i0);
-                const float4* b4 = reinterpret_cast<const float4*>(buf);
-                float4 p = b4[0], q = b4[1];
-#pragma unroll 1
-                for (uint32_t j = 0; j < CHAIN_CHUNK; j += 64u) {
-                    const float before = acc;
-#pragma unroll
-                    for (uint32_t s8 = 0; s8 < 8u; ++s8) {
-                        // the next eight (past the chunk's end: the other buffer or the pad, never used)
-                        const float4 p2 = b4[(j >> 2) + 2u * s8 + 2u], q2 = b4[(j >> 2) + 2u * s8 + 3u];
-                        acc = op(acc, p.x); acc = op(acc, p.y); acc = op(acc, p.z); acc = op(acc, p.w);
-                        acc = op(acc, q.x); acc = op(acc, q.y); acc = op(acc, q.z); acc = op(acc, q.w);
-                        p = p2;
-                        q = q2;
-                    }
-                    if (any_hit(acc)) {
-                        float again = before;
-                        for (uint32_t e = 0; e < 64u && j + e < m; ++e) {
-                            const float was = again;
-                            again = op(again, buf[j + e]);
-                            if (hit(was, again, buf[j + e])) {
-                                acc = again;
-                                result = i0 + j + e;
-                                stop = 2;
-                                break;
-                            }
-                        }
-                        if (stop) break;
-                    }
-                }
-            }
-        }
-        stop = __shfl_sync(FULL_MASK, stop, 0);
-        if (stop) break;
-    }
-    acc_io = __shfl_sync(FULL_MASK, acc, 0);
-    return __shfl_sync(FULL_MASK, result, 0);
-}
-
-// The full ordering's four chains, each a function of its own: inlined into their caller they would
-// share its registers, and a spilled value of the walking lane costs a trip to L2 per step.
-//   sum of the exponentials (generate.rs:386-389): once the sum is >= 1 a term below 2^-24 is under half
-//   an ulp and leaves it unchanged, and the terms only get smaller: adding them and stopping are the same
-__device__ __noinline__ float chain_sum(const float* vals, uint32_t n, float* stage) {
-    float s = 0.0f;
-    warp_chain(
-        vals, n, s, [](float acc, float e) { return __fadd_rn(acc, e); }, [](float, float, float) { return false; },
-        [](float) { return false; }, [](float e0, float acc) { return e0 < 5.9604644775390625e-08f && acc >= 1.0f; }, stage);
-    return s;
-}
-//   cumulative probability up to the first entry that reaches top_p (generate.rs:396-403), or over all n
-//   entries when top_p is 1; a term below `tiny` (2^-26 of the leader) is under half an ulp of any running
-//   sum, which is at least the leader's share: it changes nothing, and neither does anything after it.
-//   The running sum never falls: it has reached top_p inside a block iff it is there at the block's end.
-__device__ __noinline__ uint32_t chain_cumulative(const float* vals, uint32_t n, float top_p, float tiny, float* total_io, float* stage) {
-    float total = *total_io;
-    auto add = [](float acc, float p) { return __fadd_rn(acc, p); };
-    auto below_tiny = [=](float p_first, float) { return p_first < tiny; };
-    uint32_t at;
-    if (top_p < 1.0f)
-        at = warp_chain(vals, n, total, add, [=](float, float after, float) { return after >= top_p; },
-                        [=](float after) { return after >= top_p; }, below_tiny, stage);
-    else
-        at = warp_chain(vals, n, total, add, [](float, float, float) { return false; }, [](float) { return false; }, below_tiny, stage);
-    *total_io = total;
-    return at;
-}
-//   the draw's walk (generate.rs:411-417) stops at the first entry with r < p. r starts at u * total >= 0,
-//   and r - p rounds to a negative number exactly when r < p; from there on it only falls: a block holds
-//   that entry iff r is negative at the block's end
-__device__ __noinline__ uint32_t chain_walk(const float* vals, uint32_t n, float r, float* stage) {
-    return warp_chain(
-        vals, n, r, [](float acc, float p) { return __fsub_rn(acc, p); }, [](float before, float, float p) { return before < p; },
-        [](float after) { return after < 0.0f; }, [](float, float) { return false; }, stage);
-}
 
 // What the full ordering needs to read one row the way the reference edits it. Held by value in the
 // functions that stream the row: fields of the launch parameters, reached through a reference, would
@@ -921,7 +794,6 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
     uint32_t* dk = slot_base + 2u * P.full_vpad;   // keys out
     uint32_t* di = slot_base + 3u * P.full_vpad;   // column indices out
     float* vals = P.full_vals + (size_t)F.slot * P.full_vpad;
-    float* chain_stage = reinterpret_cast<float*>(work + WORK_CHAIN);  // clear of the sort's tables
     if (rc.has_pen) {
         const uint32_t* hist = P.history + (size_t)b * P.hist_stride;
         for (uint32_t j = tid; j < rc.hlen; j += THREADS) {
@@ -983,8 +855,9 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
         }
         cta_sync();
         PHASE(8);
-        if (tid < 32u) {  // warp 0 runs the sequential chains, every lane alike
-            const float s = chain_sum(vals, n, chain_stage);
+        {   // the sum of the exponentials (generate.rs:386-389), by the whole CTA
+            float s = 0.0f;
+            cta_chain<true>(vals, n, CHAIN_SUM, 0.0f, &s, work + WORK_WTOT);
             if (tid == 0) {
                 F.sum = s;
                 F.keep = n;
@@ -1037,15 +910,14 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
             const bool unknown_tail = truncated && rc.min_p > 0.0f && F.keep == n && rc.min_p < 5.9604644775390625e-08f;
             const bool open_tail = truncated && F.keep == n && !(rc.min_p > 0.0f);  // the kept set continues past the window
             PHASE(10);
-            if (tid < 32u) {
+            {   // cumulative probability and the draw's walk (generate.rs:396-417), by the whole CTA, every thread alike
                 const uint32_t keep_minp = F.keep;
                 uint32_t keep = keep_minp;
                 float total = 0.0f;
                 bool reached = false;
-                const float p0 = __ldcg(&vals[0]);
-                const float tiny = __fmul_rn(p0, 1.4901161193847656e-08f);  // 2^-26 of the leader: below half an ulp of any running sum
                 {
-                    const uint32_t at = chain_cumulative(vals, keep_minp, rc.top_p, tiny, &total, chain_stage);
+                    const uint32_t at = cta_chain<true>(vals, keep_minp, rc.top_p < 1.0f ? CHAIN_CUMULATIVE : CHAIN_SUM, rc.top_p, &total,
+                                                        work + WORK_WTOT);
                     if (rc.top_p < 1.0f && at < keep_minp) {
                         keep = at + 1u;  // the first index whose running sum reaches top_p
                         reached = true;
@@ -1055,7 +927,7 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
                 float rr = __fmul_rn(u, total);
                 const float r0 = rr;
                 uint32_t flags = LLM_CUDA_ROW_DRAW_CONSUMED;
-                const uint32_t at = chain_walk(vals, keep, rr, chain_stage);
+                const uint32_t at = cta_chain<true>(vals, keep, CHAIN_WALK, 0.0f, &rr, work + WORK_WTOT);
                 const bool found = at < keep;
                 // entries past the window add less than half an ulp to the running sums, so `total` is final
                 const bool tail_kept = open_tail && !reached;
@@ -1069,6 +941,7 @@ __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullSha
                     token = id_at(keep - 1u);
                     flags |= LLM_CUDA_ROW_FALLBACK_LAST;
                 }
+                cta_sync();  // everyone has read F.keep
                 if (tid == 0) {
                     F.total = total;
                     F.u = u;

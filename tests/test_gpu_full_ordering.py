@@ -120,3 +120,20 @@ def test_window_sizes_either_side_of_the_shared_memory_tiers(sampler, bf16):
         assert np.array_equal(gpu.stats, orc.stats)
         for r, m in enumerate(sizes):
             assert bool(gpu.flags[r] & N.ROW_FULL_SORT) == (m > 4096), (m, hex(int(gpu.flags[r])))
+
+
+@pytest.mark.parametrize("vocab", [50257, 128256])
+def test_constant_and_two_level_rows_round_like_the_sequential_sums(sampler, vocab):
+    """Rows of one repeated value, or two: every term of the long sums has the same bits, so whole runs of
+    additions round the same way, land exactly between two floats again and again (the rounding then depends on
+    the running sum's parity), and cross binades at known places: the sums, the cumulative cut and the
+    walk must come out as the reference's left-to-right f32 chains, bit for bit."""
+    g = np.random.default_rng(vocab)
+    x = np.zeros((5, vocab), np.float32)
+    x[1, :] = 3.25
+    x[2, ::2] = np.float32(np.log(2.0))          # exponentials 1 and 1/2
+    x[3, : vocab // 3] = 1.0
+    x[4, :] = g.choice(np.array([0.0, 0.6931472, 1.3862944], np.float32), vocab)
+    _check(sampler, _wl(x, temperature=1.0, top_k=0, top_p=0.9))
+    _check(sampler, _wl(x, temperature=1.0, top_k=0, top_p=0.37, min_p=1e-7))
+    _check(sampler, _wl(narrow_bf16(x), temperature=2.0, top_k=0, top_p=0.999))
