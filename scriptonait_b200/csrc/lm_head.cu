@@ -131,6 +131,13 @@ __device__ __forceinline__ uint32_t tile_of(uint32_t phase, uint32_t i, uint32_t
 
 }  // namespace
 
+// Programmatic dependent launch (no-ops for a grid launched the ordinary way). The step's kernels are launched
+// so that each may start while its predecessor is still running; a kernel executes the wait before it first
+// touches anything its predecessor writes, and allows its own successor to start only after that wait, so
+// that when a kernel starts early, everything two or more launches back is complete.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __global__ void __launch_bounds__(LM_THREADS, 2)
 lm_head_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const LmParams P) {
     extern __shared__ unsigned char lm_dyn[];
@@ -164,7 +171,6 @@ lm_head_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         abort_flag = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    for (uint32_t i = tid; i < 256u; i += LM_THREADS) thr_s[i] = (P.thr && i < P.batch) ? P.thr[i] : __uint_as_float(0x7f800000u);
     if (warp == 1) {  // tensor memory: both accumulators, allocated by one whole warp, which also frees it
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(saddr(&tmem_base_slot)), "r"(P.tmem_cols)
                      : "memory");
@@ -178,6 +184,9 @@ lm_head_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     if (warp == 0) {
         // ---- TMA producer
         if (lane == 0) {
+            // the probe pass follows the kernel that writes the normalised hidden states; the main pass follows the
+            // threshold kernel, which its loads and tensor-core work do not depend on: they start at once
+            if (P.phase != LM_PHASE_MAIN) pdl_wait();
             uint32_t g = 0;  // chunks issued
             for (uint32_t i = blockIdx.x; i < n_items && !abort_flag; i += gridDim.x) {
                 const uint32_t tile = tile_of(P.phase, i, P.probe_every);
@@ -229,6 +238,11 @@ lm_head_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // ---- epilogue: warp w reads lanes 32 * (w % 4) .. + 31 of tensor memory (its quarter)
         const uint32_t quarter = warp & 3u;
         const uint32_t row_in_tile = quarter * 32u + lane;
+        // the thresholds (main pass) come from the preceding kernel, and what this one writes may still be read by it
+        pdl_wait();
+        for (uint32_t i = tid - 64u; i < 256u; i += 128u) thr_s[i] = (P.thr && i < P.batch) ? P.thr[i] : __uint_as_float(0x7f800000u);
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
+        if (tid == 64u) pdl_launch_dependents();
         uint32_t it = 0;
         for (uint32_t i = blockIdx.x; i < n_items && !abort_flag; i += gridDim.x, ++it) {
             const uint32_t j = it & 1u;
@@ -275,6 +289,7 @@ lm_head_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 __global__ void rmsnorm_bf16_kernel(const float* x, const float* gain, float eps, uint32_t batch, uint32_t dim, __nv_bfloat16* y,
                                     uint32_t* cand_count) {
     const uint32_t b = blockIdx.x;
+    pdl_launch_dependents();  // launched the ordinary way itself: whatever precedes it is complete
     if (threadIdx.x == 0 && cand_count) cand_count[b] = 0u;  // the step's candidate lists start empty
     __shared__ float part[32];
     __shared__ float inv_s;
@@ -346,6 +361,8 @@ __device__ __forceinline__ float lm_okey_to_float(uint32_t k) {
 // different groups, hardly more. One CTA of 1024 threads per row.
 __global__ void __launch_bounds__(1024) probe_threshold_kernel(const LmParams P, uint32_t rank, uint32_t exact) {
     const uint32_t b = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;  // 1024 threads: a row's probe is one round of 16-byte loads
+    pdl_wait();               // the probe pass's logits
+    pdl_launch_dependents();  // the main pass may set itself up and start its contraction meanwhile
     __shared__ uint32_t hist[256];
     __shared__ uint32_t sel_digit, sel_need;
     const float* row = P.probe_out + (size_t)b * P.probe_cols;
@@ -472,6 +489,23 @@ uint32_t lm_head_stages(uint32_t n_pad, size_t max_dyn_smem) {
 
 size_t lm_head_smem_bytes(uint32_t n_pad, uint32_t stages) { return (size_t)stages * (A_STAGE_BYTES + (size_t)n_pad * KCHUNK * 2u) + 1024u; }
 
+// A launch that may start before its predecessor on the stream has finished (programmatic stream serialization);
+// the kernels place their own waits.
+template <class... Params, class... Args>
+static cudaError_t launch_after(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, Params(args)...);
+}
+
 cudaError_t lm_head_configure(size_t max_dyn_smem) {
     return cudaFuncSetAttribute(lm_head_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)max_dyn_smem);
 }
@@ -492,14 +526,12 @@ int launch_lm_head(const LmParams& P, const void* embed, const void* x_norm, uin
     // small batches leave room for two CTAs per SM (each with half of tensor memory): more loads in flight
     const uint32_t slots = sm_count * P.ctas_per_sm;
     const uint32_t grid = P.n_items < slots ? P.n_items : slots;
-    lm_head_kernel<<<grid, LM_THREADS, lm_head_smem_bytes(P.n_pad, P.stages), stream>>>(map_w, map_x, P);
-    *cuda_error = cudaGetLastError();
+    *cuda_error = launch_after(lm_head_kernel, dim3(grid), dim3(LM_THREADS), lm_head_smem_bytes(P.n_pad, P.stages), stream, map_w, map_x, P);
     return *cuda_error == cudaSuccess ? 0 : -3;
 }
 
 cudaError_t launch_probe_threshold(const LmParams& P, uint32_t rank, bool exact, cudaStream_t stream) {
-    probe_threshold_kernel<<<P.batch, 1024, 0, stream>>>(P, rank, exact ? 1u : 0u);
-    return cudaGetLastError();
+    return launch_after(probe_threshold_kernel, dim3(P.batch), dim3(1024), 0, stream, P, rank, exact ? 1u : 0u);
 }
 
 }  // namespace llmc
