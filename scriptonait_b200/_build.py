@@ -25,6 +25,7 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-fmad=false", "-prec-div=true", "-prec-sqrt=true", "-ftz=false",
     "-Xcompiler", "-fPIC", "-shared", "-cudart", "shared",
+    "--threads", "0", "-split-compile", "0",   # the streaming kernel's 32 variants are assembled side by side
 ]
 
 
