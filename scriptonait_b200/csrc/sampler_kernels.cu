@@ -1915,6 +1915,11 @@ int plan_launch(const DeviceInfo& dev, const KParams& base, bool top_k_known, ui
         // would measure it from its own, lower maximum and keep far too much
         split = 1u;
     }
+    // a scalar rank cut above 64 is cheapest with the threshold sampled from the row's first stage (kernel MODE 3),
+    // which needs the row in one CTA: with a few dozen rows or more that beats filling the machine with shards
+    const bool sampled_fits = plan->mode == 2 && base.out_q == nullptr && base.full_keys_wanted && top_k_hint > 64u &&
+                              (uint64_t)top_k_hint * 8u <= base.vocab;
+    if (split == 0u && sampled_fits && (uint64_t)base.batch * 8u >= dev.sm_count) split = 1u;
     if (split == 0u) {
         const uint32_t target = 4u * dev.sm_count;
         split = target / (base.batch ? base.batch : 1u);
@@ -1934,8 +1939,7 @@ int plan_launch(const DeviceInfo& dev, const KParams& base, bool top_k_known, ui
     plan->shard_cols = shard_cols;
     // exact-selection launches with a scalar rank cut above 64 (and at most an eighth of the row) whose rows are
     // not split and that draw tokens: the threshold is sampled from the first stage (kernel MODE 3)
-    if (plan->mode == 2 && split == 1u && base.out_q == nullptr && base.full_keys_wanted && top_k_hint > 64u &&
-        (uint64_t)top_k_hint * 8u <= base.vocab) {
+    if (sampled_fits && split == 1u) {
         plan->mode = 3;
         plan->sample_threshold = true;
     }
