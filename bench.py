@@ -408,6 +408,27 @@ def run_ours(args, rank, world, local_rank):
                                    "rows_ordered_in_global_scratch": int(((flags & native.ROW_FULL_SORT) != 0).sum())}
             del x, call
 
+    # ------------------------------------------------------------------ the training-side row reduction (cross-entropy + gradient)
+    cross_entropy = None
+    if not args.skip_others and not args.only_lm_head:
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(77 + rank)
+        xs = [torch.randn((BATCH, VOCAB), generator=gen, device=dev, dtype=torch.float32) * 2.0 for _ in range(3)]  # 394 MB > L2
+        tg = torch.randint(0, VOCAB, (BATCH,), generator=gen, device=dev, dtype=torch.int32)
+        entry = {"rows_per_gpu": BATCH, "vocab": VOCAB, "logits": "f32 N(0, 2^2), three batches rotating (394 MB against 126 MB of L2)"}
+        for key, want in (("loss_and_gradient", True), ("loss_only", False)):
+            fns = [(lambda x=x: sampler.cross_entropy(x, tg, want_grad=want)) for x in xs]
+            for f in fns:
+                f()
+            us = statistics.median(timed(fns, 20) for _ in range(5)) / 20 * 1e3
+            by = BATCH * VOCAB * (8 if want else 4)
+            entry[key] = {"us_per_step": us, "algorithmic_gbs_per_gpu": by / us / 1e3, "frac_of_measured_peak": by / us / 1e3 / peak,
+                          "algorithmic_bytes": by}
+        entry["note"] = ("llm_cuda_cross_entropy: row loss + (softmax - one-hot) / rows; algorithmic bytes = 4 per logit read "
+                         "(+ 4 written with the gradient; its second read of the row comes from L2)")
+        cross_entropy = entry
+        del xs
+
     # ------------------------------------------------------------------ c5, vocabulary sharded over the ranks (N > 1)
     c5_shard = None
     if world > 1 and not args.skip_others and not args.only_lm_head:
@@ -535,7 +556,8 @@ def run_ours(args, rank, world, local_rank):
             "ms_per_step_strict_order": ms_per_step_strict,
             "overlapped_tokens_equal_strict_order": overlap_same,
             "region_ms_min_median_max": [min(regions), ms_region, max(regions)],
-            "strong_scaling": strong, "others": others, "full_ordering": full_ordering, "c5_vocab_shard": c5_shard,
+            "strong_scaling": strong, "others": others, "full_ordering": full_ordering, "cross_entropy_rows": cross_entropy,
+            "c5_vocab_shard": c5_shard,
             "lm_head_fused": lm_head})
         line = {
             "metric": METRIC, "value": value, "unit": "rows/s", "n_gpus": world, "steps": args.steps,

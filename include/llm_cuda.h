@@ -296,6 +296,19 @@ int32_t llm_cuda_advance_rows(llm_cuda_sampler* s, uint32_t batch, const uint32_
 int32_t llm_cuda_pack_allowed(llm_cuda_sampler* s, const uint8_t* allowed_host, uint32_t n, uint32_t* bits_out,
                               void* stream);
 
+/* Cross-entropy over the rows of a [rows, vocab] f32 logits matrix and its gradient with respect to the
+ * logits: the training-side row reduction next to the sampler's softmax. Replaces
+ * crates/llm-gpu/src/shaders/cross_entropy.wgsl:29-88 / llm_core::ops::cross_entropy
+ * (crates/llm-core/src/ops/loss.rs:20-45):
+ *   row_loss[t]    = ln(sum_v exp(x[t,v] - max_t)) + max_t - x[t, targets[t]]      (the mean over t is the loss)
+ *   d_logits[t, v] = (softmax(x[t,:])[v] - (v == targets[t])) / rows                (optional: may be NULL)
+ * All pointers are device pointers; `d_logits` uses the logits' row stride and must share the logits' base
+ * alignment modulo 16 bytes (a tensor of the same shape does). A target outside [0, vocab) gives that row a
+ * NaN loss (the reference panics). Asynchronous on `stream`. */
+int32_t llm_cuda_cross_entropy(llm_cuda_sampler* s, const float* logits, uint32_t rows, uint32_t vocab,
+                               uint32_t row_stride_elems, const uint32_t* targets, float* row_loss, float* d_logits,
+                               void* stream);
+
 /* Reads and clears the handle's device status word after `stream` has drained (this call synchronises
  * the stream). The kernels never wait without a limit: a wait that runs out gives the row up
  * (LLM_CUDA_ROW_INVALID, token 0) and sets a LLM_CUDA_STATUS_* bit here instead of hanging or guessing.

@@ -291,5 +291,20 @@ def penalized_at_history(logits: np.ndarray, cfg: SamplingConfig, recent: Sequen
     return out
 
 
+def cross_entropy(logits: np.ndarray, targets: Sequence[int], want_grad: bool = True):
+    """llm_core::ops::cross_entropy (ops/loss.rs:20-45): (mean loss, d_logits [T, V] or None, per-row loss terms)."""
+    x = np.ascontiguousarray(logits, dtype=np.float32)
+    t_len, vocab = x.shape
+    tg = np.ascontiguousarray(np.asarray(targets, dtype=np.uint32))
+    assert tg.size == t_len and (tg < vocab).all()
+    d = np.zeros_like(x) if want_grad else None
+    rl = np.zeros(t_len, np.float32)
+    L = lib()
+    L.oracle_cross_entropy.restype = C.c_float
+    L.oracle_cross_entropy.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p]
+    mean = float(L.oracle_cross_entropy(_ptr(x), _ptr(tg), t_len, vocab, _ptr(d), _ptr(rl)))
+    return mean, d, rl
+
+
 def hardware_threads() -> int:
     return int(lib().oracle_hardware_threads())

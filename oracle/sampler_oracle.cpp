@@ -422,6 +422,41 @@ void oracle_penalized_at_history(const float* logits, uint32_t vocab, const orac
         out[j] = recent[j] < vocab ? work[recent[j]] : std::numeric_limits<float>::quiet_NaN();
 }
 
+// llm_core::ops::cross_entropy (crates/llm-core/src/ops/loss.rs:20-45), statement by statement: per row the
+// maximum (fold from -inf, :26), the exponentials and their left-to-right f32 sum (:27-32), the row's loss
+// ln(sum) + max - row[target] added to a running f32 total (:33-35), the gradient (exp / sum - one-hot) / T
+// (:36-40); returns total / T (:42). `row_loss` (optional) receives each row's own term, which is what
+// crates/llm-gpu/src/shaders/cross_entropy.wgsl:72-74 writes per row.
+float oracle_cross_entropy(const float* logits, const uint32_t* targets, uint32_t t_len, uint32_t vocab, float* d_logits,
+                           float* row_loss) {
+    float total_loss = 0.0f;
+    std::vector<float> exps(vocab);
+    for (uint32_t t = 0; t < t_len; ++t) {
+        const float* row = logits + (size_t)t * vocab;
+        float max = -std::numeric_limits<float>::infinity();
+        for (uint32_t i = 0; i < vocab; ++i) max = std::fmax(max, row[i]);
+        float sum = 0.0f;
+        for (uint32_t i = 0; i < vocab; ++i) {
+            const float e = std::exp(row[i] - max);
+            exps[i] = e;
+            sum += e;
+        }
+        const uint32_t target = targets[t];
+        const float log_z = std::log(sum) + max;
+        const float term = log_z - row[target];
+        total_loss += term;
+        if (row_loss) row_loss[t] = term;
+        if (d_logits) {
+            float* d_row = d_logits + (size_t)t * vocab;
+            for (uint32_t i = 0; i < vocab; ++i) {
+                const float p = exps[i] / sum;
+                d_row[i] = (p - (i == target ? 1.0f : 0.0f)) / (float)t_len;
+            }
+        }
+    }
+    return total_loss / (float)t_len;
+}
+
 uint32_t oracle_hardware_threads(void) {
     unsigned n = std::thread::hardware_concurrency();
     return n ? n : 1;

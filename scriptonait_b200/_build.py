@@ -18,8 +18,8 @@ LIBRARY = os.path.join(LIBDIR, "libllm_cuda.so")
 # the same sources with -DLLM_CUDA_CHECKED: stores at computed shared-memory / scratch offsets are compared with their
 # bounds first (a violation sets a status bit and skips the store). The tests run small and odd shapes against it.
 CHECKED_LIBRARY = os.path.join(LIBDIR, "libllm_cuda_checked.so")
-SOURCES = ["sampler_kernels.cu", "llm_cuda_api.cu", "no_alloc.cu", "lm_head.cu"]
-HEADERS = ["sampler_kernels.h", "sampler_device.cuh", "lm_head.h", os.path.join("..", "..", "include", "llm_cuda.h")]
+SOURCES = ["sampler_kernels.cu", "llm_cuda_api.cu", "no_alloc.cu", "lm_head.cu", "cross_entropy.cu"]
+HEADERS = ["sampler_kernels.h", "sampler_device.cuh", "lm_head.h", "cross_entropy.h", os.path.join("..", "..", "include", "llm_cuda.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -43,7 +43,7 @@ EXPORTS = [
     "llm_cuda_sample", "llm_cuda_shard_select", "llm_cuda_merge_draw", "llm_cuda_advance_rows",
     "llm_cuda_pack_allowed", "llm_cuda_last_launch_info", "llm_cuda_sample_batch_static", "llm_cuda_static_last_error",
     "llm_cuda_device_status", "llm_cuda_test_hold_full_sort_slots", "llm_cuda_packed_candidates_bytes",
-    "llm_cuda_shard_select_packed", "llm_cuda_merge_draw_packed", "llm_cuda_lm_head_sample",
+    "llm_cuda_shard_select_packed", "llm_cuda_merge_draw_packed", "llm_cuda_lm_head_sample", "llm_cuda_cross_entropy",
 ]
 STATIC_MAX_BATCH, STATIC_MAX_TOP_K, STATIC_MAX_HISTORY = 64, 256, 512
 
@@ -140,6 +140,8 @@ def load(checked: bool = False) -> C.CDLL:
     L.llm_cuda_pack_allowed.argtypes = [vp, vp, u32, vp, vp]
     L.llm_cuda_last_launch_info.restype = i32
     L.llm_cuda_last_launch_info.argtypes = [vp, C.POINTER(u32), C.POINTER(u32)]
+    L.llm_cuda_cross_entropy.restype = i32
+    L.llm_cuda_cross_entropy.argtypes = [vp, vp, u32, u32, u32, vp, vp, vp, vp]
     L.llm_cuda_packed_candidates_bytes.restype = C.c_size_t
     L.llm_cuda_packed_candidates_bytes.argtypes = [u32, u32]
     L.llm_cuda_shard_select_packed.restype = i32

@@ -13,6 +13,7 @@
 
 #include "../../include/llm_cuda.h"
 #include "sampler_kernels.h"
+#include "cross_entropy.h"
 #include "lm_head.h"
 
 using namespace llmc;
@@ -690,6 +691,24 @@ int32_t llm_cuda_pack_allowed(llm_cuda_sampler* s, const uint8_t* allowed_host, 
     CUDA_TRY(s, cudaMemcpyAsync(s->arena, allowed_host, n, cudaMemcpyHostToDevice, st));
     CUDA_TRY(s, launch_pack_allowed(s->arena, n, bits_out, st));
     CUDA_TRY(s, cudaStreamSynchronize(st));  // the staging buffer is reused by the next host-buffer call
+    return LLM_CUDA_OK;
+}
+
+int32_t llm_cuda_cross_entropy(llm_cuda_sampler* s, const float* logits, uint32_t rows, uint32_t vocab, uint32_t row_stride_elems,
+                               const uint32_t* targets, float* row_loss, float* d_logits, void* stream) {
+    if (!s) return fail(nullptr, LLM_CUDA_ERR_BAD_ARGUMENT, "sampler handle is NULL");
+    if (rows == 0u) return LLM_CUDA_OK;
+    if (!logits || !targets || !row_loss) return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "logits, targets or row_loss is NULL");
+    if (vocab == 0u) return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "vocab is 0");
+    const uint32_t stride = row_stride_elems ? row_stride_elems : vocab;
+    if (stride < vocab) return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "row stride %u below vocab %u", stride, vocab);
+    if ((reinterpret_cast<uintptr_t>(logits) & 3u) || (d_logits && (reinterpret_cast<uintptr_t>(d_logits) & 3u)))
+        return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "logits or d_logits pointer not 4-byte aligned");
+    // the gradient is written with the same split into leading elements and 16-byte vectors as the row is read
+    if (d_logits && ((reinterpret_cast<uintptr_t>(logits) ^ reinterpret_cast<uintptr_t>(d_logits)) & 15u))
+        return fail(s, LLM_CUDA_ERR_BAD_ARGUMENT, "d_logits must share the logits' alignment modulo 16 bytes");
+    CUDA_TRY(s, cudaSetDevice(s->device));
+    CUDA_TRY(s, llmc::launch_cross_entropy_rows(logits, rows, vocab, stride, targets, row_loss, d_logits, static_cast<cudaStream_t>(stream)));
     return LLM_CUDA_OK;
 }
 

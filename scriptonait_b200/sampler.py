@@ -511,6 +511,29 @@ class Sampler:
         self._check(self._lib.llm_cuda_pack_allowed(self._h, a.ctypes.data, a.size, bits.data_ptr(), st))
         return bits, int(a.size)
 
+    def cross_entropy(self, logits, targets, want_grad: bool = True):
+        """llm_core::ops::cross_entropy (ops/loss.rs:20-45; shaders/cross_entropy.wgsl) over device tensors: `logits`
+        [T, V] float32, `targets` [T] int32. Returns (row_loss [T], d_logits [T, V] or None); the loss is
+        row_loss.mean(), the gradient is already divided by T."""
+        torch = _torch()
+        if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+            raise ValueError("logits must be a [T, V] float32 tensor with contiguous rows")
+        t_len, vocab = int(logits.shape[0]), int(logits.shape[1])
+        if targets.dtype != torch.int32 or targets.numel() != t_len or not targets.is_contiguous():
+            raise ValueError("targets must be a contiguous int32 tensor with one entry per row")
+        row_loss = torch.empty(t_len, dtype=torch.float32, device=logits.device)
+        grad = None
+        if want_grad:
+            # same strides, and the same offset from a 16-byte boundary: the kernel splits both rows alike
+            span = (t_len - 1) * int(logits.stride(0)) + vocab
+            lead = (logits.data_ptr() % 16) // 4
+            grad = torch.empty(span + 4, dtype=torch.float32, device=logits.device)[lead:lead + span].as_strided(
+                tuple(logits.shape), tuple(logits.stride()))
+        st = torch.cuda.current_stream(logits.device).cuda_stream
+        self._check(self._lib.llm_cuda_cross_entropy(self._h, logits.data_ptr(), t_len, vocab, int(logits.stride(0)), targets.data_ptr(),
+                                                     row_loss.data_ptr(), grad.data_ptr() if want_grad else None, st))
+        return row_loss, grad
+
     # ------------------------------------------------------------------ host-buffer path
     def sample_batch_host(self, logits: np.ndarray, *, temperature=1.0, top_k=0, top_p=1.0, min_p=0.0,
                           repetition_penalty=1.0, history: Optional[np.ndarray] = None,
