@@ -2,6 +2,8 @@
 
     python -m scriptonait_b200.timing c4-k64 c5 --steps 200
 
+`ce` times `llm_cuda_cross_entropy` (loss + gradient) over 256 x 128256 f32 logits instead.
+
 Logits are resident on the GPU; a step is one `llm_cuda_sample_batch` call over the whole batch.
 Inputs rotate over enough copies of the batch to exceed the 126 MB L2 (a copy holds the same values
 at another address, so every step misses L2 the same way). Timed with CUDA events on the launching
@@ -62,6 +64,27 @@ def time_workload(sampler: Sampler, w: workloads.Workload, steps: int, warmup: i
             "kernels_per_step": kernels, "ctas_per_row": split, "copies": copies, "overlap": overlap, "steps": steps}
 
 
+def time_cross_entropy(sampler: Sampler, steps: int, warmup: int) -> dict:
+    import torch
+    rows, vocab = 256, 128256
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(77)
+    xs = [torch.randn((rows, vocab), generator=gen, device="cuda") * 2.0 for _ in range(3)]  # 394 MB against 126 MB of L2
+    tg = torch.randint(0, vocab, (rows,), generator=gen, device="cuda", dtype=torch.int32)
+    for i in range(max(warmup, 3)):
+        sampler.cross_entropy(xs[i % 3], tg)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        sampler.cross_entropy(xs[i % 3], tg)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) / steps * 1e3
+    return {"workload": "ce", "rows": rows, "vocab": vocab, "logits_dtype": "f32", "us_per_step": us,
+            "algorithmic_gbs": rows * vocab * 8 / us / 1e3, "kernels_per_step": 1, "copies": 3, "steps": steps}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     ap.add_argument("workloads", nargs="*", default=["c3", "c2", "c4-k1", "c4-k64", "c4-k1024", "c5", "c1"])
@@ -73,7 +96,8 @@ def main() -> None:
     sampler = Sampler(device=0, max_batch=1024, max_vocab=262144, max_history=512, max_top_k=1024)
     try:
         for name in args.workloads:
-            line = time_workload(sampler, make(name), args.steps, args.warmup, args.overlap)
+            line = (time_cross_entropy(sampler, args.steps, args.warmup) if name == "ce"
+                    else time_workload(sampler, make(name), args.steps, args.warmup, args.overlap))
             if args.peak_gbs > 0:
                 line["frac_of_peak"] = line["algorithmic_gbs"] / args.peak_gbs
             print(json.dumps(line), flush=True)
