@@ -112,6 +112,13 @@ class Sampler {
         check(llm_cuda_sample_batch(h_, &args));
     }
 
+    // llm_core::ops::cross_entropy over device pointers (crates/llm-core/src/ops/loss.rs:20-45): per-row loss terms
+    // and, unless d_logits is null, the gradient already divided by `rows`; see llm_cuda_cross_entropy.
+    void cross_entropy(const float* logits, uint32_t rows, uint32_t vocab, const uint32_t* targets, float* row_loss,
+                       float* d_logits = nullptr, uint32_t row_stride_elems = 0, void* stream = nullptr) {
+        check(llm_cuda_cross_entropy(h_, logits, rows, vocab, row_stride_elems, targets, row_loss, d_logits, stream));
+    }
+
   private:
     void check(int32_t rc) {
         if (rc != LLM_CUDA_OK) throw Error(rc, llm_cuda_last_error(h_));
