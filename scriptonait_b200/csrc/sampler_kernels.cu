@@ -1719,16 +1719,6 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
 
     if (P.split == 1u) {
         const int undecided = finish_row(P, b, rc, n, overflow, qmax, S, cand_q, cand_i, scratch, window_filtered, sampled);
-#ifdef LLMC_DEV_TWICE  // experiment: the same tail once more, now with its instructions cached
-        if (!undecided) {
-            cta_sync();
-            if (tid == 0) S.sortmax = 0u;
-            cta_sync();
-            PHASE(14);
-            (void)finish_row(P, b, rc, n, overflow, qmax, S, cand_q, cand_i, scratch, window_filtered);
-            PHASE(15);
-        }
-#endif
         if (undecided)
             // the window alone is tried first, unless it is most of the row anyway
             full_sort_row(P, b, *reinterpret_cast<FullShared*>(ring), reinterpret_cast<uint32_t*>(ring + 512), hkeys, hcnt,
