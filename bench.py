@@ -269,6 +269,12 @@ def run_ours(args, rank, world, local_rank):
     overlapped_tokens = [t.clone() for t in tokens_per_buffer]  # what the overlapped launches left, per buffer
     strict_regions = [timed(calls_strict, args.steps) for _ in range(min(len(regions), 40))]
     ms_per_step_strict = statistics.median(strict_regions) / args.steps
+    # the same strict data order with the grid set up early (overlap_previous = 2): what a decode loop can use
+    calls_early = prepared(dev_logits, tokens_per_buffer, 2)
+    for i in range(3):
+        calls_early[i % N_BUFFERS]()
+    early_regions = [timed(calls_early, args.steps) for _ in range(min(len(regions), 40))]
+    ms_per_step_early = statistics.median(early_regions) / args.steps
     for c in calls_strict:  # every buffer's tokens from the overlapped launches must equal a strict-order launch's (untimed)
         c()
     torch.cuda.synchronize()
@@ -554,6 +560,7 @@ def run_ours(args, rank, world, local_rank):
                             "each launch may start streaming while the previous step's launch finishes "
                             "(programmatic dependent launch); independent batches with their own outputs",
             "ms_per_step_strict_order": ms_per_step_strict,
+            "ms_per_step_strict_order_early_launch": ms_per_step_early,
             "overlapped_tokens_equal_strict_order": overlap_same,
             "region_ms_min_median_max": [min(regions), ms_region, max(regions)],
             "strong_scaling": strong, "others": others, "full_ordering": full_ordering, "cross_entropy_rows": cross_entropy,
