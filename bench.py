@@ -122,8 +122,18 @@ class ClockSampler:
             for name, val in zip(names, parts[3:7]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+        out = {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+               "samples": len(sm), "reasons": sorted(reasons)}
+        watts = []
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            try:
+                watts.append(float(parts[2]))
+            except (IndexError, ValueError):
+                pass
+        if watts:
+            out["power_w"] = statistics.median(watts)
+        return out
 
 
 def cpu_rows_per_s(w, rows: int, threads: int, reps: int) -> float:
@@ -530,6 +540,16 @@ def run_ours(args, rank, world, local_rank):
                      "logits_bytes_never_written": Bd * Vv * 4}
             if bf16_peak:
                 entry["frac_of_measured_bf16_peak_sustained"] = entry["tflops"] / bf16_peak
+            if Bd == 256 and rank == 0:
+                # the contraction-bound batch runs near the power limit: clocks and power over about a second of fused steps
+                cs = ClockSampler(sel)
+                cs.start()
+                t_end = time.time() + 1.2
+                while time.time() < t_end:
+                    for _ in range(200):
+                        fused()
+                    torch.cuda.synchronize()
+                entry["clocks_under_load"] = cs.stop()
             lm_head[f"batch{Bd}"] = entry
         lm_head["note"] = ("final RMSNorm + tied LM head (tcgen05, TMA) + top-k/top-p sampling, logits never written; one read of the "
                            "1.05 GB embedding per step bounds the small batch (HBM), the contraction the large one")
