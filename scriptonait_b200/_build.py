@@ -18,14 +18,15 @@ LIBRARY = os.path.join(LIBDIR, "libllm_cuda.so")
 # the same sources with -DLLM_CUDA_CHECKED: stores at computed shared-memory / scratch offsets are compared with their
 # bounds first (a violation sets a status bit and skips the store). The tests run small and odd shapes against it.
 CHECKED_LIBRARY = os.path.join(LIBDIR, "libllm_cuda_checked.so")
-SOURCES = ["sampler_kernels.cu", "llm_cuda_api.cu", "no_alloc.cu", "lm_head.cu", "cross_entropy.cu"]
+SOURCES = ["sampler_kernels.cu", "stream_variants_f32.cu", "stream_variants_f32_tables.cu", "stream_variants_bf16.cu",
+           "stream_variants_bf16_tables.cu", "llm_cuda_api.cu", "no_alloc.cu", "lm_head.cu", "cross_entropy.cu"]
 HEADERS = ["sampler_kernels.h", "sampler_device.cuh", "lm_head.h", "cross_entropy.h", os.path.join("..", "..", "include", "llm_cuda.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-fmad=false", "-prec-div=true", "-prec-sqrt=true", "-ftz=false",
     "-Xcompiler", "-fPIC", "-shared", "-cudart", "shared",
-    "--threads", "0", "-split-compile", "0",   # the streaming kernel's 32 variants are assembled side by side
+    "--threads", "0",   # the translation units compile side by side (the streaming kernel's variants are four of them)
 ]
 
 

@@ -540,7 +540,7 @@ __device__ __forceinline__ void sort_keys64_regs(uint32_t n, float* cand_q, uint
 }
 
 // Not inlined: the network's registers stay out of the streaming kernel's own allocation.
-__device__ __noinline__ void sort_keys64(uint32_t n, float* cand_q, uint32_t* cand_i, uint64_t* keys) {
+static __device__ __noinline__ void sort_keys64(uint32_t n, float* cand_q, uint32_t* cand_i, uint64_t* keys) {
     if (n <= 2u * THREADS)
         sort_keys64_regs<2>(n, cand_q, cand_i, keys);
     else if (n <= 4u * THREADS)
@@ -932,7 +932,7 @@ __device__ __noinline__ uint32_t cta_chain(const float* v, uint32_t n, int kind,
 // almost no L1).
 //   generate.rs:374, the left-to-right f32 sum. Once the sum is >= 1 a term below 2^-24 is under half an
 //   ulp and leaves it unchanged, and the terms only get smaller.
-__device__ __noinline__ float tail_sum(const float* probs, uint32_t n) {
+static __device__ __noinline__ float tail_sum(const float* probs, uint32_t n) {
     float s = 0.0f;
     thread_chain<1>(
         probs, n, s, [](float acc, float e) { return __fadd_rn(acc, e); }, [](float, float, float) { return false; },
@@ -942,7 +942,7 @@ __device__ __noinline__ float tail_sum(const float* probs, uint32_t n) {
 //   generate.rs:397-409; the later re-summation of the kept prefix (:411) repeats the same additions. The
 //   running sum never falls: it has reached top_p inside a block iff it is there at the block's end.
 //   Returns the first index that reaches top_p (n if none, or if top_p is 1); the sum so far in *total.
-__device__ __noinline__ uint32_t tail_cumulative(const float* probs, uint32_t n, float top_p, float* total) {
+static __device__ __noinline__ uint32_t tail_cumulative(const float* probs, uint32_t n, float top_p, float* total) {
     float acc = 0.0f;
     auto add = [](float a, float p) { return __fadd_rn(a, p); };
     auto never = [](float, float) { return false; };
@@ -958,7 +958,7 @@ __device__ __noinline__ uint32_t tail_cumulative(const float* probs, uint32_t n,
 //   generate.rs:413-418 stops at the first entry with r < p. r starts at u * total >= 0, and r - p rounds to
 //   a negative number exactly when r < p; from there on it only falls: a block holds that entry iff r is
 //   negative at the block's end. Returns that entry's index (n if there is none).
-__device__ __noinline__ uint32_t tail_walk(const float* probs, uint32_t n, float r) {
+static __device__ __noinline__ uint32_t tail_walk(const float* probs, uint32_t n, float r) {
     return thread_chain<2>(
         probs, n, r, [](float acc, float p) { return __fsub_rn(acc, p); }, [](float before, float, float p) { return before < p; },
         [](float after) { return after < 0.0f; }, [](float, float) { return false; });

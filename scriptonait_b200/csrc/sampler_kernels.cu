@@ -171,7 +171,7 @@ __device__ __forceinline__ uint32_t warp_rth_largest(uint32_t key, uint32_t r, u
 // and either the ordered tail (token out) or the candidate list out. `scratch`
 // is EPILOGUE_SCRATCH bytes of shared memory nothing else uses any more.
 // `need_k`: the candidates came from a sampled threshold, and only decide the row if at least k_eff of them exist.
-__device__ int finish_row(const KParams& P, uint32_t b, const RowCfg& rc, uint32_t n, bool overflow, float qmax, Shared& S,
+static __device__ int finish_row(const KParams& P, uint32_t b, const RowCfg& rc, uint32_t n, bool overflow, float qmax, Shared& S,
                            float* cand_q, uint32_t* cand_i, unsigned char* scratch, bool window_filtered = false,
                            bool need_k = false) {
     float* probs = reinterpret_cast<float*>(scratch);                               // up to MAX_SORT floats
@@ -248,7 +248,7 @@ __device__ int finish_row(const KParams& P, uint32_t b, const RowCfg& rc, uint32
 constexpr uint32_t LIST_SORTED = 0x40000000u;  // flag in a list's count: entries are in the reference order
 constexpr uint32_t LIST_COUNT = 0x3fffffffu;
 
-__device__ uint32_t merge_lists(const KParams& P, uint32_t b, const RowCfg& rc, uint32_t nsh, Shared& S, float* cand_q,
+static __device__ uint32_t merge_lists(const KParams& P, uint32_t b, const RowCfg& rc, uint32_t nsh, Shared& S, float* cand_q,
                                 uint32_t* cand_i, bool& overflow, float& qmax, bool all_sorted = false) {
     const uint32_t LOWEST = 0x007fffffu;  // okey(-inf)
     if (threadIdx.x == 0) {
@@ -371,7 +371,7 @@ struct FullShared {
 
 // Claims a free scratch slot. Every holder is a running CTA of this same grid that releases its
 // slot without waiting for anyone, so a bounded poll is enough; 0xffffffff when the bound runs out.
-__device__ uint32_t acquire_full_slot(const KParams& P) {
+static __device__ uint32_t acquire_full_slot(const KParams& P) {
     const uint32_t n = P.full_nslots;
     if (!P.full_slots || n == 0u) return 0xffffffffu;
     uint32_t i = (blockIdx.y * gridDim.x + blockIdx.x) % n;
@@ -476,7 +476,7 @@ __device__ __forceinline__ uint32_t build_all_keys_t(const RowSource& R, uint32_
     return valid;
 }
 
-__device__ __noinline__ uint32_t build_all_keys(const RowSource R, uint32_t* __restrict__ sk, uint32_t* __restrict__ si) {
+static __device__ __noinline__ uint32_t build_all_keys(const RowSource R, uint32_t* __restrict__ sk, uint32_t* __restrict__ si) {
     if (R.allowed_bits || R.has_pen) return build_all_keys_t<true>(R, sk, si);
     return build_all_keys_t<false>(R, sk, si);
 }
@@ -544,7 +544,7 @@ __device__ __forceinline__ uint32_t build_window_keys_t(const KParams& P, const 
     return run_base;
 }
 
-__device__ __noinline__ uint32_t build_window_keys(const KParams& P, const RowSource R, float win_qmax, uint32_t* __restrict__ sk,
+static __device__ __noinline__ uint32_t build_window_keys(const KParams& P, const RowSource R, float win_qmax, uint32_t* __restrict__ sk,
                                                    uint32_t* __restrict__ si, uint32_t cap, uint32_t* work) {
     if (R.allowed_bits || R.has_pen) return build_window_keys_t<true>(P, R, win_qmax, sk, si, cap, work);
     return build_window_keys_t<false>(P, R, win_qmax, sk, si, cap, work);
@@ -586,7 +586,7 @@ __device__ __forceinline__ void count_digit(uint32_t* hist, uint32_t d, bool hav
 // a digit: scattered 4-byte stores, one memory transaction each, cost more than everything else in
 // the pass together. The next tile's keys are already on their way while this tile is placed.
 // Sorts n_all (key, column) pairs; the pointers are exchanged so that sk / si hold the result.
-__device__ __noinline__ void radix_sort_row(const KParams& P, uint32_t n_all, uint32_t*& sk_io, uint32_t*& si_io, uint32_t*& dk_io, uint32_t*& di_io,
+static __device__ __noinline__ void radix_sort_row(const KParams& P, uint32_t n_all, uint32_t*& sk_io, uint32_t*& si_io, uint32_t*& dk_io, uint32_t*& di_io,
                                             uint32_t* work) {
     const uint32_t tid = threadIdx.x;
     const unsigned lane = tid & 31u, warp = tid >> 5;
@@ -754,7 +754,7 @@ __device__ __noinline__ void radix_sort_row(const KParams& P, uint32_t n_all, ui
 // maximum after temperature): first only the row's significance window is ordered - usually a few
 // thousand values instead of the whole row - with the same rules about what such a truncated ordering
 // can and cannot decide as the shared-memory path; the whole row follows only if it cannot.
-__device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullShared& F, uint32_t* work, uint32_t* hkeys,
+static __device__ __noinline__ void full_sort_row(const KParams& P, uint32_t b, FullShared& F, uint32_t* work, uint32_t* hkeys,
                                            uint32_t* hcnt, bool try_window = false, float win_qmax = 0.0f) {
     const uint32_t tid = threadIdx.x;
     const uint32_t V = P.vocab;
@@ -1777,6 +1777,84 @@ __global__ void __launch_bounds__(STREAM_THREADS, 4) stream_select_kernel(const 
                       undecided == 1 && rc.windowed && !(S.error & 4u) && qmax > neg_inf(), qmax);
 }
 
+// ---------------------------------------------------------------------------
+// The streaming kernel's 32 variants are compiled in four translation units of eight (one per element type
+// and with / without the mask and penalty tables), each of which includes this file with
+// LLMC_STREAM_ELEM / LLMC_STREAM_BITS / LLMC_STREAM_TAG defined and exports two host functions:
+// configure_stream_<tag> and launch_stream_<tag>. The units compile side by side, and every build gives the
+// same binary (nvcc's own splitting of one unit does not: its output, and its speed, varied from build to build).
+#ifdef LLMC_STREAM_ELEM
+template <typename ElemT, bool BITS, int MODE, int U>
+static cudaError_t configure_one(int v) {
+    cudaError_t e = cudaFuncSetAttribute(stream_select_kernel<ElemT, BITS, MODE, U>, cudaFuncAttributeMaxDynamicSharedMemorySize, v);
+    if (e != cudaSuccess) return e;
+    // four CTAs of ~55 KB each only fit when the SM's L1/shared split favours shared memory
+    return cudaFuncSetAttribute(stream_select_kernel<ElemT, BITS, MODE, U>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                (int)cudaSharedmemCarveoutMaxShared);
+}
+
+template <typename ElemT, bool BITS>
+static cudaError_t configure_stream(int v) {
+    cudaError_t e;
+    if ((e = configure_one<ElemT, BITS, 0, 3>(v)) != cudaSuccess) return e;
+    if ((e = configure_one<ElemT, BITS, 1, 3>(v)) != cudaSuccess) return e;
+    if ((e = configure_one<ElemT, BITS, 2, 3>(v)) != cudaSuccess) return e;
+    if ((e = configure_one<ElemT, BITS, 3, 3>(v)) != cudaSuccess) return e;
+    if ((e = configure_one<ElemT, BITS, 0, 4>(v)) != cudaSuccess) return e;
+    if ((e = configure_one<ElemT, BITS, 1, 4>(v)) != cudaSuccess) return e;
+    if ((e = configure_one<ElemT, BITS, 2, 4>(v)) != cudaSuccess) return e;
+    return configure_one<ElemT, BITS, 3, 4>(v);
+}
+
+template <typename ElemT, bool BITS, int MODE, int U>
+static cudaError_t launch_stream_t(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap) {
+    auto kern = stream_select_kernel<ElemT, BITS, MODE, U>;
+    dim3 grid(plan.split, P.batch, 1);
+    if (!overlap) {
+        kern<<<grid, STREAM_THREADS, plan.smem, stream>>>(P);
+        return cudaGetLastError();
+    }
+    // programmatic dependent launch: the grid may start while the previous kernel of the stream is
+    // still running, if that kernel allows it (this kernel does, at its first instruction); it reads
+    // only its inputs until its dependency wait, which returns once the previous grid has finished
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(STREAM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = plan.smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, P);
+}
+
+template <typename ElemT, bool BITS, int MODE>
+static cudaError_t launch_stream_u(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap) {
+    if (plan.stage_u == 4u) return launch_stream_t<ElemT, BITS, MODE, 4>(P, plan, stream, overlap);
+    return launch_stream_t<ElemT, BITS, MODE, 3>(P, plan, stream, overlap);
+}
+
+template <typename ElemT, bool BITS>
+static cudaError_t launch_stream_m(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap) {
+    if (plan.mode == 1) return launch_stream_u<ElemT, BITS, 1>(P, plan, stream, overlap);
+    if (plan.mode == 2) return launch_stream_u<ElemT, BITS, 2>(P, plan, stream, overlap);
+    if (plan.mode == 3) return launch_stream_u<ElemT, BITS, 3>(P, plan, stream, overlap);
+    return launch_stream_u<ElemT, BITS, 0>(P, plan, stream, overlap);
+}
+
+#define LLMC_CAT2(a, b) a##b
+#define LLMC_CAT(a, b) LLMC_CAT2(a, b)
+cudaError_t LLMC_CAT(configure_stream_, LLMC_STREAM_TAG)(int max_dyn_smem) {
+    return configure_stream<LLMC_STREAM_ELEM, LLMC_STREAM_BITS>(max_dyn_smem);
+}
+cudaError_t LLMC_CAT(launch_stream_, LLMC_STREAM_TAG)(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap) {
+    return launch_stream_m<LLMC_STREAM_ELEM, LLMC_STREAM_BITS>(P, plan, stream, overlap);
+}
+#endif  // LLMC_STREAM_ELEM
+
+#ifndef LLMC_KERNELS_ONLY  // a translation unit that only wants the streaming kernel's variants stops here
 // Ordered tail over gathered candidate lists: one CTA per row.
 __global__ void __launch_bounds__(THREADS) merge_draw_kernel(const __grid_constant__ KParams P) {
     extern __shared__ __align__(128) unsigned char dyn[];
@@ -1850,7 +1928,6 @@ __global__ void pack_allowed_kernel(const uint8_t* allowed, uint32_t n, uint32_t
     bits[w] = word;
 }
 
-#ifndef LLMC_KERNELS_ONLY  // a translation unit that only wants some kernel instantiations stops here
 // ---------------------------------------------------------------------------
 // host side: launch plans
 #ifdef LLMC_DEV
@@ -2027,84 +2104,21 @@ void dev_override(int key, int value) {
 }
 #endif
 
-template <typename ElemT, bool BITS, int MODE, int U>
-static cudaError_t configure_one(int v) {
-    cudaError_t e = cudaFuncSetAttribute(stream_select_kernel<ElemT, BITS, MODE, U>, cudaFuncAttributeMaxDynamicSharedMemorySize, v);
-    if (e != cudaSuccess) return e;
-    // four CTAs of ~55 KB each only fit when the SM's L1/shared split favours shared memory
-    return cudaFuncSetAttribute(stream_select_kernel<ElemT, BITS, MODE, U>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                (int)cudaSharedmemCarveoutMaxShared);
-}
-
-template <typename ElemT, bool BITS>
-static cudaError_t configure_stream(int v) {
-    cudaError_t e;
-    if ((e = configure_one<ElemT, BITS, 0, 3>(v)) != cudaSuccess) return e;
-    if ((e = configure_one<ElemT, BITS, 1, 3>(v)) != cudaSuccess) return e;
-    if ((e = configure_one<ElemT, BITS, 2, 3>(v)) != cudaSuccess) return e;
-    if ((e = configure_one<ElemT, BITS, 3, 3>(v)) != cudaSuccess) return e;
-    if ((e = configure_one<ElemT, BITS, 0, 4>(v)) != cudaSuccess) return e;
-    if ((e = configure_one<ElemT, BITS, 1, 4>(v)) != cudaSuccess) return e;
-    if ((e = configure_one<ElemT, BITS, 2, 4>(v)) != cudaSuccess) return e;
-    return configure_one<ElemT, BITS, 3, 4>(v);
-}
-
 cudaError_t configure_kernels(size_t max_dyn_smem) {
     const int v = (int)max_dyn_smem;
     cudaError_t e;
-    if ((e = configure_stream<float, false>(v)) != cudaSuccess) return e;
-    if ((e = configure_stream<float, true>(v)) != cudaSuccess) return e;
-    if ((e = configure_stream<uint16_t, false>(v)) != cudaSuccess) return e;
-    if ((e = configure_stream<uint16_t, true>(v)) != cudaSuccess) return e;
+    if ((e = configure_stream_f32(v)) != cudaSuccess) return e;
+    if ((e = configure_stream_f32_tables(v)) != cudaSuccess) return e;
+    if ((e = configure_stream_bf16(v)) != cudaSuccess) return e;
+    if ((e = configure_stream_bf16_tables(v)) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(merge_draw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, v)) != cudaSuccess) return e;
     return cudaSuccess;
 }
 
-template <typename ElemT, bool BITS, int MODE, int U>
-static cudaError_t launch_stream_t(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap) {
-    auto kern = stream_select_kernel<ElemT, BITS, MODE, U>;
-    dim3 grid(plan.split, P.batch, 1);
-    if (!overlap) {
-        kern<<<grid, STREAM_THREADS, plan.smem, stream>>>(P);
-        return cudaGetLastError();
-    }
-    // programmatic dependent launch: the grid may start while the previous kernel of the stream is
-    // still running, if that kernel allows it (this kernel does, at its first instruction); it reads
-    // only its inputs until its dependency wait, which returns once the previous grid has finished
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = grid;
-    cfg.blockDim = dim3(STREAM_THREADS, 1, 1);
-    cfg.dynamicSmemBytes = plan.smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kern, P);
-}
-
-template <typename ElemT, bool BITS, int MODE>
-static cudaError_t launch_stream_u(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap) {
-    if (plan.stage_u == 4u) return launch_stream_t<ElemT, BITS, MODE, 4>(P, plan, stream, overlap);
-    return launch_stream_t<ElemT, BITS, MODE, 3>(P, plan, stream, overlap);
-}
-
-template <typename ElemT, bool BITS>
-static cudaError_t launch_stream_m(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap) {
-    if (plan.mode == 1) return launch_stream_u<ElemT, BITS, 1>(P, plan, stream, overlap);
-    if (plan.mode == 2) return launch_stream_u<ElemT, BITS, 2>(P, plan, stream, overlap);
-    if (plan.mode == 3) return launch_stream_u<ElemT, BITS, 3>(P, plan, stream, overlap);
-    return launch_stream_u<ElemT, BITS, 0>(P, plan, stream, overlap);
-}
-
 cudaError_t launch_stream_select(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap) {
-    if (P.dtype == LLM_CUDA_DTYPE_BF16) {
-        return plan.bits ? launch_stream_m<uint16_t, true>(P, plan, stream, overlap)
-                         : launch_stream_m<uint16_t, false>(P, plan, stream, overlap);
-    }
-    return plan.bits ? launch_stream_m<float, true>(P, plan, stream, overlap)
-                     : launch_stream_m<float, false>(P, plan, stream, overlap);
+    if (P.dtype == LLM_CUDA_DTYPE_BF16)
+        return plan.bits ? launch_stream_bf16_tables(P, plan, stream, overlap) : launch_stream_bf16(P, plan, stream, overlap);
+    return plan.bits ? launch_stream_f32_tables(P, plan, stream, overlap) : launch_stream_f32(P, plan, stream, overlap);
 }
 
 cudaError_t launch_merge_draw(const KParams& P, const LaunchPlan& plan, cudaStream_t stream) {

@@ -102,6 +102,15 @@ struct LaunchPlan {
 
 // Raises the dynamic shared-memory limit of every kernel; once per device.
 cudaError_t configure_kernels(size_t max_dyn_smem);
+// the four translation units of the streaming kernel's variants (stream_variants_*.cu)
+cudaError_t configure_stream_f32(int max_dyn_smem);
+cudaError_t configure_stream_f32_tables(int max_dyn_smem);
+cudaError_t configure_stream_bf16(int max_dyn_smem);
+cudaError_t configure_stream_bf16_tables(int max_dyn_smem);
+cudaError_t launch_stream_f32(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap);
+cudaError_t launch_stream_f32_tables(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap);
+cudaError_t launch_stream_bf16(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap);
+cudaError_t launch_stream_bf16_tables(const KParams& P, const LaunchPlan& plan, cudaStream_t stream, bool overlap);
 
 // Chooses candidate capacity, CTAs per row and shared-memory layout. Returns 0, or -1
 // when the layout does not fit in shared memory.
